@@ -1,0 +1,125 @@
+"""Per-sample operations.
+
+Every function here takes torch tensors.  CUDA tensors are served by the
+hand-written sm_100a kernels in ``opacus_b200/csrc`` (bound in :mod:`._cuda`);
+a missing or stale extension on a machine with a GPU is an error, never a
+silent fallback.  CPU tensors are served by the plain-PyTorch statements in
+:mod:`._ref`, which are also the test oracle.
+"""
+from typing import Optional
+
+import torch
+
+from . import _ref
+
+_cuda = None
+
+
+def _k():
+    """The CUDA binding module, loaded on first use."""
+    global _cuda
+    if _cuda is None:
+        from . import _cuda as mod
+
+        mod.load()
+        _cuda = mod
+    return _cuda
+
+
+def _on_gpu(*ts) -> bool:
+    return any(t is not None and t.is_cuda for t in ts)
+
+
+def _kernel_dtype(t: torch.Tensor) -> bool:
+    return t.dtype in (torch.bfloat16, torch.float16, torch.float32)
+
+
+# ----------------------------------------------------------------------- Linear
+def linear_grad_sample(a, g):
+    if _on_gpu(a, g) and _kernel_dtype(g) and g.shape[0] > 0:
+        return _k().linear_grad_sample(a, g)
+    return _ref.linear_grad_sample(a, g)
+
+
+def linear_bias_grad_sample(g):
+    return _ref.linear_bias_grad_sample(g)
+
+
+def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0):
+    if _on_gpu(a, g) and _kernel_dtype(g) and g.shape[0] > 0:
+        return _k().linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+    return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+
+
+def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False):
+    if _on_gpu(a, g) and _kernel_dtype(g) and g.shape[0] > 0:
+        return _k().linear_weighted_grad(a, g, c, g_scale, want_bias)
+    return _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+
+
+# -------------------------------------------------------------------- Embedding
+def embedding_grad_sample(ids, g, num_embeddings):
+    return _ref.embedding_grad_sample(ids, g, num_embeddings)
+
+
+def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None):
+    if _on_gpu(g) and _kernel_dtype(g) and g.shape[0] > 0:
+        return _k().embedding_norm_sq(ids, g, g_scale, padding_idx)
+    return _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+
+
+def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None):
+    if _on_gpu(g) and _kernel_dtype(g) and g.shape[0] > 0:
+        return _k().embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype)
+    return _ref.embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype)
+
+
+# ----------------------------------------------------------- normalisation layers
+def affine_grad_sample(xhat, g, keep_last=0, channel_dim=False, want_weight=True, want_bias=True):
+    return _ref.affine_grad_sample(xhat, g, keep_last, channel_dim, want_weight, want_bias)
+
+
+def norm_affine_grad_sample(kind, x, g, *, eps, normalized_ndim=1, num_groups=1, want_weight=True, want_bias=True):
+    """Per-sample affine-parameter gradients of a normalisation layer from its
+    *input* ``x``: the normalised activation is recomputed inside the kernel, in
+    one pass over ``x`` and ``g``.  ``kind`` is ``"layer"``, ``"rms"``,
+    ``"group"`` or ``"instance"``."""
+    if _on_gpu(x, g) and _kernel_dtype(g) and g.shape[0] > 0 and _k().supports_norm(kind, x, normalized_ndim):
+        return _k().norm_affine_grad_sample(kind, x, g, eps, normalized_ndim, num_groups, want_weight, want_bias)
+    import torch.nn.functional as F
+
+    if kind == "layer":
+        xhat = F.layer_norm(x, x.shape[x.dim() - normalized_ndim:], eps=eps)
+        return _ref.affine_grad_sample(xhat, g, keep_last=normalized_ndim, want_weight=want_weight, want_bias=want_bias)
+    if kind == "rms":
+        xhat = F.rms_norm(x, x.shape[x.dim() - normalized_ndim:], eps=eps)
+        return _ref.affine_grad_sample(xhat, g, keep_last=normalized_ndim, want_weight=want_weight, want_bias=False)
+    if kind == "group":
+        xhat = F.group_norm(x, num_groups, eps=eps)
+    elif kind == "instance":
+        xhat = F.instance_norm(x, eps=eps)
+    else:
+        raise ValueError(kind)
+    return _ref.affine_grad_sample(xhat, g, channel_dim=True, want_weight=want_weight, want_bias=want_bias)
+
+
+# --------------------------------------------------------------- clipping pieces
+def clip_factor(norm_sq, max_grad_norm: float):
+    if _on_gpu(norm_sq) and norm_sq.dtype == torch.float32 and norm_sq.numel() > 0:
+        return _k().clip_factor(norm_sq, max_grad_norm)
+    return _ref.clip_factor(norm_sq, max_grad_norm)
+
+
+def grad_sample_norm_sq(gs):
+    if _on_gpu(gs) and _kernel_dtype(gs) and gs.shape[0] > 0:
+        return _k().grad_sample_norm_sq(gs)
+    return _ref.grad_sample_norm_sq(gs)
+
+
+def weighted_sum(gs, c):
+    if _on_gpu(gs) and _kernel_dtype(gs) and gs.shape[0] > 0:
+        return _k().weighted_sum(gs, c)
+    return _ref.weighted_sum(gs, c)
+
+
+gaussian_like = _ref.gaussian_like
