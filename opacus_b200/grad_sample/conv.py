@@ -1,0 +1,82 @@
+"""Conv1d/2d/3d rules.
+
+Per-sample gradient: ``gs[n] = G[n] unfold(x[n])^T`` with the contraction over
+output positions; groups are handled block by block (no off-diagonal blocks are
+ever formed).  The clipped sum is an ordinary convolution weight gradient with
+``G`` scaled per sample.
+
+Behavioural parity: ``opacus/grad_sample/conv.py:28-119``.
+"""
+from typing import Dict, List, Union
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..utils.tensor_utils import unfold_nd
+from .utils import register_grad_sampler, register_wgrad_sampler
+
+_CONVS = [nn.Conv1d, nn.Conv2d, nn.Conv3d]
+
+
+def _base_type(layer):
+    """FSDP2 renames a wrapped ``Conv2d`` to ``FSDPConv2d(FSDPModule, Conv2d)``."""
+    for cls in type(layer).__mro__:
+        if cls in _CONVS:
+            return cls
+    return type(layer)
+
+
+@register_grad_sampler(_CONVS)
+def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], activations: List[torch.Tensor],
+                             backprops: torch.Tensor) -> Dict[nn.Parameter, torch.Tensor]:
+    x = activations[0].to(backprops.dtype)
+    n = x.shape[0]
+    want_b = layer.bias is not None and layer.bias.requires_grad
+    if n == 0:
+        out = {layer.weight: torch.zeros_like(layer.weight).unsqueeze(0)}
+        if want_b:
+            out[layer.bias] = torch.zeros_like(layer.bias).unsqueeze(0)
+        return out
+    cols = unfold_nd(x, kernel_size=layer.kernel_size, padding=layer.padding, stride=layer.stride,
+                     dilation=layer.dilation)                      # [n, C*k, L]
+    L = cols.shape[-1]
+    g = backprops.reshape(n, layer.out_channels, L)                # [n, O, L]
+    out = {}
+    if layer.weight.requires_grad:
+        G_ = layer.groups
+        k = cols.shape[1] // layer.in_channels
+        cols_g = cols.reshape(n * G_, (layer.in_channels // G_) * k, L)
+        g_g = g.reshape(n * G_, layer.out_channels // G_, L)
+        gs = torch.bmm(g_g, cols_g.transpose(1, 2))                # [n*G, O/G, C/G*k]
+        out[layer.weight] = gs.reshape((n,) + tuple(layer.weight.shape))
+    if want_b:
+        out[layer.bias] = g.sum(dim=2)
+    return out
+
+
+@register_wgrad_sampler(_CONVS)
+def compute_conv_weighted_grad(layer, activations, backprops, coef, g_scale: float = 1.0):
+    x = activations[0]
+    shape = (-1,) + (1,) * (backprops.dim() - 1)
+    gw = backprops * (coef.to(backprops.dtype) * g_scale).reshape(shape)
+    out = {}
+    if layer.weight.requires_grad:
+        pad = layer.padding
+        if isinstance(pad, str):
+            # explicit symmetric/asymmetric padding, then a "valid" weight gradient
+            nsp = x.dim() - 2
+            if pad == "same":
+                pads = []
+                for k_, d_ in zip(layer.kernel_size, layer.dilation):
+                    tot = d_ * (k_ - 1)
+                    pads.append((tot // 2, tot - tot // 2))
+                x = F.pad(x, [v for lr in reversed(pads) for v in lr])
+            pad = (0,) * nsp
+        fn = {nn.Conv1d: torch.nn.grad.conv1d_weight, nn.Conv2d: torch.nn.grad.conv2d_weight,
+              nn.Conv3d: torch.nn.grad.conv3d_weight}[_base_type(layer)]
+        out[layer.weight] = fn(x.to(gw.dtype), layer.weight.shape, gw, stride=layer.stride, padding=pad,
+                               dilation=layer.dilation, groups=layer.groups)
+    if layer.bias is not None and layer.bias.requires_grad:
+        out[layer.bias] = gw.reshape(gw.shape[0], gw.shape[1], -1).sum(dim=(0, 2))
+    return out

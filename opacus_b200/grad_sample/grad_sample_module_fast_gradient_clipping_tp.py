@@ -1,0 +1,103 @@
+"""Ghost clipping under 1-d tensor parallelism ("ghost_tp").
+
+Every rank holds a shard of each parallel weight, so a layer's sampler yields
+the squared norm of the local shard of the per-sample gradient.  The global
+squared norm is the sum over tensor-parallel ranks.  Parameters that are *not*
+sharded (plain tensors, or an Embedding sharded along its rows where every rank
+sees the same per-sample gradient rows) must be counted once: only rank 0 of
+the group contributes them (``param.merge_flag = False``).
+
+Accepted parameter kinds: ``DTensor`` parameters from
+``torch.distributed.tensor.parallel.parallelize_module`` and the
+``ColumnParallelLinear``/``RowParallelLinear`` layers of
+:mod:`opacus_b200.parallel.tensor_parallel`, which mark their weights with
+``tp_sharded = True``.
+
+Behavioural parity: ``opacus/grad_sample/grad_sample_module_fast_gradient_clipping_tp.py:33-147``.
+"""
+from __future__ import annotations
+
+import logging
+import warnings
+
+import torch
+import torch.nn as nn
+
+from .grad_sample_module_fast_gradient_clipping import GradSampleHooksFastGradientClipping
+from .gsm_base import AbstractGradSampleModule
+
+logger = logging.getLogger(__name__)
+
+
+def _is_dtensor(p) -> bool:
+    try:
+        from torch.distributed.tensor import DTensor
+    except Exception:  # pragma: no cover
+        return False
+    return isinstance(p, DTensor)
+
+
+class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping):
+    def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
+                 force_functorch=False, max_grad_norm=1, use_ghost_clipping=True, single_pass: bool = False,
+                 process_group=None):
+        self.process_group = process_group
+        super().__init__(m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
+                         force_functorch=force_functorch, max_grad_norm=max_grad_norm,
+                         use_ghost_clipping=use_ghost_clipping, single_pass=single_pass)
+        self.set_pattern_param_sample_norm_sum()
+        warnings.warn("Opacus TP is currently in beta. Custom model output placements may cause unexpected behavior.")
+
+    def set_pattern_param_sample_norm_sum(self):
+        """Decide per parameter whether every rank's norm counts (sharded) or only rank 0's."""
+        for module in self.iterate_submodules(self._module):
+            for _, p in module.named_parameters():
+                if not p.requires_grad:
+                    continue
+                if getattr(p, "tp_sharded", False):
+                    p.merge_flag = True
+                elif not _is_dtensor(p):
+                    p.merge_flag = False
+                elif isinstance(module, nn.Embedding) and p.placements[0].is_shard(0):
+                    p.merge_flag = False
+                elif p.placements[0].is_replicate():
+                    p.merge_flag = False
+                    raise NotImplementedError(
+                        "We currently do not support replicated model parameters, due to the constraint of "
+                        "fsdpoptimizwer. This means that nn.Linear.bias must be disabled or configured to be sharded."
+                    )
+                else:
+                    p.merge_flag = True
+
+    def _group_rank(self) -> int:
+        return torch.distributed.get_rank(self.process_group)
+
+    def get_norm_sample(self) -> torch.Tensor:
+        first = self._group_rank() == 0
+        sq = None
+        for p in self.trainable_parameters:
+            if not p.merge_flag and not first:
+                continue
+            v = p._norm_sample.float().square()
+            sq = v if sq is None else sq + v
+        if sq is None:
+            ref = self.trainable_parameters[0]._norm_sample
+            sq = torch.zeros_like(ref, dtype=torch.float32)
+        torch.distributed.all_reduce(sq, op=torch.distributed.ReduceOp.SUM, group=self.process_group)
+        norm = sq.sqrt()
+        self.per_sample_gradient_norms = norm
+        return norm
+
+    def get_clipping_coef(self) -> torch.Tensor:
+        norm = self.get_norm_sample()
+        return (self.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
+
+
+class GradSampleModuleFastGradientClippingTP(GradSampleHooksFastGradientClippingTP, AbstractGradSampleModule):
+    def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
+                 force_functorch=False, max_grad_norm=1, process_group=None):
+        nn.Module.__init__(self)
+        GradSampleHooksFastGradientClippingTP.__init__(
+            self, m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
+            force_functorch=force_functorch, max_grad_norm=max_grad_norm, process_group=process_group)
+        self.grad_accumulation_hook = None

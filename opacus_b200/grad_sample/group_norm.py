@@ -1,0 +1,27 @@
+"""GroupNorm: per-channel affine, reduce spatial axes
+(``opacus/grad_sample/group_norm.py:26-47``)."""
+from typing import Dict, List
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .utils import register_grad_sampler
+
+
+@register_grad_sampler(nn.GroupNorm)
+def compute_group_norm_grad_sample(layer: nn.GroupNorm, activations: List[torch.Tensor],
+                                   backprops: torch.Tensor) -> Dict[nn.Parameter, torch.Tensor]:
+    if layer.weight is None:
+        return {}
+    want_w = layer.weight.requires_grad
+    want_b = layer.bias is not None and layer.bias.requires_grad
+    gw, gb = ops.norm_affine_grad_sample(
+        "group", activations[0], backprops, eps=layer.eps, num_groups=layer.num_groups,
+        want_weight=want_w, want_bias=want_b)
+    out = {}
+    if want_w:
+        out[layer.weight] = gw
+    if want_b:
+        out[layer.bias] = gb
+    return out

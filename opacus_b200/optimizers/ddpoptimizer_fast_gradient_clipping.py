@@ -1,0 +1,44 @@
+"""Data-parallel optimiser for ghost clipping
+(``opacus/optimizers/ddpoptimizer_fast_gradient_clipping.py:25-83``)."""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+from torch.optim import Optimizer
+
+from ._collectives import all_reduce_grads
+from .optimizer_fast_gradient_clipping import DPOptimizerFastGradientClipping
+
+
+class DistributedDPOptimizerFastGradientClipping(DPOptimizerFastGradientClipping):
+    _fused_ok = False
+
+    def __init__(self, optimizer: Optimizer, *, noise_multiplier: float, max_grad_norm: float,
+                 expected_batch_size: Optional[int], loss_reduction: str = "mean", generator=None,
+                 secure_mode: bool = False, **kwargs):
+        super().__init__(optimizer, noise_multiplier=noise_multiplier, max_grad_norm=max_grad_norm,
+                         expected_batch_size=expected_batch_size, loss_reduction=loss_reduction,
+                         generator=generator, secure_mode=secure_mode, **kwargs)
+        self.rank = torch.distributed.get_rank()
+        self.world_size = torch.distributed.get_world_size()
+
+    def add_noise(self):
+        if self.rank == 0:
+            super().add_noise()
+        else:
+            for p in self.params:
+                p.grad = p.summed_grad.view_as(p)
+
+    def reduce_gradients(self):
+        grads = [p.grad for p in self.params if p.requires_grad]
+        all_reduce_grads(grads, average_by=self.world_size if self.loss_reduction == "mean" else 1)
+
+    def step(self, closure: Optional[Callable[[], float]] = None) -> Optional[torch.Tensor]:
+        if closure is not None:
+            with torch.enable_grad():
+                closure()
+        if self.pre_step():
+            self.reduce_gradients()
+            return self.original_optimizer.step()
+        return None

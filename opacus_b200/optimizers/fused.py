@@ -1,0 +1,65 @@
+"""Fused noise + scale + update for SGD / Adam / AdamW inner optimisers.
+
+One multi-tensor kernel launch per step reads every ``summed_grad`` once,
+draws the Gaussian noise from a counter-based Philox stream (seeded from the
+torch generator, so ``torch.manual_seed`` / ``noise_generator=`` keep their
+meaning), writes the private gradient back (it is exposed as ``p.grad``) and
+updates the parameter and the optimiser state in the layout
+``torch.optim`` itself uses, so ``state_dict()`` stays interchangeable.
+
+Replaces ``opacus/optimizers/optimizer.py:477-504,570`` (three elementwise
+passes plus the inner optimiser's own kernels per parameter).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+class _FusedPlan:
+    def __init__(self, kind: str):
+        self.kind = kind  # "sgd" | "adam" | "adamw"
+
+    def run(self, opt, *, noise_std: float, denominator: float):
+        from ..ops import _k
+
+        inner = opt.original_optimizer
+        gen = opt.generator
+        k = _k()
+        for group in inner.param_groups:
+            ps = [p for p in group["params"] if p.requires_grad and getattr(p, "summed_grad", None) is not None]
+            if not ps:
+                continue
+            k.fused_dp_step(self.kind, inner, group, ps, noise_std=noise_std, inv_scale=1.0 / denominator,
+                            generator=gen)
+            for p in ps:
+                p.grad = p.summed_grad.view_as(p)
+
+
+def plan_for(opt) -> Optional[_FusedPlan]:
+    """A plan if every parameter is a CUDA tensor and the wrapped optimiser is a
+    configuration the kernel implements; else ``None`` (the staged path runs)."""
+    cached = getattr(opt, "_fused_plan_cache", None)
+    inner = opt.original_optimizer
+    if cached is not None and cached[0] is type(inner):
+        return cached[1]
+    plan = None
+    ps = opt.params
+    ok = bool(ps) and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in ps)
+    if ok:
+        t = type(inner)
+        if t is torch.optim.SGD:
+            ok = all(not g.get("maximize", False) and not g.get("differentiable", False) for g in inner.param_groups)
+            plan = _FusedPlan("sgd") if ok else None
+        elif t in (torch.optim.Adam, torch.optim.AdamW):
+            ok = all(
+                not g.get("amsgrad", False) and not g.get("maximize", False) and not g.get("capturable", False)
+                and not g.get("differentiable", False) and not isinstance(g["lr"], torch.Tensor)
+                for g in inner.param_groups
+            )
+            decoupled = t is torch.optim.AdamW or any(g.get("decoupled_weight_decay", False)
+                                                      for g in inner.param_groups)
+            plan = _FusedPlan("adamw" if decoupled else "adam") if ok else None
+    opt._fused_plan_cache = (type(inner), plan)
+    return plan
