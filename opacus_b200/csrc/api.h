@@ -1,0 +1,84 @@
+// C interface of the sm_100a kernels.  Every function enqueues work on `stream`
+// and returns a cudaError_t value (0 = success) for launch/argument errors.
+// Pointers are device pointers unless stated otherwise.  `status` points to four
+// 32-bit words in device memory, zeroed by the caller; a kernel that had to give
+// up on a bounded wait writes a non-zero code there and returns early.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- ghost norms: out_w[n] (+)= scale * <X_n X_n^T, G_n G_n^T>, out_b[n] (+)= scale * sum(G_n G_n^T)
+// x: [B, T, d_x] bf16 (or NULL), ids: [B, T] int64 (or NULL; used when x is NULL: X X^T := [id_t == id_s]),
+// g: [B, T, d_g] bf16.  scratch: at least dpk_gram_pair_scratch_floats(B, T) floats.
+size_t dpk_gram_pair_scratch_floats(int B, int T);
+int dpk_gram_pair_norm(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g, float scale,
+                       float* scratch, float* out_w, float* out_b, int accumulate, uint32_t* status,
+                       cudaStream_t stream);
+
+// ---- clipped weight gradient: out[M, N] = beta*out + sum_k Gs[k, m] * A[k, n]   (bf16 in, fp32 accumulate)
+// gs: [K, M] bf16 row-major, a: [K, N] bf16 row-major, out: [M, N] fp32 or bf16 (out_bf16 != 0).
+int dpk_wgrad_tn(const void* gs, const void* a, int K, int M, int N, void* out, int out_bf16, float beta,
+                 uint32_t* status, cudaStream_t stream);
+
+// ---- elementwise / reduction kernels
+// y[r, :] = bf16(x[r, :] * c[r / rows_per_sample] * scale)
+int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, int64_t rows, int64_t cols,
+                   int64_t rows_per_sample, float scale, cudaStream_t stream);
+// c[n] = min(1, C / (sqrt(max(norm_sq[n], 0)) + 1e-6))
+int dpk_clip_factor(const float* norm_sq, float* c, int64_t B, float max_grad_norm, cudaStream_t stream);
+// out[n] (+)= sum_j x[n, j]^2    (x: fp32 / bf16 / fp16 by elem_kind 0/1/2)
+int dpk_row_norm_sq(const void* x, int elem_kind, int64_t B, int64_t cols, float* out, int accumulate,
+                    cudaStream_t stream);
+// out[j] = sum_n c[n] * x[n, j]  (out fp32)
+int dpk_weighted_sum(const void* x, int elem_kind, const float* c, int64_t B, int64_t cols, float* out,
+                     cudaStream_t stream);
+// per-sample 2-d input fast path: out_w[n] (+)= scale * |a_n|^2 |g_n|^2, out_b[n] (+)= scale * |g_n|^2
+int dpk_outer_norm_sq(const void* a, const void* g, int elem_kind, int64_t B, int64_t d_a, int64_t d_g, float scale,
+                      float* out_w, float* out_b, int accumulate, cudaStream_t stream);
+// Normalisation layers: per-sample affine gradients from the layer input x and output gradient g.
+// kind 0 = LayerNorm, 1 = RMSNorm over the last `d` elements of [B, rows, d];  gw/gb: [B, d] fp32.
+// stats_scratch: 2 * B * rows floats of scratch (per-row mean and reciprocal std).
+int dpk_norm_lastdim_grad(int kind, const void* x, const void* g, int elem_kind, int64_t B, int64_t rows, int64_t d,
+                          float eps, float* stats_scratch, float* gw, float* gb, cudaStream_t stream);
+// kind 2 = GroupNorm / InstanceNorm on [B, C, S] with `groups` groups; gw/gb: [B, C] fp32.
+int dpk_norm_channel_grad(const void* x, const void* g, int elem_kind, int64_t B, int64_t C, int64_t S, int groups,
+                          float eps, float* gw, float* gb, cudaStream_t stream);
+// Embedding clipped gradient: out[ids[r], :] += c[r / T] * scale * g[r, :]   (out fp32 [V, D], zeroed by caller)
+int dpk_embedding_scatter(const int64_t* ids, const void* g, int elem_kind, const float* c, int64_t rows, int64_t T,
+                          int64_t D, int64_t V, int64_t padding_idx, float scale, float* out, cudaStream_t stream);
+
+// ---- fused noise + scale + optimiser update over a table of tensors
+struct DpkTensorEntry {
+  void* param;         // fp32 or bf16 (param_bf16)
+  float* grad;         // in: clipped sum; out: private gradient (noised, scaled)
+  float* state0;       // SGD: momentum buffer (or NULL); Adam: exp_avg
+  float* state1;       // Adam: exp_avg_sq
+  float* master;       // optional fp32 master copy when param is bf16 (or NULL)
+  int64_t numel;
+  int64_t rng_offset;  // element offset of this tensor in the step's Philox stream
+  int32_t param_bf16;
+  int32_t pad;
+};
+struct DpkStepHyper {
+  int32_t kind;        // 0 sgd, 1 adam (L2 weight decay), 2 adamw (decoupled)
+  int32_t nesterov;
+  int32_t first_step;  // SGD momentum buffer not initialised yet
+  int32_t pad;
+  float lr, momentum, dampening, weight_decay;
+  float beta1, beta2, eps, bias_c1, bias_c2_sqrt;  // bias_c1 = 1 - beta1^t, bias_c2_sqrt = sqrt(1 - beta2^t)
+  float noise_std, inv_scale;
+  uint64_t seed, offset;
+};
+int dpk_fused_dp_step(const struct DpkTensorEntry* table_dev, int n_tensors, int64_t total_chunks,
+                      const int64_t* chunk_prefix_dev, struct DpkStepHyper h, cudaStream_t stream);
+
+// Standard normal samples (testing the generator): out[i] for i < n.
+int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,292 @@
+// Python bindings (module opacus_b200._C): thin tensor -> pointer marshalling
+// around the C interface in api.h.  All work is enqueued on the current torch
+// CUDA stream.  A kernel that gives up on a bounded wait records a code in a
+// pinned, device-visible status block; every call checks that block first and
+// raises if an earlier kernel failed.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <mutex>
+#include <vector>
+
+#include "api.h"
+
+namespace {
+
+struct StatusBlock {
+  uint32_t* host = nullptr;
+  uint32_t* dev = nullptr;
+};
+StatusBlock g_status[64];
+std::mutex g_mu;
+
+StatusBlock& status_for(int device) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  StatusBlock& s = g_status[device & 63];
+  if (s.host == nullptr) {
+    void* h = nullptr;
+    TORCH_CHECK(cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess,
+                "opacus_b200: cannot allocate the kernel status block");
+    memset(h, 0, 64);
+    void* d = nullptr;
+    TORCH_CHECK(cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess, "opacus_b200: cannot map the kernel status block");
+    s.host = static_cast<uint32_t*>(h);
+    s.dev = static_cast<uint32_t*>(d);
+  }
+  return s;
+}
+
+void raise_if_failed(int device) {
+  StatusBlock& s = status_for(device);
+  const uint32_t code = *reinterpret_cast<volatile uint32_t*>(s.host);
+  if (code != 0) {
+    const uint32_t blk = s.host[1], d0 = s.host[2], d1 = s.host[3];
+    s.host[0] = s.host[1] = s.host[2] = s.host[3] = 0;
+    TORCH_CHECK(false, "opacus_b200: a kernel gave up on a bounded wait (site ", code >> 8, ", code ", code & 0xff,
+                ", block ", blk, ", detail ", d0, "/", d1, "); its results are invalid");
+  }
+}
+
+void check(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "opacus_b200: ", what, " failed: ", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+}
+
+int elem_kind(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kBFloat16: return 1;
+    case at::kHalf: return 2;
+    default: TORCH_CHECK(false, "opacus_b200: unsupported dtype ", t.scalar_type());
+  }
+}
+
+void need_cuda_contig(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "opacus_b200: ", name, " must be a contiguous CUDA tensor");
+}
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// ------------------------------------------------------------------ ghost norms
+// x: [B,T,dx] bf16 or None; ids: [B,T] int64 or None; g: [B,T,dg] bf16.
+void gram_pair_norm(c10::optional<at::Tensor> x, c10::optional<at::Tensor> ids, at::Tensor g, double scale,
+                    at::Tensor scratch, c10::optional<at::Tensor> out_w, c10::optional<at::Tensor> out_b,
+                    bool accumulate) {
+  c10::cuda::CUDAGuard guard(g.device());
+  raise_if_failed(g.get_device());
+  need_cuda_contig(g, "g");
+  TORCH_CHECK(g.dim() == 3 && g.scalar_type() == at::kBFloat16, "g must be [B,T,d] bf16");
+  const int B = g.size(0), T = g.size(1), dg = g.size(2);
+  const void* xp = nullptr;
+  int dx = 0;
+  if (x.has_value()) {
+    need_cuda_contig(*x, "x");
+    TORCH_CHECK(x->dim() == 3 && x->scalar_type() == at::kBFloat16 && x->size(0) == B && x->size(1) == T,
+                "x must be [B,T,d] bf16");
+    xp = x->data_ptr();
+    dx = x->size(2);
+  }
+  const int64_t* idp = nullptr;
+  if (ids.has_value()) {
+    need_cuda_contig(*ids, "ids");
+    TORCH_CHECK(ids->scalar_type() == at::kLong && ids->numel() == (int64_t)B * T, "ids must be [B,T] int64");
+    idp = ids->data_ptr<int64_t>();
+  }
+  TORCH_CHECK(scratch.is_cuda() && scratch.scalar_type() == at::kFloat &&
+                  (size_t)scratch.numel() >= dpk_gram_pair_scratch_floats(B, T),
+              "scratch too small");
+  float* ow = out_w.has_value() ? out_w->data_ptr<float>() : nullptr;
+  float* ob = out_b.has_value() ? out_b->data_ptr<float>() : nullptr;
+  check(dpk_gram_pair_norm(xp, idp, g.data_ptr(), B, T, dx, dg, (float)scale, scratch.data_ptr<float>(), ow, ob,
+                           accumulate ? 1 : 0, status_for(g.get_device()).dev, stream()),
+        "gram_pair_norm");
+}
+
+int64_t gram_pair_scratch_floats(int64_t B, int64_t T) { return (int64_t)dpk_gram_pair_scratch_floats(B, T); }
+
+// ------------------------------------------------------------------ clipped weight gradient
+void wgrad_tn(at::Tensor gs, at::Tensor a, at::Tensor out, double beta) {
+  c10::cuda::CUDAGuard guard(gs.device());
+  raise_if_failed(gs.get_device());
+  need_cuda_contig(gs, "gs");
+  need_cuda_contig(a, "a");
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(gs.dim() == 2 && a.dim() == 2 && gs.size(0) == a.size(0), "gs [K,M] and a [K,N] expected");
+  TORCH_CHECK(gs.scalar_type() == at::kBFloat16 && a.scalar_type() == at::kBFloat16, "bf16 operands expected");
+  const int K = gs.size(0), M = gs.size(1), N = a.size(1);
+  TORCH_CHECK(out.numel() == (int64_t)M * N, "out must have M*N elements");
+  TORCH_CHECK(out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16, "out must be fp32 or bf16");
+  check(dpk_wgrad_tn(gs.data_ptr(), a.data_ptr(), K, M, N, out.data_ptr(), out.scalar_type() == at::kBFloat16,
+                     (float)beta, status_for(gs.get_device()).dev, stream()),
+        "wgrad_tn");
+}
+
+at::Tensor scale_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t rows_per_sample, double scale) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2, "x must be [rows, cols]");
+  TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "x must be fp32 or bf16");
+  at::Tensor y = at::empty(x.sizes(), x.options().dtype(at::kBFloat16));
+  const float* cp = nullptr;
+  if (c.has_value()) {
+    TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kFloat && c->is_contiguous(), "c must be fp32 CUDA");
+    cp = c->data_ptr<float>();
+  }
+  check(dpk_scale_rows(x.data_ptr(), x.scalar_type() == at::kFloat, cp, y.data_ptr(), x.size(0), x.size(1),
+                       rows_per_sample, (float)scale, stream()),
+        "scale_rows");
+  return y;
+}
+
+at::Tensor clip_factor(at::Tensor n2, double C) {
+  c10::cuda::CUDAGuard guard(n2.device());
+  need_cuda_contig(n2, "norm_sq");
+  TORCH_CHECK(n2.scalar_type() == at::kFloat, "norm_sq must be fp32");
+  at::Tensor c = at::empty_like(n2);
+  check(dpk_clip_factor(n2.data_ptr<float>(), c.data_ptr<float>(), n2.numel(), (float)C, stream()), "clip_factor");
+  return c;
+}
+
+at::Tensor row_norm_sq(at::Tensor x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  const int64_t B = x.size(0);
+  at::Tensor out = at::empty({B}, x.options().dtype(at::kFloat));
+  check(dpk_row_norm_sq(x.data_ptr(), elem_kind(x), B, B ? x.numel() / B : 0, out.data_ptr<float>(), 0, stream()),
+        "row_norm_sq");
+  return out;
+}
+
+at::Tensor weighted_sum(at::Tensor x, at::Tensor c) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(c, "c");
+  TORCH_CHECK(c.scalar_type() == at::kFloat && c.numel() == x.size(0), "c must be fp32 [B]");
+  const int64_t B = x.size(0), cols = x.numel() / B;
+  at::Tensor out = at::empty({cols}, x.options().dtype(at::kFloat));
+  check(dpk_weighted_sum(x.data_ptr(), elem_kind(x), c.data_ptr<float>(), B, cols, out.data_ptr<float>(), stream()),
+        "weighted_sum");
+  return out;
+}
+
+void outer_norm_sq(c10::optional<at::Tensor> a, at::Tensor g, double scale, c10::optional<at::Tensor> out_w,
+                   c10::optional<at::Tensor> out_b, bool accumulate) {
+  c10::cuda::CUDAGuard guard(g.device());
+  need_cuda_contig(g, "g");
+  const int64_t B = g.size(0);
+  const void* ap = nullptr;
+  int64_t da = 0;
+  if (a.has_value()) {
+    need_cuda_contig(*a, "a");
+    TORCH_CHECK(a->scalar_type() == g.scalar_type(), "a and g must share a dtype");
+    ap = a->data_ptr();
+    da = a->numel() / B;
+  }
+  check(dpk_outer_norm_sq(ap, g.data_ptr(), elem_kind(g), B, da, g.numel() / B, (float)scale,
+                          out_w.has_value() ? out_w->data_ptr<float>() : nullptr,
+                          out_b.has_value() ? out_b->data_ptr<float>() : nullptr, accumulate, stream()),
+        "outer_norm_sq");
+}
+
+std::vector<at::Tensor> norm_lastdim_grad(int64_t kind, at::Tensor x, at::Tensor g, int64_t d, double eps,
+                                          bool want_w, bool want_b) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(g, "g");
+  TORCH_CHECK(x.scalar_type() == g.scalar_type() && x.numel() == g.numel(), "x and g must match");
+  const int64_t B = x.size(0), rows = x.numel() / B / d;
+  auto opt = x.options().dtype(at::kFloat);
+  at::Tensor gw = want_w ? at::empty({B, d}, opt) : at::Tensor();
+  at::Tensor gb = want_b ? at::empty({B, d}, opt) : at::Tensor();
+  at::Tensor stats = at::empty({B * rows * 2}, opt);
+  check(dpk_norm_lastdim_grad((int)kind, x.data_ptr(), g.data_ptr(), elem_kind(x), B, rows, d, (float)eps,
+                              stats.data_ptr<float>(), want_w ? gw.data_ptr<float>() : nullptr,
+                              want_b ? gb.data_ptr<float>() : nullptr, stream()),
+        "norm_lastdim_grad");
+  return {gw, gb};
+}
+
+std::vector<at::Tensor> norm_channel_grad(at::Tensor x, at::Tensor g, int64_t groups, double eps, bool want_w,
+                                          bool want_b) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(g, "g");
+  TORCH_CHECK(x.scalar_type() == g.scalar_type() && x.numel() == g.numel() && x.dim() >= 2, "x and g must match");
+  const int64_t B = x.size(0), C = x.size(1), S = x.numel() / B / C;
+  auto opt = x.options().dtype(at::kFloat);
+  at::Tensor gw = want_w ? at::empty({B, C}, opt) : at::Tensor();
+  at::Tensor gb = want_b ? at::empty({B, C}, opt) : at::Tensor();
+  check(dpk_norm_channel_grad(x.data_ptr(), g.data_ptr(), elem_kind(x), B, C, S, (int)groups, (float)eps,
+                              want_w ? gw.data_ptr<float>() : nullptr, want_b ? gb.data_ptr<float>() : nullptr,
+                              stream()),
+        "norm_channel_grad");
+  return {gw, gb};
+}
+
+void embedding_scatter(at::Tensor ids, at::Tensor g, at::Tensor c, int64_t T, int64_t padding_idx, double scale,
+                       at::Tensor out) {
+  c10::cuda::CUDAGuard guard(g.device());
+  need_cuda_contig(ids, "ids");
+  need_cuda_contig(g, "g");
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && out.scalar_type() == at::kFloat && c.scalar_type() == at::kFloat,
+              "ids int64, out fp32, c fp32 expected");
+  const int64_t rows = ids.numel(), D = g.numel() / rows, V = out.size(0);
+  check(dpk_embedding_scatter(ids.data_ptr<int64_t>(), g.data_ptr(), elem_kind(g), c.data_ptr<float>(), rows, T, D, V,
+                              padding_idx, (float)scale, out.data_ptr<float>(), stream()),
+        "embedding_scatter");
+}
+
+// ------------------------------------------------------------------ fused DP step
+// table: uint8 CUDA tensor holding n DpkTensorEntry records; prefix: int64 CUDA [n+1].
+void fused_dp_step(at::Tensor table, at::Tensor prefix, int64_t n_tensors, int64_t total_chunks, int64_t kind,
+                   bool nesterov, bool first_step, double lr, double momentum, double dampening, double weight_decay,
+                   double beta1, double beta2, double eps, double bias_c1, double bias_c2_sqrt, double noise_std,
+                   double inv_scale, int64_t seed, int64_t offset) {
+  c10::cuda::CUDAGuard guard(table.device());
+  raise_if_failed(table.get_device());
+  TORCH_CHECK(table.is_cuda() && prefix.is_cuda() && prefix.scalar_type() == at::kLong, "bad table");
+  TORCH_CHECK((size_t)table.numel() >= sizeof(DpkTensorEntry) * (size_t)n_tensors, "table too small");
+  DpkStepHyper h{};
+  h.kind = (int)kind; h.nesterov = nesterov; h.first_step = first_step;
+  h.lr = (float)lr; h.momentum = (float)momentum; h.dampening = (float)dampening; h.weight_decay = (float)weight_decay;
+  h.beta1 = (float)beta1; h.beta2 = (float)beta2; h.eps = (float)eps; h.bias_c1 = (float)bias_c1;
+  h.bias_c2_sqrt = (float)bias_c2_sqrt; h.noise_std = (float)noise_std; h.inv_scale = (float)inv_scale;
+  h.seed = (uint64_t)seed; h.offset = (uint64_t)offset;
+  check(dpk_fused_dp_step(reinterpret_cast<const DpkTensorEntry*>(table.data_ptr()), (int)n_tensors, total_chunks,
+                          prefix.data_ptr<int64_t>(), h, stream()),
+        "fused_dp_step");
+}
+
+at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
+  c10::cuda::CUDAGuard guard(device);
+  at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  check(dpk_philox_normal(out.data_ptr<float>(), n, (uint64_t)seed, (uint64_t)offset, (float)std, stream()),
+        "philox_normal");
+  return out;
+}
+
+void check_status(int64_t device) { raise_if_failed((int)device); }
+
+int64_t tensor_entry_size() { return (int64_t)sizeof(DpkTensorEntry); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gram_pair_norm", &gram_pair_norm);
+  m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
+  m.def("wgrad_tn", &wgrad_tn);
+  m.def("scale_rows", &scale_rows);
+  m.def("clip_factor", &clip_factor);
+  m.def("row_norm_sq", &row_norm_sq);
+  m.def("weighted_sum", &weighted_sum);
+  m.def("outer_norm_sq", &outer_norm_sq);
+  m.def("norm_lastdim_grad", &norm_lastdim_grad);
+  m.def("norm_channel_grad", &norm_channel_grad);
+  m.def("embedding_scatter", &embedding_scatter);
+  m.def("fused_dp_step", &fused_dp_step);
+  m.def("philox_normal", &philox_normal);
+  m.def("check_status", &check_status);
+  m.def("tensor_entry_size", &tensor_entry_size);
+}

@@ -1,0 +1,461 @@
+// Bandwidth-bound kernels of the DP step: row scaling, clip factors, per-sample
+// squared norms, clip-weighted sums, normalisation-layer per-sample gradients,
+// embedding scatter, and the fused "noise + scale + optimiser update" pass with
+// an in-kernel Philox generator.  All of them stream their inputs once with
+// 16-byte accesses; none uses shared-memory tiling because there is no reuse.
+#include "api.h"
+#include "common.cuh"
+#include "host_util.h"
+#include <cuda_fp16.h>
+
+namespace dpk {
+
+// ---------------------------------------------------------------- typed 8-wide loads
+template <int KIND> struct Elem;                       // 0 fp32, 1 bf16, 2 fp16
+template <> struct Elem<0> { using T = float; };
+template <> struct Elem<1> { using T = __nv_bfloat16; };
+template <> struct Elem<2> { using T = __half; };
+
+template <int KIND>
+__device__ __forceinline__ void load8(const void* base, int64_t idx, float (&v)[8]) {
+  if constexpr (KIND == 0) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+    float4 a = p[0], b = p[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if constexpr (KIND == 1) {
+        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[q]);
+        v[2 * q] = __bfloat162float(h.x); v[2 * q + 1] = __bfloat162float(h.y);
+      } else {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[q]);
+        v[2 * q] = __half2float(h.x); v[2 * q + 1] = __half2float(h.y);
+      }
+    }
+  }
+}
+template <int KIND>
+__device__ __forceinline__ float load1(const void* base, int64_t idx) {
+  if constexpr (KIND == 0) return reinterpret_cast<const float*>(base)[idx];
+  else if constexpr (KIND == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  else return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Sum over a block of up to 1024 threads; result valid in every thread.
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) t = warp_sum(t);
+  if (threadIdx.x == 0) sh[0] = t;
+  __syncthreads();
+  return sh[0];
+}
+
+// ---------------------------------------------------------------- scale_rows
+template <int KIND>
+__global__ void scale_rows_kernel(const void* x, const float* c, __nv_bfloat16* y, int64_t rows, int64_t cols,
+                                  int64_t rps, float scale) {
+  const int64_t vec_per_row = cols >> 3;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const float f = (c ? c[r / rps] : 1.f) * scale;
+    float v[8];
+    load8<KIND>(x, i << 3, v);
+    uint4 out;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q] * f, v[2 * q + 1] * f);
+      ow[q] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(y + (i << 3)) = out;
+  }
+}
+
+// ---------------------------------------------------------------- clip factor
+__global__ void clip_factor_kernel(const float* n2, float* c, int64_t B, float C) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < B) c[i] = fminf(1.f, C / (sqrtf(fmaxf(n2[i], 0.f)) + 1e-6f));
+}
+
+// ---------------------------------------------------------------- per-row squared norm
+template <int KIND>
+__global__ void row_norm_sq_kernel(const void* x, int64_t cols, float* out) {
+  __shared__ float sh[32];
+  const int64_t row = blockIdx.y;
+  const int64_t base = row * cols;
+  float acc = 0.f;
+  const bool vec_ok = (cols & 7) == 0;
+  if (vec_ok) {
+    const int64_t nvec = cols >> 3;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+      float v[8];
+      load8<KIND>(x, base + (i << 3), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(v[j], v[j], acc);
+    }
+  } else {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < cols; i += (int64_t)gridDim.x * blockDim.x) {
+      const float v = load1<KIND>(x, base + i);
+      acc = fmaf(v, v, acc);
+    }
+  }
+  const float tot = block_sum(acc, sh);
+  if (threadIdx.x == 0) atomicAdd(out + row, tot);
+}
+
+// ---------------------------------------------------------------- weighted sum over samples
+template <int KIND>
+__global__ void weighted_sum_kernel(const void* x, const float* c, int64_t B, int64_t cols, float* out) {
+  const int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t b0 = blockIdx.y, bstep = gridDim.y;
+  if ((cols & 7) == 0) {
+    if ((j << 3) >= cols) return;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int64_t n = b0; n < B; n += bstep) {
+      float v[8];
+      load8<KIND>(x, n * cols + (j << 3), v);
+      const float w = c[n];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = fmaf(w, v[q], acc[q]);
+    }
+    if (bstep == 1) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) out[(j << 3) + q] = acc[q];
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) atomicAdd(out + (j << 3) + q, acc[q]);
+    }
+  } else {
+    if (j >= cols) return;
+    float acc = 0.f;
+    for (int64_t n = b0; n < B; n += bstep) acc = fmaf(c[n], load1<KIND>(x, n * cols + j), acc);
+    if (bstep == 1) out[j] = acc; else atomicAdd(out + j, acc);
+  }
+}
+
+// ---------------------------------------------------------------- 2-d input ghost norm
+template <int KIND>
+__global__ void outer_norm_sq_kernel(const void* a, const void* g, int64_t d_a, int64_t d_g, float scale, float* out_w,
+                                     float* out_b, int accumulate) {
+  __shared__ float sh[32];
+  const int64_t n = blockIdx.x;
+  float sa = 0.f, sg = 0.f;
+  if (a) for (int64_t i = threadIdx.x; i < d_a; i += blockDim.x) { const float v = load1<KIND>(a, n * d_a + i); sa = fmaf(v, v, sa); }
+  for (int64_t i = threadIdx.x; i < d_g; i += blockDim.x) { const float v = load1<KIND>(g, n * d_g + i); sg = fmaf(v, v, sg); }
+  sa = block_sum(sa, sh);
+  sg = block_sum(sg, sh);
+  if (threadIdx.x == 0) {
+    if (out_w) out_w[n] = (accumulate ? out_w[n] : 0.f) + sa * sg * scale;
+    if (out_b) out_b[n] = (accumulate ? out_b[n] : 0.f) + sg * scale;
+  }
+}
+
+// ---------------------------------------------------------------- LayerNorm / RMSNorm
+// stats[row] = (mean, rstd) over the last dimension (mean = 0 for RMSNorm).
+template <int KIND>
+__global__ void row_stats_kernel(int kind, const void* x, int64_t nrows, int64_t d, float eps, float2* stats) {
+  const int warps = blockDim.x >> 5;
+  const int64_t row = blockIdx.x * (int64_t)warps + (threadIdx.x >> 5);
+  if (row >= nrows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f, ss = 0.f;
+  for (int64_t i = lane; i < d; i += 32) {
+    const float v = load1<KIND>(x, row * d + i);
+    s += v; ss = fmaf(v, v, ss);
+  }
+  s = warp_sum(s); ss = warp_sum(ss);
+  if (lane == 0) {
+    if (kind == 0) {
+      const float mean = s / d;
+      const float var = fmaxf(ss / d - mean * mean, 0.f);
+      stats[row] = make_float2(mean, rsqrtf(var + eps));
+    } else {
+      stats[row] = make_float2(0.f, rsqrtf(ss / d + eps));
+    }
+  }
+}
+// gw[n, j] += sum_r (x[n,r,j]-mean)*rstd*g[n,r,j];  gb[n, j] += sum_r g[n,r,j]
+template <int KIND>
+__global__ void lastdim_grad_kernel(const void* x, const void* g, const float2* stats, int64_t rows, int64_t d,
+                                    int64_t rows_per_block, float* gw, float* gb) {
+  const int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (j >= d) return;
+  const int64_t n = blockIdx.z;
+  const int64_t r0 = blockIdx.y * rows_per_block;
+  const int64_t r1 = min(rows, r0 + rows_per_block);
+  float aw = 0.f, ab = 0.f;
+  for (int64_t r = r0; r < r1; ++r) {
+    const int64_t row = n * rows + r;
+    const float2 st = stats[row];
+    const float xv = load1<KIND>(x, row * d + j);
+    const float gv = load1<KIND>(g, row * d + j);
+    aw = fmaf((xv - st.x) * st.y, gv, aw);
+    ab += gv;
+  }
+  if (gw) atomicAdd(gw + n * d + j, aw);
+  if (gb) atomicAdd(gb + n * d + j, ab);
+}
+
+// ---------------------------------------------------------------- GroupNorm / InstanceNorm
+// One block per (sample, group).  x, g: [B, C, S].
+template <int KIND>
+__global__ void channel_grad_kernel(const void* x, const void* g, int64_t C, int64_t S, int groups, float eps,
+                                    float* gw, float* gb) {
+  __shared__ float sh[32];
+  const int64_t n = blockIdx.x / groups;
+  const int grp = blockIdx.x % groups;
+  const int64_t cpg = C / groups;
+  const int64_t base = (n * C + grp * cpg) * S;
+  const int64_t cnt = cpg * S;
+  float s = 0.f, ss = 0.f;
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+    const float v = load1<KIND>(x, base + i);
+    s += v; ss = fmaf(v, v, ss);
+  }
+  s = block_sum(s, sh);
+  ss = block_sum(ss, sh);
+  const float mean = s / cnt;
+  const float rstd = rsqrtf(fmaxf(ss / cnt - mean * mean, 0.f) + eps);
+  for (int64_t c = 0; c < cpg; ++c) {
+    float aw = 0.f, ab = 0.f;
+    for (int64_t i = threadIdx.x; i < S; i += blockDim.x) {
+      const float xv = load1<KIND>(x, base + c * S + i);
+      const float gv = load1<KIND>(g, base + c * S + i);
+      aw = fmaf((xv - mean) * rstd, gv, aw);
+      ab += gv;
+    }
+    aw = block_sum(aw, sh);
+    ab = block_sum(ab, sh);
+    if (threadIdx.x == 0) {
+      if (gw) gw[n * C + grp * cpg + c] = aw;
+      if (gb) gb[n * C + grp * cpg + c] = ab;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- embedding scatter
+template <int KIND>
+__global__ void embedding_scatter_kernel(const int64_t* ids, const void* g, const float* c, int64_t rows, int64_t T,
+                                         int64_t D, int64_t V, int64_t padding_idx, float scale, float* out) {
+  const int64_t vec_per_row = (D + 3) >> 2;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int64_t col = (i - r * vec_per_row) << 2;
+    const int64_t id = ids[r];
+    if (id < 0 || id >= V || id == padding_idx) continue;
+    const float f = c[r / T] * scale;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (col + q < D) atomicAdd(out + id * D + col + q, f * load1<KIND>(g, r * D + col + q));
+  }
+}
+
+// ---------------------------------------------------------------- fused DP step
+constexpr int kStepChunk = 4096;        // elements per block
+constexpr int kStepThreads = 256;       // 4 per thread per iteration
+
+__global__ void __launch_bounds__(kStepThreads)
+fused_dp_step_kernel(const DpkTensorEntry* table, int n_tensors, const int64_t* chunk_prefix, DpkStepHyper h) {
+  // locate the tensor owning this chunk: chunk_prefix[t] <= blockIdx.x < chunk_prefix[t+1]
+  int lo = 0, hi = n_tensors;
+  const int64_t b = blockIdx.x;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (chunk_prefix[mid] <= b) lo = mid; else hi = mid;
+  }
+  const DpkTensorEntry e = table[lo];
+  const int64_t start = (b - chunk_prefix[lo]) * kStepChunk;
+  const int64_t end = min(e.numel, start + kStepChunk);
+  const Philox rng(h.seed);
+  float* pf = reinterpret_cast<float*>(e.param);
+  __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(e.param);
+
+  for (int64_t i0 = start + 4 * (int64_t)threadIdx.x; i0 < end; i0 += 4 * kStepThreads) {
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    if (h.noise_std != 0.f) {
+      const uint4 u = rng(static_cast<uint64_t>(e.rng_offset + i0) >> 2, h.offset);
+      const float2 n01 = box_muller(u.x, u.y), n23 = box_muller(u.z, u.w);
+      z[0] = n01.x * h.noise_std; z[1] = n01.y * h.noise_std; z[2] = n23.x * h.noise_std; z[3] = n23.y * h.noise_std;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int64_t i = i0 + q;
+      if (i >= end) break;
+      float grad = (e.grad[i] + z[q]) * h.inv_scale;
+      e.grad[i] = grad;
+      float pv = e.master ? e.master[i] : (e.param_bf16 ? __bfloat162float(pb[i]) : pf[i]);
+      if (h.kind == 0) {
+        if (h.weight_decay != 0.f) grad = fmaf(h.weight_decay, pv, grad);
+        if (h.momentum != 0.f) {
+          float buf = h.first_step ? grad : fmaf(h.momentum, e.state0[i], (1.f - h.dampening) * grad);
+          e.state0[i] = buf;
+          grad = h.nesterov ? fmaf(h.momentum, buf, grad) : buf;
+        }
+        pv = fmaf(-h.lr, grad, pv);
+      } else {
+        if (h.weight_decay != 0.f) {
+          if (h.kind == 2) pv *= (1.f - h.lr * h.weight_decay);
+          else grad = fmaf(h.weight_decay, pv, grad);
+        }
+        const float m = fmaf(h.beta1, e.state0[i], (1.f - h.beta1) * grad);
+        const float v = fmaf(h.beta2, e.state1[i], (1.f - h.beta2) * grad * grad);
+        e.state0[i] = m;
+        e.state1[i] = v;
+        const float denom = sqrtf(v) / h.bias_c2_sqrt + h.eps;
+        pv -= (h.lr / h.bias_c1) * (m / denom);
+      }
+      if (e.master) e.master[i] = pv;
+      if (e.param_bf16) pb[i] = __float2bfloat16_rn(pv); else pf[i] = pv;
+    }
+  }
+}
+
+__global__ void philox_normal_kernel(float* out, int64_t n, uint64_t seed, uint64_t offset, float std) {
+  const Philox rng(seed);
+  for (int64_t i0 = 4 * (blockIdx.x * (int64_t)blockDim.x + threadIdx.x); i0 < n; i0 += 4 * (int64_t)gridDim.x * blockDim.x) {
+    const uint4 u = rng(static_cast<uint64_t>(i0) >> 2, offset);
+    const float2 a = box_muller(u.x, u.y), b = box_muller(u.z, u.w);
+    const float z[4] = {a.x, a.y, b.x, b.y};
+    for (int q = 0; q < 4 && i0 + q < n; ++q) out[i0 + q] = z[q] * std;
+  }
+}
+
+inline int grid_for(int64_t work, int threads, int max_blocks) {
+  int64_t b = (work + threads - 1) / threads;
+  if (b < 1) b = 1;
+  return (int)(b > max_blocks ? max_blocks : b);
+}
+
+}  // namespace dpk
+
+using namespace dpk;
+
+#define DISPATCH_KIND(kind, ...)                         \
+  switch (kind) {                                        \
+    case 0: { constexpr int KIND = 0; __VA_ARGS__; break; } \
+    case 1: { constexpr int KIND = 1; __VA_ARGS__; break; } \
+    case 2: { constexpr int KIND = 2; __VA_ARGS__; break; } \
+    default: return cudaErrorInvalidValue;               \
+  }
+
+extern "C" int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y, int64_t rows, int64_t cols,
+                              int64_t rps, float scale, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) || rps <= 0) return cudaErrorInvalidValue;
+  const int grid = grid_for(rows * (cols >> 3), 256, num_sms() * 16);
+  if (x_is_fp32) scale_rows_kernel<0><<<grid, 256, 0, stream>>>(x, c, (__nv_bfloat16*)y, rows, cols, rps, scale);
+  else scale_rows_kernel<1><<<grid, 256, 0, stream>>>(x, c, (__nv_bfloat16*)y, rows, cols, rps, scale);
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_clip_factor(const float* n2, float* c, int64_t B, float C, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  clip_factor_kernel<<<(int)((B + 255) / 256), 256, 0, stream>>>(n2, c, B, C);
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_row_norm_sq(const void* x, int kind, int64_t B, int64_t cols, float* out, int accumulate,
+                               cudaStream_t stream) {
+  if (B <= 0 || cols <= 0) return 0;
+  if (!accumulate) cudaMemsetAsync(out, 0, sizeof(float) * B, stream);
+  int64_t per_row = (cols + 8 * 256 - 1) / (8 * 256);
+  int64_t want = (int64_t)num_sms() * 8 / (B > 0 ? B : 1) + 1;
+  int gx = (int)(per_row < want ? per_row : want);
+  if (gx < 1) gx = 1;
+  dim3 grid(gx, (unsigned)B);
+  if (B > 65535) return cudaErrorInvalidValue;
+  DISPATCH_KIND(kind, (row_norm_sq_kernel<KIND><<<grid, 256, 0, stream>>>(x, cols, out)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_weighted_sum(const void* x, int kind, const float* c, int64_t B, int64_t cols, float* out,
+                                cudaStream_t stream) {
+  if (cols <= 0) return 0;
+  const int64_t lanes = (cols & 7) == 0 ? (cols >> 3) : cols;
+  const int gx = (int)((lanes + 127) / 128);
+  int gy = 1;
+  if (gx < num_sms() * 2 && B >= 16) {
+    gy = (int)((num_sms() * 4 + gx - 1) / gx);
+    if (gy > B / 4) gy = (int)(B / 4);
+    if (gy < 1) gy = 1;
+    if (gy > 1024) gy = 1024;
+  }
+  if (gy > 1) cudaMemsetAsync(out, 0, sizeof(float) * cols, stream);
+  dim3 grid(gx, gy);
+  DISPATCH_KIND(kind, (weighted_sum_kernel<KIND><<<grid, 128, 0, stream>>>(x, c, B, cols, out)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_outer_norm_sq(const void* a, const void* g, int kind, int64_t B, int64_t d_a, int64_t d_g,
+                                 float scale, float* out_w, float* out_b, int accumulate, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  DISPATCH_KIND(kind, (outer_norm_sq_kernel<KIND><<<(unsigned)B, 256, 0, stream>>>(a, g, d_a, d_g, scale, out_w, out_b,
+                                                                                 accumulate)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_norm_lastdim_grad(int norm_kind, const void* x, const void* g, int kind, int64_t B, int64_t rows,
+                                     int64_t d, float eps, float* stats_scratch, float* gw, float* gb,
+                                     cudaStream_t stream) {
+  if (B <= 0 || rows <= 0 || d <= 0) return 0;
+  float2* stats = reinterpret_cast<float2*>(stats_scratch);  // [B*rows] (mean, rstd)
+  if (gw) cudaMemsetAsync(gw, 0, sizeof(float) * B * d, stream);
+  if (gb) cudaMemsetAsync(gb, 0, sizeof(float) * B * d, stream);
+  const int64_t nrows = B * rows;
+  DISPATCH_KIND(kind, (row_stats_kernel<KIND><<<(unsigned)((nrows + 7) / 8), 256, 0, stream>>>(norm_kind, x, nrows, d, eps, stats)));
+  int64_t rpb = rows;
+  const int gx = (int)((d + 127) / 128);
+  int64_t want_y = ((int64_t)num_sms() * 8) / ((int64_t)gx * B) + 1;
+  if (want_y > rows) want_y = rows;
+  rpb = (rows + want_y - 1) / want_y;
+  const int gy = (int)((rows + rpb - 1) / rpb);
+  if (B > 65535 || gy > 65535) return cudaErrorInvalidValue;
+  dim3 grid(gx, gy, (unsigned)B);
+  DISPATCH_KIND(kind, (lastdim_grad_kernel<KIND><<<grid, 128, 0, stream>>>(x, g, stats, rows, d, rpb, gw, gb)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_norm_channel_grad(const void* x, const void* g, int kind, int64_t B, int64_t C, int64_t S,
+                                     int groups, float eps, float* gw, float* gb, cudaStream_t stream) {
+  if (B <= 0 || C <= 0 || S <= 0 || groups <= 0 || C % groups) return cudaErrorInvalidValue;
+  DISPATCH_KIND(kind, (channel_grad_kernel<KIND><<<(unsigned)(B * groups), 256, 0, stream>>>(x, g, C, S, groups, eps, gw, gb)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_embedding_scatter(const int64_t* ids, const void* g, int kind, const float* c, int64_t rows,
+                                     int64_t T, int64_t D, int64_t V, int64_t padding_idx, float scale, float* out,
+                                     cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int grid = grid_for(rows * ((D + 3) >> 2), 256, num_sms() * 16);
+  DISPATCH_KIND(kind, (embedding_scatter_kernel<KIND><<<grid, 256, 0, stream>>>(ids, g, c, rows, T, D, V, padding_idx,
+                                                                               scale, out)));
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_fused_dp_step(const DpkTensorEntry* table, int n_tensors, int64_t total_chunks,
+                                 const int64_t* chunk_prefix, DpkStepHyper h, cudaStream_t stream) {
+  if (n_tensors <= 0 || total_chunks <= 0) return 0;
+  if (total_chunks > 0x7fffffffLL) return cudaErrorInvalidValue;
+  fused_dp_step_kernel<<<(unsigned)total_chunks, kStepThreads, 0, stream>>>(table, n_tensors, chunk_prefix, h);
+  return cudaGetLastError();
+}
+
+extern "C" int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  philox_normal_kernel<<<grid_for((n + 3) / 4, 256, num_sms() * 8), 256, 0, stream>>>(out, n, seed, offset, std);
+  return cudaGetLastError();
+}

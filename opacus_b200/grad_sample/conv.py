@@ -80,3 +80,27 @@ def compute_conv_weighted_grad(layer, activations, backprops, coef, g_scale: flo
     if layer.bias is not None and layer.bias.requires_grad:
         out[layer.bias] = gw.reshape(gw.shape[0], gw.shape[1], -1).sum(dim=(0, 2))
     return out
+
+
+def convolution2d_backward_as_a_convolution(layer: nn.Conv2d, activations: List[torch.Tensor],
+                                            backprops: torch.Tensor) -> Dict[nn.Parameter, torch.Tensor]:
+    """Alternative Conv2d rule without im2col: the per-sample weight gradient is
+    itself a correlation of the input with the output gradient in which the
+    roles of stride and dilation are exchanged.  Input channels become the
+    batch axis and ``(sample, group)`` pairs become convolution groups, so one
+    grouped ``conv2d`` yields every sample's gradient
+    (``opacus/grad_sample/conv.py:122-191``)."""
+    x = activations[0]
+    B, C, H, W = x.shape
+    O = backprops.shape[1]
+    G_ = layer.groups
+    xin = x.reshape(B * G_, C // G_, H, W).transpose(0, 1)             # [C/G, B*G, H, W]
+    ker = backprops.reshape(B * O, 1, backprops.shape[2], backprops.shape[3])
+    res = F.conv2d(xin, ker, None, stride=layer.dilation, padding=layer.padding, dilation=layer.stride,
+                   groups=B * G_)                                       # [C/G, B*O, kh+, kw+]
+    kh, kw = layer.weight.shape[2], layer.weight.shape[3]
+    res = res[:, :, :kh, :kw].reshape(C // G_, B, O, kh, kw).permute(1, 2, 0, 3, 4)
+    out = {layer.weight: res}
+    if layer.bias is not None:
+        out[layer.bias] = backprops.sum(dim=(-1, -2))
+    return out

@@ -1,0 +1,281 @@
+"""CUDA side of :mod:`opacus_b200.ops`: shape/dtype preparation around the
+kernels bound in ``opacus_b200._C`` (sources in ``opacus_b200/csrc``).
+
+The tensor-core kernels take bf16 operands and accumulate in fp32.  fp32 inputs
+are routed to them only where a bf16 rounding of the operands is acceptable by
+construction (never for fp32 models: those use the fp32 statements in
+:mod:`._ref` for the GEMM-shaped ops, while the bandwidth-bound kernels are
+dtype generic).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import _ref
+
+_C = None
+_scratch: Dict[torch.device, torch.Tensor] = {}
+
+
+def load():
+    """Import the native module; a GPU machine without it is an error."""
+    global _C
+    if _C is not None:
+        return _C
+    try:
+        from .. import _C as mod
+    except ImportError as e:
+        raise RuntimeError(
+            "opacus_b200: the native extension is not built. Run `python -m opacus_b200.build` "
+            "(needs nvcc; compiles for sm_100a) before using CUDA tensors."
+        ) from e
+    _C = mod
+    return mod
+
+
+def check_status(device=None):
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    load().check_status(dev or 0)
+
+
+def _bt(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() == 2:
+        return x.unsqueeze(1)
+    return x.reshape(x.shape[0], -1, x.shape[-1])
+
+
+def _scratch_for(device, floats: int) -> torch.Tensor:
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < floats:
+        buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def _bf16(x: torch.Tensor) -> torch.Tensor:
+    """bf16, contiguous (conversion through the row-scaling kernel when needed)."""
+    if x.dtype == torch.bfloat16:
+        return x.contiguous()
+    if x.dtype == torch.float32 and x.shape[-1] % 8 == 0:
+        x2 = x.contiguous().reshape(-1, x.shape[-1])
+        return load().scale_rows(x2, None, 1, 1.0).view(x.shape)
+    return x.to(torch.bfloat16).contiguous()
+
+
+def _tensor_core_ok(*ts) -> bool:
+    """bf16 (or fp16-free) operands whose rows are 16-byte multiples."""
+    return all(t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0 for t in ts)
+
+
+# ----------------------------------------------------------------------- Linear
+def linear_grad_sample(a, g):
+    return _ref.linear_grad_sample(a, g)
+
+
+def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0):
+    a3, g3 = _bt(a), _bt(g)
+    B, T, d_in = a3.shape
+    d_out = g3.shape[-1]
+    s2 = float(g_scale) ** 2
+    C = load()
+    if T == 1:
+        dt = g3.dtype
+        a2 = a3.reshape(B, d_in).to(dt).contiguous()
+        g2 = g3.reshape(B, d_out).contiguous()
+        w = torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None
+        b = torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None
+        C.outer_norm_sq(a2 if want_weight else None, g2, s2, w, b, False)
+        return w, b
+    gram_cheaper = T * (d_in + d_out) <= 2 * d_in * d_out  # symmetric tiles halve the Gram cost
+    if g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0 and (gram_cheaper or not want_weight):
+        gb = g3.contiguous()
+        ab = _bf16(a3) if want_weight else None
+        w = torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None
+        b = torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None
+        scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
+        C.gram_pair_norm(ab, None, gb, s2, scratch, w, b, False)
+        return w, b
+    return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+
+
+def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False):
+    a3, g3 = _bt(a), _bt(g)
+    B, T, d_in = a3.shape
+    d_out = g3.shape[-1]
+    if not (g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0):
+        return _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+    C = load()
+    c = c.float().contiguous()
+    a2 = a3.reshape(B * T, d_in)
+    g2 = g3.reshape(B * T, d_out)
+    # the clip factors go onto the narrower operand (fewer bytes to rewrite)
+    if d_in <= d_out and a2.dtype in (torch.float32, torch.bfloat16):
+        a_op = C.scale_rows(a2.contiguous(), c, T, float(g_scale))
+        g_op = g2.contiguous()
+    else:
+        g_op = C.scale_rows(g2.contiguous(), c, T, float(g_scale))
+        a_op = _bf16(a2)
+    out = torch.empty(d_out, d_in, dtype=torch.float32, device=g.device)
+    C.wgrad_tn(g_op, a_op, out, 0.0)
+    bias = None
+    if want_bias:
+        per_sample = g3.float().sum(dim=1)                       # [B, d_out]
+        bias = C.weighted_sum(per_sample.contiguous(), c * float(g_scale))
+    return out, bias
+
+
+# -------------------------------------------------------------------- Embedding
+def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None):
+    B = ids.shape[0]
+    ids2 = ids.reshape(B, -1)
+    T = ids2.shape[1]
+    g3 = g.reshape(B, T, -1)
+    if padding_idx is not None or g3.dtype != torch.bfloat16 or g3.shape[-1] % 8:
+        return _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+    C = load()
+    w = torch.empty(B, dtype=torch.float32, device=g.device)
+    scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
+    C.gram_pair_norm(None, ids2.contiguous().long(), g3.contiguous(), float(g_scale) ** 2, scratch, w, None, False)
+    return w
+
+
+def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None):
+    B = ids.shape[0]
+    D = g.shape[-1]
+    T = ids.numel() // B
+    out = torch.zeros(num_embeddings, D, dtype=torch.float32, device=g.device)
+    load().embedding_scatter(ids.reshape(-1).contiguous().long(), g.reshape(-1, D).contiguous(),
+                             c.float().contiguous(), T, -1 if padding_idx is None else int(padding_idx),
+                             float(g_scale), out)
+    return out if out_dtype in (None, torch.float32) else out.to(out_dtype)
+
+
+# ----------------------------------------------------------- normalisation layers
+def supports_norm(kind, x, normalized_ndim) -> bool:
+    if kind in ("layer", "rms"):
+        return normalized_ndim == 1 and x.dim() >= 2
+    return x.dim() >= 2
+
+
+def norm_affine_grad_sample(kind, x, g, eps, normalized_ndim, num_groups, want_weight, want_bias):
+    C = load()
+    if x.dtype != g.dtype:
+        wide = torch.promote_types(x.dtype, g.dtype)
+        x, g = x.to(wide), g.to(wide)
+    x, g = x.contiguous(), g.contiguous()
+    if kind in ("layer", "rms"):
+        d = x.shape[-1]
+        gw, gb = C.norm_lastdim_grad(0 if kind == "layer" else 1, x, g, d, float(eps), bool(want_weight),
+                                     bool(want_bias) and kind == "layer")
+    else:
+        groups = x.shape[1] if kind == "instance" else int(num_groups)
+        gw, gb = C.norm_channel_grad(x, g, groups, float(eps), bool(want_weight), bool(want_bias))
+    # fp32 results are kept: these per-sample gradients are tiny and feed the norm
+    return (gw if want_weight else None), (gb if (want_bias and gb is not None and gb.numel()) else None)
+
+
+# --------------------------------------------------------------- clipping pieces
+def clip_factor(norm_sq, max_grad_norm: float):
+    return load().clip_factor(norm_sq.contiguous(), float(max_grad_norm))
+
+
+def grad_sample_norm_sq(gs):
+    return load().row_norm_sq(gs.contiguous())
+
+
+def weighted_sum(gs, c):
+    out = load().weighted_sum(gs.contiguous(), c.float().contiguous())
+    return out.view(gs.shape[1:]).to(gs.dtype)
+
+
+# ------------------------------------------------------------------- fused step
+_ENTRY = np.dtype([("param", "<u8"), ("grad", "<u8"), ("state0", "<u8"), ("state1", "<u8"), ("master", "<u8"),
+                   ("numel", "<i8"), ("rng_offset", "<i8"), ("param_bf16", "<i4"), ("pad", "<i4")])
+_CHUNK = 4096
+_DOMAIN = 0x6F70616375736232  # separates this generator's streams from torch's own use of (seed, offset)
+
+
+def _rng_state(generator, device, n_elems: int):
+    gen = generator if generator is not None else torch.cuda.default_generators[device.index]
+    seed = int(gen.initial_seed())
+    offset = int(gen.get_offset())
+    gen.set_offset(offset + 4 * ((n_elems + 3) // 4 + 1))
+    seed = (seed ^ _DOMAIN) & 0x7FFFFFFFFFFFFFFF
+    return seed, offset
+
+
+def fused_dp_step(kind, inner, group, ps, *, noise_std: float, inv_scale: float, generator=None):
+    """One launch: p.summed_grad <- (summed_grad + N(0, std^2)) * inv_scale, then the
+    SGD / Adam / AdamW update of ``p`` and its state, for every tensor in ``ps``."""
+    C = load()
+    assert C.tensor_entry_size() == _ENTRY.itemsize
+    dev = ps[0].device
+    state = inner.state
+    hyper = dict(lr=float(group["lr"]), momentum=0.0, dampening=0.0, weight_decay=float(group.get("weight_decay", 0.0)),
+                 beta1=0.0, beta2=0.0, eps=0.0, bias_c1=1.0, bias_c2_sqrt=1.0)
+    first_step = False
+    nesterov = False
+    if kind == "sgd":
+        hyper["momentum"] = float(group.get("momentum", 0.0))
+        hyper["dampening"] = float(group.get("dampening", 0.0))
+        nesterov = bool(group.get("nesterov", False))
+        if hyper["momentum"] != 0.0:
+            first_step = state[ps[0]].get("momentum_buffer") is None if ps[0] in state else True
+            for p in ps:
+                st = state[p]
+                if st.get("momentum_buffer") is None:
+                    st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
+        kcode = 0
+    else:
+        beta1, beta2 = group["betas"]
+        for p in ps:
+            st = state[p]
+            if len(st) == 0:
+                st["step"] = torch.tensor(0.0, dtype=torch.float32)
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
+        t = float(state[ps[0]]["step"]) + 1.0
+        for p in ps:
+            state[p]["step"] += 1
+        hyper.update(beta1=float(beta1), beta2=float(beta2), eps=float(group["eps"]),
+                     bias_c1=1.0 - float(beta1) ** t, bias_c2_sqrt=math.sqrt(1.0 - float(beta2) ** t))
+        kcode = 2 if kind == "adamw" else 1
+
+    table = np.zeros(len(ps), dtype=_ENTRY)
+    prefix = np.zeros(len(ps) + 1, dtype=np.int64)
+    rng_ofs = 0
+    for i, p in enumerate(ps):
+        g = p.summed_grad
+        if g.dtype != torch.float32 or not g.is_contiguous():
+            g = g.float().contiguous()
+            p.summed_grad = g
+        st = state[p] if p in state else {}
+        e = table[i]
+        e["param"] = p.data_ptr()
+        e["grad"] = g.data_ptr()
+        if kind == "sgd":
+            buf = st.get("momentum_buffer")
+            e["state0"] = buf.data_ptr() if buf is not None else 0
+        else:
+            e["state0"] = st["exp_avg"].data_ptr()
+            e["state1"] = st["exp_avg_sq"].data_ptr()
+        e["numel"] = p.numel()
+        e["rng_offset"] = rng_ofs
+        e["param_bf16"] = 1 if p.dtype == torch.bfloat16 else 0
+        rng_ofs += 4 * ((p.numel() + 3) // 4)
+        prefix[i + 1] = prefix[i] + (p.numel() + _CHUNK - 1) // _CHUNK
+    seed, offset = _rng_state(generator, dev, rng_ofs)
+    table_t = torch.from_numpy(table.view(np.uint8)).to(dev, non_blocking=True)
+    prefix_t = torch.from_numpy(prefix).to(dev, non_blocking=True)
+    C.fused_dp_step(table_t, prefix_t, len(ps), int(prefix[-1]), kcode, nesterov, first_step,
+                    hyper["lr"], hyper["momentum"], hyper["dampening"], hyper["weight_decay"], hyper["beta1"],
+                    hyper["beta2"], hyper["eps"], hyper["bias_c1"], hyper["bias_c2_sqrt"], float(noise_std),
+                    float(inv_scale), seed, offset)
+
+
+def philox_normal(n: int, seed: int, offset: int, std: float, device) -> torch.Tensor:
+    return load().philox_normal(int(n), int(seed), int(offset), float(std), torch.device(device))

@@ -15,6 +15,8 @@ def _bt(x: torch.Tensor) -> torch.Tensor:
     """View as ``[B, T, d]`` (``T = 1`` for 2-d input)."""
     if x.dim() == 2:
         return x.unsqueeze(1)
+    if x.shape[0] == 0:
+        return x.new_zeros(0, 1, x.shape[-1])
     return x.reshape(x.shape[0], -1, x.shape[-1])
 
 
@@ -128,7 +130,7 @@ def affine_grad_sample(xhat: torch.Tensor, g: torch.Tensor, keep_last: int = 0, 
     """
     def red(t):
         if channel_dim:
-            return t.reshape(t.shape[0], t.shape[1], -1).sum(dim=-1)
+            return t.sum(dim=list(range(2, t.dim()))) if t.dim() > 2 else t
         mid = t.dim() - keep_last - 1
         return t if mid == 0 else t.sum(dim=list(range(1, 1 + mid)))
 

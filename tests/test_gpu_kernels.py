@@ -1,0 +1,190 @@
+"""Numerics of every CUDA kernel against the plain-PyTorch fp32 statement of
+the same operation (``opacus_b200.ops._ref``)."""
+import pytest
+import torch
+
+from opacus_b200 import ops
+from opacus_b200.ops import _ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("B,T,din,dout", [(3, 128, 64, 64), (2, 256, 128, 192), (5, 100, 72, 40), (2, 300, 200, 136),
+                                           (4, 1024, 256, 512)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_ghost_norm(B, T, din, dout, bias):
+    torch.manual_seed(0)
+    a = torch.randn(B, T, din, device=_dev()).bfloat16()
+    g = (torch.randn(B, T, dout, device=_dev()) * 0.1).bfloat16()
+    w, b = ops.linear_norm_sq(a, g, True, bias, g_scale=3.0)
+    gs = torch.bmm(g.float().transpose(1, 2), a.float()) * 3.0
+    want_w = gs.pow(2).sum(dim=(1, 2))
+    assert _rel(w, want_w) < 2e-3, (w, want_w)
+    if bias:
+        want_b = (g.float().sum(1) * 3.0).pow(2).sum(1)
+        assert _rel(b, want_b) < 2e-3, (b, want_b)
+    ops._cuda.check_status()
+
+
+def test_linear_ghost_norm_2d():
+    torch.manual_seed(0)
+    a = torch.randn(7, 33, device=_dev())
+    g = torch.randn(7, 10, device=_dev())
+    w, b = ops.linear_norm_sq(a, g, True, True, g_scale=2.0)
+    rw, rb = _ref.linear_norm_sq(a, g, True, True, g_scale=2.0)
+    assert torch.allclose(w, rw, rtol=1e-5) and torch.allclose(b, rb, rtol=1e-5)
+
+
+@pytest.mark.parametrize("B,T,D,V", [(3, 128, 64, 50), (2, 200, 128, 1000), (4, 512, 256, 32)])
+def test_embedding_ghost_norm(B, T, D, V):
+    torch.manual_seed(0)
+    ids = torch.randint(0, V, (B, T), device=_dev())
+    g = (torch.randn(B, T, D, device=_dev()) * 0.1).bfloat16()
+    got = ops.embedding_norm_sq(ids, g, g_scale=2.0)
+    dense = _ref.embedding_grad_sample(ids, g.float() * 2.0, V)
+    want = dense.pow(2).sum(dim=(1, 2))
+    assert _rel(got, want) < 2e-3, (got, want)
+    ops._cuda.check_status()
+
+
+@pytest.mark.parametrize("B,T,din,dout", [(2, 128, 64, 128), (3, 100, 72, 40), (4, 256, 256, 512), (2, 64, 512, 1000),
+                                           (8, 1024, 2048, 512)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_weighted_grad(B, T, din, dout, bias):
+    torch.manual_seed(0)
+    a = torch.randn(B, T, din, device=_dev()).bfloat16()
+    g = (torch.randn(B, T, dout, device=_dev()) * 0.1).bfloat16()
+    c = torch.rand(B, device=_dev())
+    w, b = ops.linear_weighted_grad(a, g, c, g_scale=1.5, want_bias=bias)
+    rw, rb = _ref.linear_weighted_grad(a.float(), g.float(), c, g_scale=1.5, want_bias=bias)
+    assert w.shape == rw.shape
+    assert _rel(w, rw) < 6e-3, _rel(w, rw)
+    if bias:
+        assert _rel(b, rb) < 1e-3
+    ops._cuda.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_sq_weighted_sum_clip(dtype):
+    torch.manual_seed(0)
+    gs = torch.randn(9, 37, 50, device=_dev()).to(dtype)
+    n2 = ops.grad_sample_norm_sq(gs)
+    assert torch.allclose(n2, _ref.grad_sample_norm_sq(gs), rtol=1e-4)
+    c = ops.clip_factor(n2, 3.0)
+    assert torch.allclose(c, _ref.clip_factor(n2, 3.0), rtol=1e-6)
+    s = ops.weighted_sum(gs, c)
+    assert torch.allclose(s.float(), _ref.weighted_sum(gs.float(), c), rtol=2e-2 if dtype != torch.float32 else 1e-4,
+                          atol=1e-2 if dtype != torch.float32 else 1e-5)
+    big = torch.randn(4, 1 << 16, device=_dev()).to(dtype)
+    assert torch.allclose(ops.grad_sample_norm_sq(big), _ref.grad_sample_norm_sq(big), rtol=1e-3)
+    assert torch.allclose(ops.weighted_sum(big, c[:4]).float(), _ref.weighted_sum(big.float(), c[:4]), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("kind", ["layer", "rms", "group", "instance"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_layer_grads(kind, dtype):
+    import torch.nn.functional as F
+
+    torch.manual_seed(0)
+    if kind in ("layer", "rms"):
+        x = torch.randn(5, 17, 96, device=_dev()).to(dtype)
+        g = torch.randn_like(x)
+        gw, gb = ops.norm_affine_grad_sample(kind, x, g, eps=1e-5, normalized_ndim=1)
+        xf, gf = x.float(), g.float()
+        xhat = F.layer_norm(xf, (96,), eps=1e-5) if kind == "layer" else F.rms_norm(xf, (96,), eps=1e-5)
+        assert torch.allclose(gw.float(), (xhat * gf).sum(1), rtol=1e-3, atol=1e-3)
+        if kind == "layer":
+            assert torch.allclose(gb.float(), gf.sum(1), rtol=1e-3, atol=1e-3)
+    else:
+        x = torch.randn(4, 16, 6, 5, device=_dev()).to(dtype)
+        g = torch.randn_like(x)
+        gw, gb = ops.norm_affine_grad_sample(kind, x, g, eps=1e-5, num_groups=4)
+        xf, gf = x.float(), g.float()
+        xhat = F.group_norm(xf, 4, eps=1e-5) if kind == "group" else F.instance_norm(xf, eps=1e-5)
+        assert torch.allclose(gw.float(), (xhat * gf).sum((2, 3)), rtol=1e-3, atol=1e-3)
+        assert torch.allclose(gb.float(), gf.sum((2, 3)), rtol=1e-3, atol=1e-3)
+
+
+def test_embedding_weighted_grad():
+    torch.manual_seed(0)
+    ids = torch.randint(0, 40, (6, 33), device=_dev())
+    g = torch.randn(6, 33, 24, device=_dev()).bfloat16()
+    c = torch.rand(6, device=_dev())
+    got = ops.embedding_weighted_grad(ids, g, c, 40, g_scale=2.0)
+    want = _ref.embedding_weighted_grad(ids, g.float(), c, 40, g_scale=2.0)
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_philox_normal_statistics():
+    z = ops._cuda.philox_normal(1 << 22, 1234, 0, 2.0, "cuda")
+    assert abs(z.mean().item()) < 5e-3
+    assert abs(z.std().item() - 2.0) < 5e-3
+    zz = (z / 2.0)
+    assert abs((zz ** 4).mean().item() - 3.0) < 3e-2          # kurtosis of a Gaussian
+    assert abs((zz[:-1] * zz[1:]).mean().item()) < 3e-3        # no lag-1 correlation
+    z2 = ops._cuda.philox_normal(1 << 22, 1234, 4, 2.0, "cuda")
+    assert abs((z * z2).mean().item()) / 4.0 < 3e-3            # different offsets are independent
+    assert torch.equal(z, ops._cuda.philox_normal(1 << 22, 1234, 0, 2.0, "cuda"))
+
+
+@pytest.mark.parametrize("opt_name", ["sgd", "sgd_momentum", "adam", "adamw"])
+def test_fused_step_matches_torch_without_noise(opt_name):
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+
+    torch.manual_seed(0)
+
+    def make():
+        torch.manual_seed(1)
+        ps = [torch.nn.Parameter(torch.randn(33, 17, device=_dev())), torch.nn.Parameter(torch.randn(5000, device=_dev()))]
+        if opt_name == "sgd":
+            o = torch.optim.SGD(ps, lr=0.1, weight_decay=0.01)
+        elif opt_name == "sgd_momentum":
+            o = torch.optim.SGD(ps, lr=0.1, momentum=0.9, nesterov=True)
+        elif opt_name == "adam":
+            o = torch.optim.Adam(ps, lr=0.01, weight_decay=0.1)
+        else:
+            o = torch.optim.AdamW(ps, lr=0.01, weight_decay=0.1)
+        return ps, o
+
+    ps_a, oa = make()
+    ps_b, ob = make()
+    dp = DPOptimizerFastGradientClipping(oa, noise_multiplier=0.0, max_grad_norm=1.0, expected_batch_size=4)
+    for it in range(3):
+        grads = [torch.randn_like(p) for p in ps_a]
+        dp.zero_grad()
+        for p, g in zip(ps_a, grads):
+            p.grad = g.clone()
+        dp.step()
+        for p, g in zip(ps_b, grads):
+            p.grad = g / 4
+        ob.step()
+        ob.zero_grad()
+        for pa, pb in zip(ps_a, ps_b):
+            assert torch.allclose(pa, pb, rtol=1e-5, atol=1e-6), (opt_name, it, (pa - pb).abs().max())
+    assert dp._fused_plan() is not None
+
+
+def test_fused_step_noise_level():
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+
+    p = torch.nn.Parameter(torch.zeros(1 << 20, device=_dev()))
+    o = torch.optim.SGD([p], lr=1.0)
+    dp = DPOptimizerFastGradientClipping(o, noise_multiplier=2.0, max_grad_norm=0.5, expected_batch_size=1)
+    p.grad = torch.zeros_like(p)
+    dp.step()
+    assert abs(p.detach().std().item() - 1.0) < 1e-2
+    assert abs(p.detach().mean().item()) < 5e-3
+    first = p.detach().clone()
+    dp.zero_grad()
+    p.grad = torch.zeros_like(p)
+    dp.step()
+    second = p.detach() - first
+    assert abs((first * second).mean().item()) < 5e-3        # fresh noise every step
