@@ -12,18 +12,19 @@ import torch
 
 from . import _ref
 
-_cuda = None
+_kernels = None
 
 
 def _k():
     """The CUDA binding module, loaded on first use."""
-    global _cuda
-    if _cuda is None:
-        from . import _cuda as mod
+    global _kernels
+    if _kernels is None:
+        import importlib
 
+        mod = importlib.import_module(__name__ + "._cuda")
         mod.load()
-        _cuda = mod
-    return _cuda
+        _kernels = mod
+    return _kernels
 
 
 def _on_gpu(*ts) -> bool:
