@@ -1,0 +1,126 @@
+"""Micro-benchmark of the hot kernels at given shapes, timed with CUDA events.
+
+    python -m opacus_b200.benchmarks.kernels --op ghost_norm --B 8 --T 1024 --din 2048 --dout 8192
+    python -m opacus_b200.benchmarks.kernels --op wgrad --B 8 --T 1024 --din 2048 --dout 8192
+    python -m opacus_b200.benchmarks.kernels --op all
+
+Reports time per call, achieved TFLOP/s (or GB/s) and the fraction of the
+measured peak: ``MEASURED_PEAKS.json`` next to the repository root if present,
+otherwise 1590 TFLOP/s bf16 and 6650 GB/s.  Between timed calls a buffer larger
+than the L2 cache is rewritten so every call starts cold.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+from .. import ops
+from ..ops import _cuda
+
+
+def _peaks():
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.add_(1.0)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run(op, B, T, din, dout, iters=20):
+    dev = torch.device("cuda")
+    C = _cuda.load()
+    flush = torch.zeros(64 << 20, device=dev)          # 256 MB > L2
+    a = torch.randn(B, T, din, device=dev).bfloat16()
+    g = (torch.randn(B, T, dout, device=dev) * 0.1).bfloat16()
+    c = torch.rand(B, device=dev)
+    tf_peak, bw_peak, src = _peaks()
+    rows = []
+    if op in ("ghost_norm", "all"):
+        nT = (T + 127) // 128
+        tiles = B * nT * (nT + 1) // 2
+        flops = 2.0 * 128 * 128 * (din + dout) * tiles
+        ms = _time(lambda: ops.linear_norm_sq(a, g, True, False), iters, flush)
+        rows.append(("ghost_norm", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+    if op in ("wgrad", "all"):
+        gs = g.reshape(B * T, dout).contiguous()
+        a2 = a.reshape(B * T, din).contiguous()
+        out = torch.empty(dout, din, device=dev)
+        flops = 2.0 * B * T * din * dout
+        ms = _time(lambda: C.wgrad_tn(gs, a2, out, 0.0), iters, flush)
+        rows.append(("wgrad_tn", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+        ms = _time(lambda: torch.matmul(gs.t(), a2), iters, flush)
+        rows.append(("cublas_tn (library, for scale)", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+    if op in ("weighted_grad", "all"):
+        flops = 2.0 * B * T * din * dout
+        ms = _time(lambda: ops.linear_weighted_grad(a, g, c), iters, flush)
+        rows.append(("linear_weighted_grad (scale_rows + wgrad_tn)", ms, flops / ms / 1e9, "TFLOP/s",
+                     flops / ms / 1e9 / tf_peak))
+    if op in ("scale_rows", "all"):
+        x = a.reshape(B * T, din)
+        byts = x.numel() * 4.0
+        ms = _time(lambda: C.scale_rows(x, c, T, 1.0), iters, flush)
+        rows.append(("scale_rows", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    if op in ("embedding_norm", "all"):
+        ids = torch.randint(0, 32000, (B, T), device=dev)
+        nT = (T + 127) // 128
+        flops = 2.0 * 128 * 128 * dout * B * nT * (nT + 1) // 2
+        ms = _time(lambda: ops.embedding_norm_sq(ids, g), iters, flush)
+        rows.append(("embedding_ghost_norm", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+    if op in ("dp_step", "all"):
+        n = 1 << 27
+        p = torch.nn.Parameter(torch.zeros(n, device=dev))
+        from ..optimizers import DPOptimizerFastGradientClipping
+
+        dp = DPOptimizerFastGradientClipping(torch.optim.AdamW([p], lr=1e-3), noise_multiplier=1.0,
+                                             max_grad_norm=1.0, expected_batch_size=8)
+        grad = torch.zeros(n, device=dev)
+
+        def one():
+            p.summed_grad = grad
+            dp._is_last_step_skipped = False
+            if hasattr(grad, "_processed"):
+                del grad._processed
+            plan = dp._fused_plan()
+            plan.run(dp, noise_std=1.0, denominator=8.0)
+
+        byts = n * 4.0 * 8        # read+write of param, grad, exp_avg, exp_avg_sq
+        ms = _time(one, iters, flush)
+        rows.append(("fused_dp_adamw_step", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    _cuda.check_status()
+    print(f"shape B={B} T={T} d_in={din} d_out={dout}; peaks: {tf_peak} TFLOP/s bf16, {bw_peak} GB/s ({src})")
+    for name, ms, rate, unit, frac in rows:
+        print(f"{name:48s} {ms:9.4f} ms  {rate:10.1f} {unit:8s} {frac:6.3f} of {src} peak")
+    return rows
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--B", type=int, default=8)
+    ap.add_argument("--T", type=int, default=1024)
+    ap.add_argument("--din", type=int, default=2048)
+    ap.add_argument("--dout", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    run(args.op, args.B, args.T, args.din, args.dout, args.iters)
