@@ -60,8 +60,10 @@ class DPMultiheadAttention(nn.Module):
 
         self.add_bias_kv = add_bias_kv
         if add_bias_kv:
-            self.seq_bias_k = SequenceBias(embed_dim)
-            self.seq_bias_v = SequenceBias(embed_dim)
+            # same layout as the module's inputs, so that per-sample gradient
+            # capture sees the batch on the axis it expects
+            self.seq_bias_k = SequenceBias(embed_dim, batch_first=batch_first)
+            self.seq_bias_v = SequenceBias(embed_dim, batch_first=batch_first)
         self.add_zero_attn = add_zero_attn
         self.dropout = nn.Dropout(dropout)
         # attributes probed by nn.TransformerEncoderLayer's fast-path check
@@ -86,6 +88,8 @@ class DPMultiheadAttention(nn.Module):
         q = self.qlinear(query)
         k = self.klinear(key)
         v = self.vlinear(value)
+        if self.add_bias_kv:
+            k, v = self.seq_bias_k(k), self.seq_bias_v(v)
         if self.batch_first:  # work time-major like nn.MultiheadAttention
             q, k, v = (t.transpose(0, 1) for t in (q, k, v))
 
@@ -97,7 +101,7 @@ class DPMultiheadAttention(nn.Module):
             if attn_mask.dtype == torch.uint8:
                 warnings.warn("Byte tensor for attn_mask in nn.MultiheadAttention is deprecated.Use bool tensor instead.")
                 attn_mask = attn_mask.to(torch.bool)
-            Tk_in = k.shape[0]
+            Tk_in = k.shape[0] - (1 if self.add_bias_kv else 0)
             if attn_mask.dim() == 2:
                 if tuple(attn_mask.shape) != (Tq, Tk_in):
                     raise ValueError("The size of the 2D attn_mask is not correct.")
@@ -119,7 +123,6 @@ class DPMultiheadAttention(nn.Module):
                 key_padding_mask = F.pad(key_padding_mask, (0, 1))
 
         if self.add_bias_kv:
-            k, v = self.seq_bias_k(k), self.seq_bias_v(v)
             _grow_masks()
         if self.add_zero_attn:
             k = torch.cat([k, k.new_zeros(1, *k.shape[1:])], dim=0)

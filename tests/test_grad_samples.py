@@ -1,0 +1,212 @@
+"""Per-layer per-sample gradients against the micro-batch oracle (one
+batch-of-one backward pass per sample), for hooks and functorch modes and both
+loss reductions; plus ghost norms and clipped sums against the same oracle."""
+import pytest
+import torch
+import torch.nn as nn
+from torch.nn.utils.rnn import pack_padded_sequence
+
+from opacus_b200.grad_sample import GradSampleModule, GradSampleModuleFastGradientClipping
+from opacus_b200.layers import DPGRU, DPLSTM, DPRNN, DPMultiheadAttention, SequenceBias
+from opacus_b200.utils.per_sample_gradients_utils import (
+    check_per_sample_gradients_are_correct,
+    compute_grad_samples_microbatch_and_opacus,
+)
+
+torch.manual_seed(0)
+
+
+class _First(nn.Module):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+
+    def forward(self, *a):
+        out = self.m(*a)
+        if isinstance(out, tuple) and not isinstance(out, torch.nn.utils.rnn.PackedSequence):
+            return out[0]
+        return out
+
+
+CASES = [
+    ("linear2d", lambda: nn.Linear(7, 5), lambda: torch.randn(6, 7), True),
+    ("linear3d", lambda: nn.Linear(7, 5, bias=False), lambda: torch.randn(4, 9, 7), True),
+    ("linear4d", lambda: nn.Linear(3, 4), lambda: torch.randn(3, 2, 5, 3), True),
+    ("conv1d", lambda: nn.Conv1d(4, 6, 3, stride=2, padding=1), lambda: torch.randn(5, 4, 11), True),
+    ("conv1d_same", lambda: nn.Conv1d(4, 4, 4, padding="same", dilation=2, groups=2), lambda: torch.randn(3, 4, 13), True),
+    ("conv2d", lambda: nn.Conv2d(3, 8, (3, 2), stride=(1, 2), padding=(1, 0), dilation=(2, 1)), lambda: torch.randn(4, 3, 9, 8), True),
+    ("conv2d_groups", lambda: nn.Conv2d(6, 9, 3, groups=3, bias=False), lambda: torch.randn(3, 6, 7, 7), True),
+    ("conv3d", lambda: nn.Conv3d(2, 4, (2, 3, 2), stride=(1, 2, 1), padding=1), lambda: torch.randn(3, 2, 5, 6, 5), True),
+    ("layernorm", lambda: nn.LayerNorm(12), lambda: torch.randn(5, 7, 12), True),
+    ("layernorm2", lambda: nn.LayerNorm([7, 12]), lambda: torch.randn(5, 3, 7, 12), True),
+    ("rmsnorm", lambda: nn.RMSNorm(12, eps=1e-5), lambda: torch.randn(5, 7, 12), True),
+    ("groupnorm", lambda: nn.GroupNorm(2, 6), lambda: torch.randn(4, 6, 5, 3), True),
+    ("instancenorm", lambda: nn.InstanceNorm2d(5, affine=True), lambda: torch.randn(4, 5, 6, 3), True),
+    ("embedding", lambda: nn.Embedding(11, 6), lambda: torch.randint(0, 11, (5, 8)), True),
+    ("seqbias", lambda: SequenceBias(6, batch_first=True), lambda: torch.randn(4, 5, 6), True),
+    ("lstm", lambda: _First(DPLSTM(5, 6, num_layers=2, bidirectional=True, batch_first=True)), lambda: torch.randn(4, 7, 5), True),
+    ("gru_tf", lambda: _First(DPGRU(5, 6, batch_first=False)), lambda: torch.randn(7, 4, 5), False),
+    ("rnn", lambda: _First(DPRNN(5, 6, batch_first=True, nonlinearity="relu")), lambda: torch.randn(4, 7, 5), True),
+]
+
+
+@pytest.mark.parametrize("name,make,inp,batch_first", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("mode", ["hooks", "functorch"])
+def test_per_sample_grads(name, make, inp, batch_first, mode):
+    if mode == "functorch" and name in ("embedding",):
+        pass
+    torch.manual_seed(1)
+    assert check_per_sample_gradients_are_correct(inp(), make(), batch_first=batch_first, atol=1e-4, rtol=1e-3,
+                                                  grad_sample_mode=mode)
+
+
+class _SelfAttention(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.att = DPMultiheadAttention(8, 2, add_bias_kv=True, batch_first=True)
+
+    def forward(self, x):
+        return self.att(x, x, x)[0]
+
+
+def test_mha_per_sample_grads():
+    assert check_per_sample_gradients_are_correct(torch.randn(3, 5, 8), _SelfAttention(), atol=1e-4, rtol=1e-3)
+
+
+def test_packed_sequence_lstm():
+    torch.manual_seed(2)
+    x = pack_padded_sequence(torch.randn(4, 6, 5), [6, 4, 3, 1], batch_first=True)
+    micro, ours = compute_grad_samples_microbatch_and_opacus(x, _First(DPLSTM(5, 4, batch_first=True)), batch_first=True)
+    for k in micro:
+        assert torch.allclose(micro[k], ours[k], atol=1e-4, rtol=1e-3), k
+
+
+def test_embedding_bag():
+    torch.manual_seed(3)
+    for mode in ("sum", "mean"):
+        import copy
+
+        bag = nn.EmbeddingBag(13, 5, mode=mode)
+        plain = copy.deepcopy(bag)
+        idx = torch.randint(0, 13, (17,))
+        off = torch.tensor([0, 3, 4, 9, 12])
+        want = []
+        for b in range(5):
+            plain.zero_grad()
+            end = off[b + 1] if b < 4 else 17
+            plain(idx[off[b]:end], torch.tensor([0])).sum().backward()
+            want.append(plain.weight.grad.clone())
+        gsm = GradSampleModule(bag, loss_reduction="sum")
+        gsm(idx, off).sum().backward()
+        assert torch.allclose(bag.weight.grad_sample, torch.stack(want), atol=1e-5)
+        gsm.to_standard_module()
+
+
+def test_empty_batch_runs():
+    for layer, x in [(nn.Linear(4, 3), torch.randn(0, 5, 4)), (nn.Conv2d(2, 3, 3), torch.randn(0, 2, 6, 6)),
+                     (nn.Embedding(5, 3), torch.zeros(0, 4, dtype=torch.long)), (nn.GroupNorm(1, 2), torch.randn(0, 2, 3))]:
+        gsm = GradSampleModule(layer)
+        gsm(x).sum().backward()
+        for p in layer.parameters():
+            assert p.grad_sample.shape[0] == 0 or p.grad_sample.abs().sum() == 0
+
+
+class _Net(nn.Module):
+    """Embedding -> Linear -> LayerNorm -> Conv1d -> Linear, with a custom layer in the middle."""
+
+    def __init__(self, tied=False):
+        super().__init__()
+        self.emb = nn.Embedding(20, 8)
+        self.fc1 = nn.Linear(8, 8)
+        self.ln = nn.LayerNorm(8)
+        self.conv = nn.Conv1d(8, 8, 3, padding=1)
+        self.rms = nn.RMSNorm(8, eps=1e-5)
+        self.out = nn.Linear(8, 20, bias=False)
+        if tied:
+            self.out.weight = self.emb.weight
+
+    def forward(self, ids):
+        x = self.ln(torch.tanh(self.fc1(self.emb(ids))))
+        x = x + self.conv(x.transpose(1, 2)).transpose(1, 2)
+        return self.out(self.rms(x))
+
+
+def _oracle(model, ids, y, C, token_mean=True):
+    """Per-sample norms and clipped gradient sum by brute force."""
+    crit = nn.CrossEntropyLoss(reduction="sum")
+    params = [p for p in model.parameters()]
+    grads, norms = [], []
+    for i in range(ids.shape[0]):
+        model.zero_grad()
+        crit(model(ids[i:i + 1]).flatten(0, 1), y[i:i + 1].flatten()).div(ids.shape[1] if token_mean else 1).backward()
+        g = [p.grad.detach().clone() for p in params]
+        grads.append(g)
+        norms.append(torch.sqrt(sum(t.pow(2).sum() for t in g)))
+    norms = torch.stack(norms)
+    coef = (C / (norms + 1e-6)).clamp(max=1.0)
+    summed = [sum(coef[i] * grads[i][k] for i in range(len(grads))) for k in range(len(params))]
+    return norms, summed
+
+
+@pytest.mark.parametrize("tied", [False, True])
+@pytest.mark.parametrize("single_pass", [True, False])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_ghost_matches_oracle(tied, single_pass, reduction):
+    if tied and not single_pass:
+        pytest.skip("two-pass ghost clipping rejects tied parameters (as the reference does)")
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    torch.manual_seed(4)
+    model = _Net(tied)
+    ids = torch.randint(0, 20, (5, 7))
+    y = torch.randint(0, 20, (5, 7))
+    C = 0.7
+    norms, summed = _oracle(model, ids, y, C, token_mean=reduction == "mean")
+    model.zero_grad()
+    gsm = GradSampleModuleFastGradientClipping(model, max_grad_norm=C, loss_reduction=reduction, single_pass=single_pass)
+    opt = DPOptimizerFastGradientClipping(torch.optim.SGD(model.parameters(), lr=0.0), noise_multiplier=0.0,
+                                          max_grad_norm=C, expected_batch_size=5, loss_reduction=reduction)
+    crit = DPLossFastGradientClipping(gsm, opt, nn.CrossEntropyLoss(reduction=reduction), reduction)
+    loss = crit(gsm(ids).flatten(0, 1), y.flatten(), shape=(5, 7))
+    loss.backward()
+    assert torch.allclose(gsm.per_sample_gradient_norms, norms, rtol=1e-4, atol=1e-5)
+    for p, want in zip(model.parameters(), summed):
+        assert torch.allclose(p.grad, want, rtol=1e-3, atol=1e-5)
+    gsm.to_standard_module()
+    for p in model.parameters():
+        assert not hasattr(p, "grad_sample") and not hasattr(p, "_forward_counter")
+
+
+def test_hooks_controller_and_state_dict_prefix():
+    from opacus_b200.grad_sample import GradSampleHooks
+
+    m = nn.Sequential(nn.Linear(3, 4), nn.ReLU(), nn.Linear(4, 2))
+    ctl = GradSampleHooks(m)
+    m(torch.randn(5, 3)).sum().backward()
+    assert m[0].weight.grad_sample.shape == (5, 4, 3)
+    with pytest.raises(ValueError):
+        GradSampleHooks(m)
+    ctl.cleanup()
+    assert not hasattr(m[0].weight, "grad_sample")
+    w = GradSampleModule(m)
+    assert all(k.startswith("_module.") for k in w.state_dict())
+    assert w.to_standard_module() is m
+
+
+def test_accumulation_list_and_poisson_guard():
+    m = GradSampleModule(nn.Linear(3, 2))
+    for _ in range(2):
+        m(torch.randn(4, 3)).sum().backward()
+    assert isinstance(m._module.weight.grad_sample, list) and len(m._module.weight.grad_sample) == 2
+    m.zero_grad()
+    assert m._module.weight.grad_sample is None
+    m.forbid_grad_accumulation()
+    m(torch.randn(4, 3)).sum().backward()
+    with pytest.raises(ValueError):
+        m(torch.randn(4, 3)).sum().backward()
+
+
+def test_buffers_rejected():
+    with pytest.raises(NotImplementedError):
+        GradSampleModule(nn.BatchNorm1d(3))
