@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--engine", default="sharded", choices=["sharded", "plain"],
+                    help="ours: sharded data-parallel engine (default) or, on one GPU, the plain ghost path")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a benchmark)")
     ap.add_argument("--vocab", type=int, default=None, help="debug only")
     ap.add_argument("--seq", type=int, default=SEQ, help="debug only")
@@ -139,14 +141,13 @@ def build_ours(args, rank, world):
     model, cfg = make_model(args, tie=True)
     module = model
     mode = "ghost"
-    if world > 1:
-        try:
-            from opacus_b200.parallel.sharded import ShardedDataParallel
+    if args.engine == "sharded":
+        from opacus_b200.utils.fsdp_utils import FSDP2Wrapper
 
-            module = ShardedDataParallel(model)
-            mode = "ghost_fsdp"
-        except (ImportError, TypeError, NotImplementedError):
-            module = DPDDP(model)
+        module = FSDP2Wrapper(model)          # -> ShardedDataParallel: bf16 compute weights, sharded fp32 state
+        mode = "ghost_fsdp"
+    elif world > 1:
+        module = DPDDP(model)
     optimizer = torch.optim.AdamW(model.parameters(), lr=LR)
     n_data = DATASET_BATCHES * args.batch * world
     ds = TensorDataset(torch.zeros(n_data, 1, dtype=torch.long))     # only its length matters (sample rate)
@@ -233,13 +234,16 @@ def main():
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))
         return 0
     rank, local, world = setup_dist(args.gpus)
-    if world > 1 or args.impl == "reference":
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        os.environ.setdefault("RANK", "0")
-        os.environ.setdefault("WORLD_SIZE", "1")
-        if world > 1 and not dist.is_initialized():
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    need_pg = world > 1 or (args.impl == "ours" and args.engine == "sharded")
+    if need_pg and not dist.is_initialized():
+        import datetime
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=180))
 
     try:
         if args.impl == "reference":
@@ -287,6 +291,8 @@ def main():
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    # every rank runs the profiled extra step (it contains collectives / peer barriers)
+    per_step = count_launches(step, ids_d[0], labels_d[0]) if args.impl == "ours" else None
 
     if rank == 0:
         eps = None
@@ -294,10 +300,7 @@ def main():
             eps = float(engine.get_epsilon(1e-5))
         except Exception:
             pass
-        launches = None
-        if args.impl == "ours":
-            per_step = count_launches(step, ids_d[0], labels_d[0])
-            launches = None if per_step is None else per_step * args.steps
+        launches = None if per_step is None else per_step * args.steps
         full = args.layers is None and args.vocab is None and args.seq == SEQ and args.batch == PER_GPU_BATCH
         out = {
             "metric": "dp_sgd_tokens_per_s_llama1b_ghost_clip",
@@ -330,7 +333,7 @@ def main():
             "gpu_launches": launches,
         }
         print(json.dumps(out))
-    if world > 1:
+    if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
     return 0

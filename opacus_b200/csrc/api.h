@@ -76,6 +76,26 @@ struct DpkStepHyper {
 int dpk_fused_dp_step(const struct DpkTensorEntry* table_dev, int n_tensors, int64_t total_chunks,
                       const int64_t* chunk_prefix_dev, struct DpkStepHyper h, cudaStream_t stream);
 
+// ---- sharded data-parallel step: reduce-scatter + noise + update + all-gather over peer memory
+// Pointer arrays are indexed by rank and hold addresses that are valid on THIS GPU (peer mappings of
+// symmetric allocations; entry [rank] is local).  grad/param are flat buffers over the whole parameter
+// space; master/state0/state1 cover only the owned slice [slice_begin, slice_begin + slice_len).
+// flags: at least 32 zero-initialised 32-bit words per rank.  epoch: 1, 2, 3, ... on successive calls.
+struct DpkShardedStep {
+  const float* grad[8];
+  void* param[8];
+  uint32_t* flags[8];
+  float* master;
+  float* state0;
+  float* state1;
+  int64_t slice_begin, slice_len;
+  int32_t world, rank, param_bf16, pad;
+  uint32_t epoch, pad2;
+  struct DpkStepHyper h;
+  uint32_t* status;
+};
+int dpk_sharded_dp_step(const struct DpkShardedStep* p, cudaStream_t stream);
+
 // Standard normal samples (testing the generator): out[i] for i < n.
 int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream);
 

@@ -259,6 +259,41 @@ void fused_dp_step(at::Tensor table, at::Tensor prefix, int64_t n_tensors, int64
         "fused_dp_step");
 }
 
+// ------------------------------------------------------------------ sharded DP step over peer memory
+void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_ptrs, std::vector<int64_t> flag_ptrs,
+                     at::Tensor master, c10::optional<at::Tensor> state0, c10::optional<at::Tensor> state1,
+                     int64_t slice_begin, int64_t slice_len, int64_t rank, bool param_bf16, int64_t epoch,
+                     int64_t kind, bool nesterov, bool first_step, double lr, double momentum, double dampening,
+                     double weight_decay, double beta1, double beta2, double eps, double bias_c1,
+                     double bias_c2_sqrt, double noise_std, double inv_scale, int64_t seed, int64_t offset) {
+  c10::cuda::CUDAGuard guard(master.device());
+  raise_if_failed(master.get_device());
+  const int world = (int)grad_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)param_ptrs.size() == world && (int)flag_ptrs.size() == world,
+              "sharded_dp_step supports 1..8 ranks");
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.numel() >= slice_len, "bad master");
+  DpkShardedStep p{};
+  for (int r = 0; r < world; ++r) {
+    p.grad[r] = reinterpret_cast<const float*>(grad_ptrs[r]);
+    p.param[r] = reinterpret_cast<void*>(param_ptrs[r]);
+    p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  p.master = master.data_ptr<float>();
+  p.state0 = state0.has_value() ? state0->data_ptr<float>() : nullptr;
+  p.state1 = state1.has_value() ? state1->data_ptr<float>() : nullptr;
+  p.slice_begin = slice_begin; p.slice_len = slice_len;
+  p.world = world; p.rank = (int)rank; p.param_bf16 = param_bf16 ? 1 : 0;
+  p.epoch = (uint32_t)epoch;
+  DpkStepHyper& h = p.h;
+  h.kind = (int)kind; h.nesterov = nesterov; h.first_step = first_step;
+  h.lr = (float)lr; h.momentum = (float)momentum; h.dampening = (float)dampening; h.weight_decay = (float)weight_decay;
+  h.beta1 = (float)beta1; h.beta2 = (float)beta2; h.eps = (float)eps; h.bias_c1 = (float)bias_c1;
+  h.bias_c2_sqrt = (float)bias_c2_sqrt; h.noise_std = (float)noise_std; h.inv_scale = (float)inv_scale;
+  h.seed = (uint64_t)seed; h.offset = (uint64_t)offset;
+  p.status = status_for(master.get_device()).dev;
+  check(dpk_sharded_dp_step(&p, stream()), "sharded_dp_step");
+}
+
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
   at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
@@ -286,6 +321,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("norm_channel_grad", &norm_channel_grad);
   m.def("embedding_scatter", &embedding_scatter);
   m.def("fused_dp_step", &fused_dp_step);
+  m.def("sharded_dp_step", &sharded_dp_step);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
   m.def("tensor_entry_size", &tensor_entry_size);

@@ -1,0 +1,206 @@
+// Sharded data-parallel DP step in ONE kernel per rank, over NVLink peer memory:
+//
+//   reduce-scatter : every rank sums, for the slice of the flat gradient it owns,
+//                    the clipped gradient sums of all ranks (plain peer loads)
+//   noise          : the owner draws the single N(0, (sigma*C)^2) sample of each
+//                    element (Philox counter = global element index, so no two
+//                    ranks ever draw for the same element)
+//   update         : scale, then SGD / Adam / AdamW on the fp32 master weights and
+//                    optimiser state of the owned slice (never replicated)
+//   all-gather     : the new weights are stored, in compute precision, straight
+//                    into every rank's parameter buffer (plain peer stores)
+//
+// Ranks meet twice through flag words in symmetric memory: before the first peer
+// access (everyone's gradients are final, nobody still reads the old weights) and
+// after the last store (everyone's weights are complete when the kernel ends).
+// Both waits are bounded; a rank that gives up records it and returns.
+//
+// Replaces, for the sharded (FSDP-style) path, two reduce-scatters, three
+// all-gathers and the per-parameter noise/scale/step kernels of the reference
+// (opacus/optimizers/fsdpoptimizer_fast_gradient_clipping.py:138-181 on top of
+// torch FSDP2), and for plain data parallelism the per-parameter all-reduce of
+// opacus/optimizers/ddpoptimizer.py:64-70.
+#include "api.h"
+#include "common.cuh"
+#include "host_util.h"
+
+namespace dpk {
+
+constexpr int kSlotStart = 0;     // flags[kSlotStart + r]  : rank r reached the kernel (epoch)
+constexpr int kSlotDone = 8;      // flags[kSlotDone + r]   : rank r finished its stores (epoch)
+constexpr int kSlotGo = 16;       // local: block 0 -> other blocks
+constexpr int kSlotCount = 17;    // local: finished-block counter
+constexpr uint32_t kAbortBit = 0x80000000u;
+constexpr int kShThreads = 512;
+
+__device__ __forceinline__ bool spin_until_epoch(volatile uint32_t* word, uint32_t epoch, uint32_t* status,
+                                                 uint32_t site) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    const uint32_t v = *word;
+    if (v & kAbortBit) return false;
+    if (static_cast<int32_t>(v - epoch) >= 0) return true;
+    if ((++spins & 0xffu) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        report_error(status, site, ERR_WAIT_TIMEOUT, epoch, v);
+        return false;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep p) {
+  __shared__ uint32_t sh_ok;
+  volatile uint32_t* my_flags = p.flags[p.rank];
+
+  // ---------------------------------------------------------------- meet #1
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) sh_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < p.world) {
+      __threadfence_system();
+      volatile uint32_t* theirs = p.flags[threadIdx.x] + kSlotStart + p.rank;
+      *theirs = p.epoch;
+      if (!spin_until_epoch(my_flags + kSlotStart + threadIdx.x, p.epoch, p.status, 21)) sh_ok = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      my_flags[kSlotGo] = sh_ok ? p.epoch : (p.epoch | kAbortBit);
+    }
+  }
+  if (threadIdx.x == 0) sh_ok = spin_until_epoch(my_flags + kSlotGo, p.epoch, p.status, 22) ? 1 : 0;
+  __syncthreads();
+  const bool go = sh_ok != 0;
+
+  // ---------------------------------------------------------------- reduce, noise, update, publish
+  if (go) {
+    const DpkStepHyper h = p.h;
+    const Philox rng(h.seed);
+    const int64_t nvec = p.slice_len >> 3;
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t li = v << 3;                 // index inside the owned slice
+      const int64_t gi = p.slice_begin + li;     // index in the flat parameter space
+      float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int q = 0; q < p.world; ++q) {
+        int r = p.rank + q;
+        if (r >= p.world) r -= p.world;
+        const float4* src = reinterpret_cast<const float4*>(p.grad[r] + gi);
+        const float4 a = __ldcg(src), b = __ldcg(src + 1);
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+      }
+      if (h.noise_std != 0.f) {
+        const uint4 u0 = rng(static_cast<uint64_t>(gi) >> 2, h.offset);
+        const uint4 u1 = rng((static_cast<uint64_t>(gi) >> 2) + 1, h.offset);
+        const float2 z0 = box_muller(u0.x, u0.y), z1 = box_muller(u0.z, u0.w);
+        const float2 z2 = box_muller(u1.x, u1.y), z3 = box_muller(u1.z, u1.w);
+        g[0] += z0.x * h.noise_std; g[1] += z0.y * h.noise_std; g[2] += z1.x * h.noise_std; g[3] += z1.y * h.noise_std;
+        g[4] += z2.x * h.noise_std; g[5] += z2.y * h.noise_std; g[6] += z3.x * h.noise_std; g[7] += z3.y * h.noise_std;
+      }
+      float w[8], m[8], s[8];
+      {
+        const float4 a = *reinterpret_cast<const float4*>(p.master + li), b = *reinterpret_cast<const float4*>(p.master + li + 4);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+      }
+      const bool has_m = p.state0 != nullptr && (h.kind != 0 || h.momentum != 0.f);
+      if (has_m) {
+        const float4 a = *reinterpret_cast<const float4*>(p.state0 + li), b = *reinterpret_cast<const float4*>(p.state0 + li + 4);
+        m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
+      }
+      if (h.kind != 0) {
+        const float4 a = *reinterpret_cast<const float4*>(p.state1 + li), b = *reinterpret_cast<const float4*>(p.state1 + li + 4);
+        s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w; s[4] = b.x; s[5] = b.y; s[6] = b.z; s[7] = b.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float grad = g[j] * h.inv_scale;
+        float pv = w[j];
+        if (h.kind == 0) {
+          if (h.weight_decay != 0.f) grad = fmaf(h.weight_decay, pv, grad);
+          if (h.momentum != 0.f) {
+            const float buf = h.first_step ? grad : fmaf(h.momentum, m[j], (1.f - h.dampening) * grad);
+            m[j] = buf;
+            grad = h.nesterov ? fmaf(h.momentum, buf, grad) : buf;
+          }
+          pv = fmaf(-h.lr, grad, pv);
+        } else {
+          if (h.weight_decay != 0.f) {
+            if (h.kind == 2) pv *= (1.f - h.lr * h.weight_decay);
+            else grad = fmaf(h.weight_decay, pv, grad);
+          }
+          m[j] = fmaf(h.beta1, m[j], (1.f - h.beta1) * grad);
+          s[j] = fmaf(h.beta2, s[j], (1.f - h.beta2) * grad * grad);
+          pv -= (h.lr / h.bias_c1) * (m[j] / (sqrtf(s[j]) / h.bias_c2_sqrt + h.eps));
+        }
+        w[j] = pv;
+      }
+      *reinterpret_cast<float4*>(p.master + li) = make_float4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<float4*>(p.master + li + 4) = make_float4(w[4], w[5], w[6], w[7]);
+      if (has_m) {
+        *reinterpret_cast<float4*>(p.state0 + li) = make_float4(m[0], m[1], m[2], m[3]);
+        *reinterpret_cast<float4*>(p.state0 + li + 4) = make_float4(m[4], m[5], m[6], m[7]);
+      }
+      if (h.kind != 0) {
+        *reinterpret_cast<float4*>(p.state1 + li) = make_float4(s[0], s[1], s[2], s[3]);
+        *reinterpret_cast<float4*>(p.state1 + li + 4) = make_float4(s[4], s[5], s[6], s[7]);
+      }
+      if (p.param_bf16) {
+        uint4 pk;
+        uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __nv_bfloat162 hv = __floats2bfloat162_rn(w[2 * q], w[2 * q + 1]);
+          pw[q] = *reinterpret_cast<uint32_t*>(&hv);
+        }
+        for (int q = 0; q < p.world; ++q) {
+          int r = p.rank + q;
+          if (r >= p.world) r -= p.world;
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.param[r]) + gi) = pk;
+        }
+      } else {
+        for (int q = 0; q < p.world; ++q) {
+          int r = p.rank + q;
+          if (r >= p.world) r -= p.world;
+          float* dst = reinterpret_cast<float*>(p.param[r]) + gi;
+          *reinterpret_cast<float4*>(dst) = make_float4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- meet #2
+  __threadfence_system();
+  __syncthreads();
+  __shared__ uint32_t sh_last;
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(const_cast<uint32_t*>(my_flags + kSlotCount), 1u);
+    sh_last = (old == gridDim.x - 1) ? 1u : 0u;
+    if (sh_last) my_flags[kSlotCount] = 0;
+  }
+  __syncthreads();
+  if (sh_last && go && threadIdx.x < p.world) {
+    __threadfence_system();
+    volatile uint32_t* theirs = p.flags[threadIdx.x] + kSlotDone + p.rank;
+    *theirs = p.epoch;
+    spin_until_epoch(my_flags + kSlotDone + threadIdx.x, p.epoch, p.status, 23);
+  }
+}
+
+}  // namespace dpk
+
+extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream) {
+  using namespace dpk;
+  const DpkShardedStep& p = *ph;
+  if (p.world < 1 || p.world > 8 || p.rank < 0 || p.rank >= p.world || (p.slice_len & 7) || (p.slice_begin & 7))
+    return cudaErrorInvalidValue;
+  int grid = num_sms();                       // one resident block per SM: every block can spin safely
+  const int64_t nvec = p.slice_len >> 3;
+  const int64_t need = (nvec + kShThreads - 1) / kShThreads;
+  if (need < grid) grid = need < 1 ? 1 : (int)need;
+  sharded_step_kernel<<<grid, kShThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}

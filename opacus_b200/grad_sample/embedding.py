@@ -58,5 +58,11 @@ def compute_embedding_norm_sample(layer: nn.Embedding, activations: List[torch.T
 def compute_embedding_weighted_grad(layer, activations, backprops, coef, g_scale: float = 1.0):
     if not layer.weight.requires_grad:
         return {}
-    return {layer.weight: ops.embedding_weighted_grad(
-        activations[0], backprops, coef, layer.num_embeddings, g_scale, out_dtype=layer.weight.dtype)}
+    dst = getattr(layer.weight, "_dp_grad_out", None)
+    fresh = getattr(layer.weight, "_dp_grad_fresh", True)
+    grad = ops.embedding_weighted_grad(
+        activations[0], backprops, coef, layer.num_embeddings, g_scale,
+        out_dtype=layer.weight.dtype if dst is None else None, out=dst, accumulate=not fresh)
+    if dst is not None:
+        layer.weight._dp_grad_fresh = False
+    return {layer.weight: grad}

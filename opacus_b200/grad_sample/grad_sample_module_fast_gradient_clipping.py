@@ -316,7 +316,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         if not self._sites or self._norm_sq_total is None:
             coef = torch.zeros(0, device=self.trainable_parameters[0].device) if self.trainable_parameters else None
             for p in self.trainable_parameters:
-                if p.grad is None:
+                if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
                     p.grad = torch.zeros_like(p)
             self._reset_single_pass_state()
             return coef
@@ -337,13 +337,23 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             for p, g in grads.items():
                 if not p.requires_grad:
                     continue
+                dst = getattr(p, "_dp_grad_out", None)
+                if dst is not None:
+                    # engine-owned gradient storage (fp32, independent of the parameter dtype)
+                    if g.data_ptr() != dst.data_ptr():
+                        if getattr(p, "_dp_grad_fresh", True):
+                            dst.copy_(g.reshape(p.shape))
+                            p._dp_grad_fresh = False
+                        else:
+                            dst.add_(g.reshape(p.shape))
+                    continue
                 g = g.reshape(p.shape).to(p.dtype)
                 if p.grad is None:
                     p.grad = g if g._base is None else g.clone()
                 else:
                     p.grad.add_(g)
         for p in self.trainable_parameters:
-            if p.grad is None:
+            if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
                 p.grad = torch.zeros_like(p)
         self._reset_single_pass_state()
         return coef

@@ -53,7 +53,14 @@ def compute_linear_norm_sample(layer: nn.Linear, activations: List[torch.Tensor]
 @register_wgrad_sampler(nn.Linear)
 def compute_linear_weighted_grad(layer, activations, backprops, coef, g_scale: float = 1.0):
     w, b = _wants(layer)
-    gw, gb = ops.linear_weighted_grad(activations[0], backprops, coef, g_scale, want_bias=b)
+    # An engine may designate where the clipped sum of this weight has to go
+    # (a slice of its flat gradient buffer); the GEMM then writes there directly.
+    dst = getattr(layer.weight, "_dp_grad_out", None) if w else None
+    fresh = getattr(layer.weight, "_dp_grad_fresh", True)
+    gw, gb = ops.linear_weighted_grad(activations[0], backprops, coef, g_scale, want_bias=b, out=dst,
+                                      accumulate=not fresh)
+    if dst is not None:
+        layer.weight._dp_grad_fresh = False
     out = {}
     if w:
         out[layer.weight] = gw

@@ -52,10 +52,15 @@ def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0
     return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
 
 
-def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False):
+def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False, out=None, accumulate=False):
+    """``out``: optional fp32 destination written in place (added to when ``accumulate``)."""
     if _on_gpu(a, g) and _kernel_dtype(g) and g.shape[0] > 0:
-        return _k().linear_weighted_grad(a, g, c, g_scale, want_bias)
-    return _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+        return _k().linear_weighted_grad(a, g, c, g_scale, want_bias, out=out, accumulate=accumulate)
+    w, b = _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+    if out is not None:
+        out.add_(w.to(out.dtype)) if accumulate else out.copy_(w)
+        w = out
+    return w, b
 
 
 # -------------------------------------------------------------------- Embedding
@@ -69,10 +74,16 @@ def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] =
     return _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
 
 
-def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None):
+def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None,
+                            out=None, accumulate=False):
     if _on_gpu(g) and _kernel_dtype(g) and g.shape[0] > 0:
-        return _k().embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype)
-    return _ref.embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype)
+        return _k().embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype,
+                                            out=out, accumulate=accumulate)
+    w = _ref.embedding_weighted_grad(ids, g, c, num_embeddings, g_scale, padding_idx, out_dtype)
+    if out is not None:
+        out.add_(w.to(out.dtype)) if accumulate else out.copy_(w)
+        w = out
+    return w
 
 
 # ----------------------------------------------------------- normalisation layers

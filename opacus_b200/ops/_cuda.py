@@ -102,12 +102,18 @@ def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0
     return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
 
 
-def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False):
+def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False, out=None, accumulate=False):
+    """``out`` (fp32 ``[d_out, d_in]``, contiguous) receives the result in place:
+    overwritten, or added to when ``accumulate``."""
     a3, g3 = _bt(a), _bt(g)
     B, T, d_in = a3.shape
     d_out = g3.shape[-1]
     if not (g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0):
-        return _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+        w, b = _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
+        if out is not None:
+            out.add_(w) if accumulate else out.copy_(w)
+            w = out
+        return w, b
     C = load()
     c = c.float().contiguous()
     a2 = a3.reshape(B * T, d_in)
@@ -119,8 +125,15 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False)
     else:
         g_op = C.scale_rows(g2.contiguous(), c, T, float(g_scale))
         a_op = _bf16(a2)
-    out = torch.empty(d_out, d_in, dtype=torch.float32, device=g.device)
-    C.wgrad_tn(g_op, a_op, out, 0.0)
+    if out is None or out.dtype != torch.float32 or not out.is_contiguous():
+        target = torch.empty(d_out, d_in, dtype=torch.float32, device=g.device)
+        C.wgrad_tn(g_op, a_op, target, 0.0)
+        if out is not None:
+            out.add_(target) if accumulate else out.copy_(target)
+        else:
+            out = target
+    else:
+        C.wgrad_tn(g_op, a_op, out, 1.0 if accumulate else 0.0)
     bias = None
     if want_bias:
         per_sample = g3.float().sum(dim=1)                       # [B, d_out]
@@ -143,10 +156,18 @@ def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] =
     return w
 
 
-def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None):
+def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None,
+                            out=None, accumulate=False):
     B = ids.shape[0]
     D = g.shape[-1]
     T = ids.numel() // B
+    if out is not None and out.dtype == torch.float32 and out.is_contiguous():
+        if not accumulate:
+            out.zero_()
+        load().embedding_scatter(ids.reshape(-1).contiguous().long(), g.reshape(-1, D).contiguous(),
+                                 c.float().contiguous(), T, -1 if padding_idx is None else int(padding_idx),
+                                 float(g_scale), out)
+        return out
     out = torch.zeros(num_embeddings, D, dtype=torch.float32, device=g.device)
     load().embedding_scatter(ids.reshape(-1).contiguous().long(), g.reshape(-1, D).contiguous(),
                              c.float().contiguous(), T, -1 if padding_idx is None else int(padding_idx),

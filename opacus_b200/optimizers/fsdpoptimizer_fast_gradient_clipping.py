@@ -69,6 +69,8 @@ class FSDPOptimizerFastGradientClipping(DPOptimizerFastGradientClipping):
         for p in self.params:
             if not self._is_last_step_skipped:
                 self.grad_state.setdefault(p, {})["summed_grad"] = None
+        if self.engine is not None and not self._is_last_step_skipped:
+            self.engine.mark_grads_fresh()
         self.original_optimizer.zero_grad(set_to_none)
 
     def add_noise(self):

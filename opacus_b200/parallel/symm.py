@@ -1,0 +1,63 @@
+"""Symmetric (peer-visible) device buffers over NVLink.
+
+One process per GPU; every rank allocates the same sizes in the same order and
+then holds, for each buffer, the addresses of all ranks' copies mapped into its
+own address space.  Allocation and handle exchange use
+``torch.distributed._symmetric_memory`` (CUDA virtual memory management plus a
+rendezvous through the process group's store); nothing else of that module is
+used -- every access to peer memory happens inside this package's own kernels
+through plain loads and stores.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class SymmetricBuffer:
+    """``tensor`` is this rank's copy; ``ptrs[r]`` is rank ``r``'s copy as seen from this GPU."""
+
+    def __init__(self, tensor: torch.Tensor, ptrs: List[int], handle=None):
+        self.tensor = tensor
+        self.ptrs = ptrs
+        self.handle = handle
+
+
+def world_info(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def alloc(numel: int, dtype: torch.dtype, device, group=None, zero: bool = True) -> SymmetricBuffer:
+    rank, world = world_info(group)
+    if world == 1:
+        t = torch.zeros(numel, dtype=dtype, device=device) if zero else torch.empty(numel, dtype=dtype, device=device)
+        return SymmetricBuffer(t, [t.data_ptr()])
+    import torch.distributed._symmetric_memory as symm_mem
+
+    t = symm_mem.empty(numel, dtype=dtype, device=device)
+    handle = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+    if zero:
+        t.zero_()
+    ptrs = [int(p) for p in handle.buffer_ptrs]
+    assert ptrs[rank] == t.data_ptr(), "symmetric buffer does not start at its allocation"
+    return SymmetricBuffer(t, ptrs, handle)
+
+
+def available(group=None) -> Optional[str]:
+    """``None`` if peer-visible buffers can be used by this job, else the reason."""
+    rank, world = world_info(group)
+    if world == 1:
+        return None
+    if not torch.cuda.is_available():
+        return "no CUDA device"
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception as e:  # pragma: no cover
+        return f"symmetric memory module unavailable: {e}"
+    if dist.get_backend(group) != "nccl":
+        return "process group backend is not nccl"
+    return None

@@ -1,0 +1,115 @@
+"""The sharded data-parallel engine on one GPU (world size 1) against the plain
+ghost path, and its fused step kernel against torch.optim."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.utils.data import DataLoader, TensorDataset
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pg():
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29541")
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=0, world_size=1)
+    yield
+    dist.destroy_process_group()
+
+
+def _model():
+    from opacus_b200.models import Llama, LlamaConfig
+
+    torch.manual_seed(0)
+    return Llama(LlamaConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=256)).cuda()
+
+
+def _private(module, mode, sigma, opt_cls=torch.optim.AdamW, **kw):
+    from opacus_b200 import PrivacyEngine
+
+    inner = module.module if hasattr(module, "module") else module
+    opt = opt_cls(inner.parameters(), lr=1e-2, **kw)
+    dl = DataLoader(TensorDataset(torch.zeros(32, 1)), batch_size=4)
+    pe = PrivacyEngine(accountant="rdp")
+    return pe.make_private(module=module, optimizer=opt, criterion=nn.CrossEntropyLoss(), data_loader=dl,
+                           noise_multiplier=sigma, max_grad_norm=0.5, grad_sample_mode=mode, poisson_sampling=False)
+
+
+def _step(m, opt, crit, ids):
+    opt.zero_grad(set_to_none=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        logits = m(ids[:, :-1])
+    loss = crit(logits.float().flatten(0, 1), ids[:, 1:].reshape(-1), shape=(ids.shape[0], ids.shape[1] - 1))
+    loss.backward()
+    opt.step()
+    return loss.item()
+
+
+@pytest.mark.parametrize("opt_cls,kw", [(torch.optim.AdamW, {}), (torch.optim.SGD, {"momentum": 0.9})])
+def test_sharded_engine_world1_matches_fp32_master_reference(pg, opt_cls, kw):
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+    from opacus_b200.ops import _cuda
+
+    ids = torch.randint(0, 512, (4, 129), device="cuda")
+    eng = ShardedDataParallel(_model())
+    m, opt, crit, _ = _private(eng, "ghost_fsdp", 0.0, opt_cls, **kw)
+    norms = []
+    for _ in range(3):
+        _step(m, opt, crit, ids)
+        norms.append(m.per_sample_gradient_norms.clone())
+    torch.cuda.synchronize()
+    _cuda.check_status()
+    got = eng.full_precision_state_dict()
+
+    # reference: the same bf16-compute / fp32-master recipe spelled out with torch ops
+    ref = _model()
+    master = {n: p.detach().clone().float() for n, p in ref.named_parameters()}
+    ref = ref.bfloat16()
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    shadow = [nn.Parameter(v.clone()) for v in master.values()]
+    torch_opt = opt_cls(shadow, lr=1e-2, **kw)
+    gsm = GradSampleModuleFastGradientClipping(ref, max_grad_norm=0.5, single_pass=True)
+    dpo = DPOptimizerFastGradientClipping(torch.optim.SGD(ref.parameters(), lr=0.0), noise_multiplier=0.0,
+                                          max_grad_norm=0.5, expected_batch_size=4, fused_step=False)
+    crit2 = DPLossFastGradientClipping(gsm, dpo, nn.CrossEntropyLoss(), "mean")
+    for it in range(3):
+        for p in ref.parameters():
+            p.grad = None
+        logits = gsm(ids[:, :-1])
+        crit2(logits.float().flatten(0, 1), ids[:, 1:].reshape(-1), shape=(4, 128)).backward()
+        assert torch.allclose(gsm.per_sample_gradient_norms, norms[it], rtol=2e-2), (it, gsm.per_sample_gradient_norms, norms[it])
+        seen = set()
+        for (n, p), s in zip(ref.named_parameters(), shadow):
+            s.grad = p.grad.float() / 4
+        torch_opt.step()
+        for (n, p), s in zip(ref.named_parameters(), shadow):
+            p.data.copy_(s.data.to(torch.bfloat16))
+    for (n, _), s in zip(ref.named_parameters(), shadow):
+        a, b = got[n], s.detach()
+        assert ((a - b).norm() / (b.norm() + 1e-12)).item() < 2e-2, (n, (a - b).abs().max())
+
+
+def test_sharded_engine_noise_and_virtual_steps(pg):
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 65), device="cuda")
+    eng = ShardedDataParallel(_model())
+    before = eng.master.clone()
+    m, opt, crit, _ = _private(eng, "ghost_fsdp", 100.0, torch.optim.SGD)
+    opt.signal_skip_step(True)
+    _step(m, opt, crit, ids)                       # accumulate only
+    assert torch.equal(eng.master, before)
+    g1 = eng.flat_grad().clone()
+    opt.signal_skip_step(False)
+    _step(m, opt, crit, ids)                       # second physical batch + the update
+    torch.cuda.synchronize()
+    delta = (eng.master - before) / 1e-2 * 4        # = -(sum of clipped grads + noise)
+    assert abs(delta.std().item() - 100.0 * 0.5) / 50.0 < 0.05
+    assert g1.abs().sum() > 0
