@@ -55,7 +55,9 @@ def available(group=None) -> Optional[str]:
     if not torch.cuda.is_available():
         return "no CUDA device"
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+
+        importlib.import_module("torch.distributed._symmetric_memory")
     except Exception as e:  # pragma: no cover
         return f"symmetric memory module unavailable: {e}"
     if dist.get_backend(group) != "nccl":

@@ -1,0 +1,25 @@
+"""Multi-GPU tests: each launches a torchrun job on all visible GPUs (2 to 8)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(script, nproc, timeout=420):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+           "--nproc-per-node", str(nproc), os.path.join(HERE, script)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_sharded_engine_multi_gpu():
+    out = _launch("dist_sharded_check.py", min(torch.cuda.device_count(), 8))
+    assert "sharded check ok" in out
