@@ -18,6 +18,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--engine", default="sharded", choices=["sharded", "plain"])
     args = ap.parse_args()
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -28,6 +29,12 @@ def main():
     build = bench.build_ours if args.impl == "ours" else bench.build_reference
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29534")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    if args.impl == "ours" and args.engine == "sharded":
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", 0))
     step, cfg, engine, mode = build(args, 0, 1)
     ids_h, labels_h = bench.make_data(cfg, args, 1, 0)
     ids, labels = ids_h.cuda(), labels_h.cuda()
