@@ -19,6 +19,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--engine", default="sharded", choices=["sharded", "plain"])
+    ap.add_argument("--cprofile", type=int, default=0, help="profile the host side of this many steps instead")
     args = ap.parse_args()
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -41,6 +42,27 @@ def main():
     for i in range(3):
         step(ids[i], labels[i])
     torch.cuda.synchronize()
+    if args.cprofile:
+        import cProfile
+        import pstats
+        import time
+
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(args.cprofile):
+            step(ids[i % len(ids)], labels[i % len(ids)])
+        host = (time.perf_counter() - t0) / args.cprofile
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) / args.cprofile
+        print(f"host time to enqueue one step {host * 1e3:.1f} ms; wall {wall * 1e3:.1f} ms")
+        pr = cProfile.Profile()
+        pr.enable()
+        for i in range(args.cprofile):
+            step(ids[i % len(ids)], labels[i % len(ids)])
+        pr.disable()
+        torch.cuda.synchronize()
+        pstats.Stats(pr).sort_stats("tottime").print_stats(args.top)
+        return
     from torch.profiler import ProfilerActivity, profile
 
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:

@@ -24,6 +24,13 @@ int dpk_gram_pair_norm(const void* x, const int64_t* ids, const void* g, int B, 
 int dpk_wgrad_tn(const void* gs, const void* a, int K, int M, int N, void* out, int out_bf16, float beta,
                  uint32_t* status, cudaStream_t stream);
 
+// Batched / tunable form: gs [batch, K, M], a [batch, K, N], out [batch, M, N]; norm_sq (or NULL) receives
+// += ||out[b]||_F^2 per batch entry (fp32 atomics; only without K splitting).  force_* = 0 lets the
+// launcher choose tile shape (256x256, 128x256, 128x128) and K split (1, 2, 4, 8).
+int dpk_wgrad_tn_ex(const void* gs, const void* a, int K, int M, int N, int batch, void* out, int out_bf16,
+                    float beta, float* norm_sq, int force_bm, int force_bn, int force_splits, uint32_t* status,
+                    cudaStream_t stream);
+
 // ---- elementwise / reduction kernels
 // y[r, :] = bf16(x[r, :] * c[r / rows_per_sample] * scale)
 int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, int64_t rows, int64_t cols,

@@ -53,6 +53,8 @@ def create_or_accumulate_grad_sample(*, param: torch.Tensor, grad_sample: torch.
         cur = torch.zeros((max_batch_len,) + tuple(grad_sample.shape[1:]), device=grad_sample.device,
                           dtype=grad_sample.dtype)
         param._current_grad_sample = cur
+    if hasattr(cur, "_dp_norm_sq"):
+        del cur._dp_norm_sq          # a norm computed for the first contribution no longer holds
     cur[:n] += grad_sample
 
 

@@ -73,7 +73,21 @@ def _tensor_core_ok(*ts) -> bool:
 
 # ----------------------------------------------------------------------- Linear
 def linear_grad_sample(a, g):
-    return _ref.linear_grad_sample(a, g)
+    """``[B, d_out, d_in]`` per-sample gradients (dtype of ``g``) by the batched
+    tensor-core kernel; the squared Frobenius norm of every sample's gradient is
+    produced in the same pass (fp32, before rounding) and travels with the
+    result as ``._dp_norm_sq`` so that clipping does not have to re-read it."""
+    a3, g3 = _bt(a), _bt(g)
+    B, T, d_in = a3.shape
+    d_out = g3.shape[-1]
+    if not (g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0):
+        return _ref.linear_grad_sample(a, g)
+    C = load()
+    out = torch.empty(B, d_out, d_in, dtype=torch.bfloat16, device=g.device)
+    n2 = torch.zeros(B, dtype=torch.float32, device=g.device)
+    C.wgrad_tn_ex(g3.contiguous(), _bf16(a3), out, 0.0, n2, 0, 0, 0)
+    out._dp_norm_sq = n2
+    return out
 
 
 def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0):
@@ -205,6 +219,9 @@ def clip_factor(norm_sq, max_grad_norm: float):
 
 
 def grad_sample_norm_sq(gs):
+    cached = getattr(gs, "_dp_norm_sq", None)
+    if cached is not None and cached.shape[0] == gs.shape[0]:
+        return cached
     return load().row_norm_sq(gs.contiguous())
 
 

@@ -188,3 +188,38 @@ def test_fused_step_noise_level():
     dp.step()
     second = p.detach() - first
     assert abs((first * second).mean().item()) < 5e-3        # fresh noise every step
+
+
+@pytest.mark.parametrize("bm,bn,splits", [(128, 128, 1), (128, 256, 1), (256, 256, 1), (128, 128, 4), (256, 256, 2),
+                                           (0, 0, 0)])
+@pytest.mark.parametrize("K,M,N", [(512, 256, 512), (1000, 520, 264), (4096, 1024, 256)])
+def test_wgrad_tile_shapes_and_split_k(bm, bn, splits, K, M, N):
+    C = ops._cuda.load()
+    torch.manual_seed(0)
+    gs = (torch.randn(K, M, device=_dev()) * 0.1).bfloat16()
+    a = torch.randn(K, N, device=_dev()).bfloat16()
+    want = gs.float().t() @ a.float()
+    if splits > 1 and (K + 63) // 64 < 8 * splits:
+        pytest.skip("contraction too short to split")
+    out = torch.full((M, N), 7.0, device=_dev())
+    C.wgrad_tn_ex(gs, a, out, 0.0, None, bm, bn, splits)
+    assert _rel(out, want) < 6e-3
+    base = torch.randn(M, N, device=_dev())
+    out2 = base.clone()
+    C.wgrad_tn_ex(gs, a, out2, 1.0, None, bm, bn, splits)
+    assert _rel(out2, want + base) < 6e-3
+    ops._cuda.check_status()
+
+
+@pytest.mark.parametrize("B,T,din,dout", [(4, 128, 256, 256), (3, 100, 136, 72), (16, 64, 512, 512)])
+def test_linear_per_sample_grad_with_fused_norm(B, T, din, dout):
+    torch.manual_seed(0)
+    a = torch.randn(B, T, din, device=_dev()).bfloat16()
+    g = (torch.randn(B, T, dout, device=_dev()) * 0.1).bfloat16()
+    gs = ops.linear_grad_sample(a, g)
+    want = torch.bmm(g.float().transpose(1, 2), a.float())
+    assert gs.shape == want.shape and _rel(gs, want) < 8e-3
+    n2 = ops.grad_sample_norm_sq(gs)
+    assert n2 is gs._dp_norm_sq
+    assert _rel(n2, want.pow(2).sum(dim=(1, 2))) < 2e-3
+    ops._cuda.check_status()
