@@ -123,27 +123,35 @@ void wgrad_tn(at::Tensor gs, at::Tensor a, at::Tensor out, double beta) {
 }
 
 // gs [batch, K, M] (or [K, M]), a [batch, K, N] (or [K, N]) bf16; out [batch, M, N]; norm_sq optional fp32 [batch]
-void wgrad_tn_ex(at::Tensor gs, at::Tensor a, at::Tensor out, double beta, c10::optional<at::Tensor> norm_sq,
-                 int64_t force_bm, int64_t force_bn, int64_t force_splits) {
+void wgrad_tn_ex(at::Tensor gs, at::Tensor a, c10::optional<at::Tensor> out_opt, double beta,
+                 c10::optional<at::Tensor> norm_sq, int64_t force_bm, int64_t force_bn, int64_t force_splits) {
   c10::cuda::CUDAGuard guard(gs.device());
   raise_if_failed(gs.get_device());
   need_cuda_contig(gs, "gs");
   need_cuda_contig(a, "a");
-  need_cuda_contig(out, "out");
+  if (out_opt.has_value()) need_cuda_contig(*out_opt, "out");
+  TORCH_CHECK(out_opt.has_value() || norm_sq.has_value(), "nothing to compute: neither out nor norm_sq given");
   TORCH_CHECK(gs.scalar_type() == at::kBFloat16 && a.scalar_type() == at::kBFloat16, "bf16 operands expected");
   TORCH_CHECK(gs.dim() == a.dim() && (gs.dim() == 2 || gs.dim() == 3), "gs and a must both be 2-d or 3-d");
   const int batch = gs.dim() == 3 ? gs.size(0) : 1;
   const int K = gs.size(-2), M = gs.size(-1), N = a.size(-1);
   TORCH_CHECK(a.size(-2) == K && (a.dim() == 2 || a.size(0) == batch), "gs and a disagree on batch / K");
-  TORCH_CHECK(out.numel() == (int64_t)batch * M * N, "out must have batch*M*N elements");
-  TORCH_CHECK(out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16, "out must be fp32 or bf16");
+  void* out_ptr = nullptr;
+  bool out_bf16 = false;
+  if (out_opt.has_value()) {
+    const at::Tensor& out = *out_opt;
+    TORCH_CHECK(out.numel() == (int64_t)batch * M * N, "out must have batch*M*N elements");
+    TORCH_CHECK(out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16, "out must be fp32 or bf16");
+    out_ptr = out.data_ptr();
+    out_bf16 = out.scalar_type() == at::kBFloat16;
+  }
   float* nsq = nullptr;
   if (norm_sq.has_value()) {
     TORCH_CHECK(norm_sq->is_cuda() && norm_sq->scalar_type() == at::kFloat && norm_sq->numel() == batch, "bad norm_sq");
     nsq = norm_sq->data_ptr<float>();
   }
-  check(dpk_wgrad_tn_ex(gs.data_ptr(), a.data_ptr(), K, M, N, batch, out.data_ptr(),
-                        out.scalar_type() == at::kBFloat16, (float)beta, nsq, (int)force_bm, (int)force_bn,
+  check(dpk_wgrad_tn_ex(gs.data_ptr(), a.data_ptr(), K, M, N, batch, out_ptr, out_bf16, (float)beta, nsq,
+                        (int)force_bm, (int)force_bn,
                         (int)force_splits, status_for(gs.get_device()).dev, stream()),
         "wgrad_tn_ex");
 }

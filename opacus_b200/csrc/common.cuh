@@ -237,9 +237,11 @@ __device__ __forceinline__ float2 box_muller(uint32_t a, uint32_t b) {
   const float two_pow_m32 = 2.3283064365386963e-10f;
   float u1 = (static_cast<float>(a) + 0.5f) * two_pow_m32;  // (0, 1)
   float u2 = (static_cast<float>(b) + 0.5f) * two_pow_m32;
-  float r = sqrtf(-2.0f * logf(u1));
+  // -2 ln(u1) = -(2 ln 2) log2(u1); the hardware log2 has an absolute error near 2^-22, which moves a
+  // sample by at most ~1e-3 standard deviations and only for the ~1e-6 of samples with u1 within 1e-6 of 1
+  float r = sqrtf(-1.3862943611198906f * __log2f(u1));
   float s, c;
-  sincosf(6.283185307179586f * u2, &s, &c);
+  sincospif(2.0f * u2, &s, &c);
   return make_float2(r * c, r * s);
 }
 

@@ -285,6 +285,11 @@ fused_dp_step_kernel(const DpkTensorEntry* table, int n_tensors, const int64_t* 
   float* pf = reinterpret_cast<float*>(e.param);
   __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(e.param);
 
+  // 16-byte accesses whenever every array of this tensor is 16-byte aligned (the usual case)
+  const bool vec = (((reinterpret_cast<uintptr_t>(e.grad) | reinterpret_cast<uintptr_t>(e.state0) |
+                      reinterpret_cast<uintptr_t>(e.state1) | reinterpret_cast<uintptr_t>(e.master)) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(e.param) & (e.param_bf16 ? 7 : 15)) == 0);
+  const bool use_m = h.kind != 0 || h.momentum != 0.f;
   for (int64_t i0 = start + 4 * (int64_t)threadIdx.x; i0 < end; i0 += 4 * kStepThreads) {
     float z[4] = {0.f, 0.f, 0.f, 0.f};
     if (h.noise_std != 0.f) {
@@ -292,18 +297,53 @@ fused_dp_step_kernel(const DpkTensorEntry* table, int n_tensors, const int64_t* 
       const float2 n01 = box_muller(u.x, u.y), n23 = box_muller(u.z, u.w);
       z[0] = n01.x * h.noise_std; z[1] = n01.y * h.noise_std; z[2] = n23.x * h.noise_std; z[3] = n23.y * h.noise_std;
     }
+    const bool full = vec && i0 + 4 <= end;
+    float g[4], w[4], m[4] = {0, 0, 0, 0}, v[4] = {0, 0, 0, 0};
+    if (full) {
+      const float4 gv = *reinterpret_cast<const float4*>(e.grad + i0);
+      g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+      if (e.master) {
+        const float4 t = *reinterpret_cast<const float4*>(e.master + i0);
+        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+      } else if (e.param_bf16) {
+        const uint2 t = *reinterpret_cast<const uint2*>(pb + i0);
+        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        w[0] = __bfloat162float(lo2.x); w[1] = __bfloat162float(lo2.y);
+        w[2] = __bfloat162float(hi2.x); w[3] = __bfloat162float(hi2.y);
+      } else {
+        const float4 t = *reinterpret_cast<const float4*>(pf + i0);
+        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+      }
+      if (use_m && !(h.kind == 0 && h.first_step)) {
+        const float4 t = *reinterpret_cast<const float4*>(e.state0 + i0);
+        m[0] = t.x; m[1] = t.y; m[2] = t.z; m[3] = t.w;
+      }
+      if (h.kind != 0) {
+        const float4 t = *reinterpret_cast<const float4*>(e.state1 + i0);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t i = i0 + q;
+        if (i >= end) { g[q] = 0.f; w[q] = 0.f; continue; }
+        g[q] = e.grad[i];
+        w[q] = e.master ? e.master[i] : (e.param_bf16 ? __bfloat162float(pb[i]) : pf[i]);
+        if (use_m && !(h.kind == 0 && h.first_step)) m[q] = e.state0[i];
+        if (h.kind != 0) v[q] = e.state1[i];
+      }
+    }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int64_t i = i0 + q;
-      if (i >= end) break;
-      float grad = (e.grad[i] + z[q]) * h.inv_scale;
-      e.grad[i] = grad;
-      float pv = e.master ? e.master[i] : (e.param_bf16 ? __bfloat162float(pb[i]) : pf[i]);
+      float grad = (g[q] + z[q]) * h.inv_scale;
+      g[q] = grad;
+      float pv = w[q];
       if (h.kind == 0) {
         if (h.weight_decay != 0.f) grad = fmaf(h.weight_decay, pv, grad);
         if (h.momentum != 0.f) {
-          float buf = h.first_step ? grad : fmaf(h.momentum, e.state0[i], (1.f - h.dampening) * grad);
-          e.state0[i] = buf;
+          const float buf = h.first_step ? grad : fmaf(h.momentum, m[q], (1.f - h.dampening) * grad);
+          m[q] = buf;
           grad = h.nesterov ? fmaf(h.momentum, buf, grad) : buf;
         }
         pv = fmaf(-h.lr, grad, pv);
@@ -312,15 +352,37 @@ fused_dp_step_kernel(const DpkTensorEntry* table, int n_tensors, const int64_t* 
           if (h.kind == 2) pv *= (1.f - h.lr * h.weight_decay);
           else grad = fmaf(h.weight_decay, pv, grad);
         }
-        const float m = fmaf(h.beta1, e.state0[i], (1.f - h.beta1) * grad);
-        const float v = fmaf(h.beta2, e.state1[i], (1.f - h.beta2) * grad * grad);
-        e.state0[i] = m;
-        e.state1[i] = v;
-        const float denom = sqrtf(v) / h.bias_c2_sqrt + h.eps;
-        pv -= (h.lr / h.bias_c1) * (m / denom);
+        m[q] = fmaf(h.beta1, m[q], (1.f - h.beta1) * grad);
+        v[q] = fmaf(h.beta2, v[q], (1.f - h.beta2) * grad * grad);
+        pv -= (h.lr / h.bias_c1) * (m[q] / (sqrtf(v[q]) / h.bias_c2_sqrt + h.eps));
       }
-      if (e.master) e.master[i] = pv;
-      if (e.param_bf16) pb[i] = __float2bfloat16_rn(pv); else pf[i] = pv;
+      w[q] = pv;
+    }
+    if (full) {
+      *reinterpret_cast<float4*>(e.grad + i0) = make_float4(g[0], g[1], g[2], g[3]);
+      if (use_m) *reinterpret_cast<float4*>(e.state0 + i0) = make_float4(m[0], m[1], m[2], m[3]);
+      if (h.kind != 0) *reinterpret_cast<float4*>(e.state1 + i0) = make_float4(v[0], v[1], v[2], v[3]);
+      if (e.master) *reinterpret_cast<float4*>(e.master + i0) = make_float4(w[0], w[1], w[2], w[3]);
+      if (e.param_bf16) {
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(w[0], w[1]), hi2 = __floats2bfloat162_rn(w[2], w[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<uint32_t*>(&lo2);
+        t.y = *reinterpret_cast<uint32_t*>(&hi2);
+        *reinterpret_cast<uint2*>(pb + i0) = t;
+      } else {
+        *reinterpret_cast<float4*>(pf + i0) = make_float4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t i = i0 + q;
+        if (i >= end) break;
+        e.grad[i] = g[q];
+        if (use_m) e.state0[i] = m[q];
+        if (h.kind != 0) e.state1[i] = v[q];
+        if (e.master) e.master[i] = w[q];
+        if (e.param_bf16) pb[i] = __float2bfloat16_rn(w[q]); else pf[i] = w[q];
+      }
     }
   }
 }

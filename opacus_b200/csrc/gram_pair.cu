@@ -317,8 +317,14 @@ int dpk_gram_pair_launch(const void* x, const int64_t* ids, const void* g, int B
   }
   const size_t smem = 1024 + kStages * kStageBytes + sizeof(GramBarriers);
   {
-    cudaError_t e = cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    static bool attr_done[64] = {false};   // per device; the attribute only has to be set once
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
   }
   const int grid = p.items < num_sms() ? p.items : num_sms();
   gram_pair_kernel<<<grid, kThreads, smem, stream>>>(map_x, map_g, p);

@@ -213,7 +213,10 @@ wgrad_tn_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
           const int col = w.n0 + c0;
-          if (row < p.M && col < p.N) {
+          if (p.out == nullptr) {          // norm only: rows/columns outside the matrix are exact zeros
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sq = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), sq);
+          } else if (row < p.M && col < p.N) {
             if (p.out_bf16) {
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_base + (int64_t)row * p.N + col;
 #pragma unroll
@@ -241,8 +244,12 @@ wgrad_tn_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
               float* o = reinterpret_cast<float*>(p.out) + out_base + (int64_t)row * p.N + col;
               if (p.atomic_out) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col + j < p.N) atomicAdd(o + j, __uint_as_float(r[j]));
+                for (int j = 0; j < 32; j += 4)
+                  if (col + j < p.N)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j),
+                                 "f"(__uint_as_float(r[j])), "f"(__uint_as_float(r[j + 1])),
+                                 "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3]))
+                                 : "memory");
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -302,8 +309,17 @@ int launch_wgrad(const void* gs, const void* a, int K, int M, int N, int batch, 
   rc = make_tmap_3d_bf16(&map_a, a, N, K, batch, WG_BOX, WG_BK);
   if (rc) return rc;
   const size_t smem = 1024 + Cfg::kStages * Cfg::kStageBytes + sizeof(WgBarriers<Cfg::kStages>);
-  cudaError_t e = cudaFuncSetAttribute(wgrad_tn_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
+  {
+    static bool attr_done[64] = {false};   // per device and per tile shape (this function is a template)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+      e = cudaFuncSetAttribute(wgrad_tn_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+  }
   if (p.atomic_out && beta == 0.f) {
     e = cudaMemsetAsync(out, 0, sizeof(float) * (size_t)M * N * batch, stream);
     if (e != cudaSuccess) return e;
@@ -320,7 +336,7 @@ int wgrad_dispatch(const void* gs, const void* a, int K, int M, int N, int batch
   if (K <= 0 || M <= 0 || N <= 0 || batch <= 0 || (M % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
   const int sms = num_sms();
   const int kblocks = (K + WG_BK - 1) / WG_BK;
-  const bool may_split = batch == 1 && norm_sq == nullptr && !out_bf16 && (beta == 0.f || beta == 1.f);
+  const bool may_split = batch == 1 && norm_sq == nullptr && out != nullptr && !out_bf16 && (beta == 0.f || beta == 1.f);
   struct Cand { int bm, bn; double w; };
   const Cand cands[3] = {{256, 256, 1.0}, {128, 256, 0.8}, {128, 128, 0.62}};
   int best_bm = 128, best_bn = 128, best_s = 1;
@@ -335,7 +351,7 @@ int wgrad_dispatch(const void* gs, const void* a, int K, int M, int N, int batch
       const long items = tiles * s;
       const long waves = (items + sms - 1) / sms;
       double score = c.w * (double)items / (double)(waves * sms);
-      for (int q = s; q > 1; q >>= 1) score *= 0.96;
+      for (int q = s; q > 1; q >>= 1) score *= 0.85;   // atomics and the zero-fill are not free
       if (score > best) { best = score; best_bm = c.bm; best_bn = c.bn; best_s = s; }
     }
   }

@@ -41,8 +41,11 @@ def compute_embeddingbag_gradsampler(layer, inputs, backprops):
 
 
 @register_norm_sq_sampler(nn.Embedding)
-def compute_embedding_norm_sq(layer, activations, backprops, g_scale: float = 1.0):
+def compute_embedding_norm_sq(layer, activations, backprops, g_scale: float = 1.0, total=None):
     if not layer.weight.requires_grad:
+        return {}
+    if total is not None:
+        ops.embedding_norm_sq(activations[0], backprops, g_scale, total=total)
         return {}
     return {layer.weight: ops.embedding_norm_sq(activations[0], backprops, g_scale)}
 

@@ -253,7 +253,18 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         if n == 0:
             norm_sq = {}
         elif self.use_ghost_clipping and not self.force_functorch and mtype in self.NORM_SQ_SAMPLERS:
-            norm_sq = self.NORM_SQ_SAMPLERS[mtype](module, activations, backprops, g_scale)
+            fn = self.NORM_SQ_SAMPLERS[mtype]
+            if backprops.shape[0] == self._batch_len and getattr(fn, "_accepts_total", None) is not False:
+                # built-in rules add straight into the running [B] buffer inside their kernel
+                if self._norm_sq_total is None:
+                    self._norm_sq_total = torch.zeros(self._batch_len, dtype=torch.float32, device=backprops.device)
+                try:
+                    norm_sq = fn(module, activations, backprops, g_scale, total=self._norm_sq_total)
+                except TypeError:
+                    fn._accepts_total = False
+                    norm_sq = fn(module, activations, backprops, g_scale)
+            else:
+                norm_sq = fn(module, activations, backprops, g_scale)
         elif self.use_ghost_clipping and mtype in self.NORM_SAMPLERS:
             scaled = backprops * g_scale if g_scale != 1.0 else backprops
             norm_sq = {p: v.float().square() for p, v in self.NORM_SAMPLERS[mtype](module, activations, scaled).items()}

@@ -33,8 +33,14 @@ def compute_linear_grad_sample(layer: nn.Linear, activations: List[torch.Tensor]
 
 
 @register_norm_sq_sampler(nn.Linear)
-def compute_linear_norm_sq(layer, activations, backprops, g_scale: float = 1.0):
+def compute_linear_norm_sq(layer, activations, backprops, g_scale: float = 1.0, total=None):
+    """``total``: running ``[B]`` sum of squared norms; when given and the
+    parameters are not shared with another layer, contributions are added to it
+    directly and nothing is returned."""
     w, b = _wants(layer)
+    if total is not None:
+        ops.linear_norm_sq(activations[0], backprops, w, b, g_scale, total=total)
+        return {}
     nw, nb = ops.linear_norm_sq(activations[0], backprops, w, b, g_scale)
     out = {}
     if w:

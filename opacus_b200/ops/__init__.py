@@ -46,10 +46,18 @@ def linear_bias_grad_sample(g):
     return _ref.linear_bias_grad_sample(g)
 
 
-def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0):
+def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0, total=None):
+    """``total``: optional fp32 ``[B]`` running sum; when given, the norms are
+    added into it in place (inside the kernel on CUDA) and ``(None, None)`` is returned."""
     if _on_gpu(a, g) and _kernel_dtype(g) and g.shape[0] > 0:
-        return _k().linear_norm_sq(a, g, want_weight, want_bias, g_scale)
-    return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+        return _k().linear_norm_sq(a, g, want_weight, want_bias, g_scale, total=total)
+    w, b = _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+    if total is not None:
+        for t in (w, b):
+            if t is not None:
+                total.add_(t.to(total.dtype))
+        return None, None
+    return w, b
 
 
 def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False, out=None, accumulate=False):
@@ -68,10 +76,14 @@ def embedding_grad_sample(ids, g, num_embeddings):
     return _ref.embedding_grad_sample(ids, g, num_embeddings)
 
 
-def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None):
+def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None, total=None):
     if _on_gpu(g) and _kernel_dtype(g) and g.shape[0] > 0:
-        return _k().embedding_norm_sq(ids, g, g_scale, padding_idx)
-    return _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+        return _k().embedding_norm_sq(ids, g, g_scale, padding_idx, total=total)
+    w = _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+    if total is not None:
+        total.add_(w.to(total.dtype))
+        return None
+    return w
 
 
 def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None,

@@ -90,30 +90,64 @@ def linear_grad_sample(a, g):
     return out
 
 
-def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0):
+def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0, total=None):
+    """``total`` (fp32 ``[B]``): add both norms into it in place and return ``(None, None)``."""
     a3, g3 = _bt(a), _bt(g)
     B, T, d_in = a3.shape
     d_out = g3.shape[-1]
     s2 = float(g_scale) ** 2
     C = load()
+    acc = total is not None
+
+    def outs():
+        if acc:
+            return (total if want_weight else None), (total if want_bias else None)
+        return (torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None,
+                torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None)
+
+    def done(w, b):
+        return (None, None) if acc else (w, b)
+
     if T == 1:
         dt = g3.dtype
         a2 = a3.reshape(B, d_in).to(dt).contiguous()
         g2 = g3.reshape(B, d_out).contiguous()
-        w = torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None
-        b = torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None
-        C.outer_norm_sq(a2 if want_weight else None, g2, s2, w, b, False)
-        return w, b
+        w, b = outs()
+        C.outer_norm_sq(a2 if want_weight else None, g2, s2, w, b, acc)
+        return done(w, b)
+    tensor_core = g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0
     gram_cheaper = T * (d_in + d_out) <= 2 * d_in * d_out  # symmetric tiles halve the Gram cost
-    if g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0 and (gram_cheaper or not want_weight):
+    if tensor_core and (gram_cheaper or not want_weight):
         gb = g3.contiguous()
         ab = _bf16(a3) if want_weight else None
-        w = torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None
-        b = torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None
+        w, b = outs()
         scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
-        C.gram_pair_norm(ab, None, gb, s2, scratch, w, b, False)
+        C.gram_pair_norm(ab, None, gb, s2, scratch, w, b, acc)
+        return done(w, b)
+    if tensor_core:
+        # wide layer, short sequence: form each sample's gradient tile by tile in TMEM and only keep its norm
+        gb = g3.contiguous()
+        n2 = torch.zeros(B, dtype=torch.float32, device=g.device)
+        C.wgrad_tn_ex(gb, _bf16(a3), None, 0.0, n2, 0, 0, 0)
+        w = n2 * s2 if s2 != 1.0 else n2
+        b = None
+        if want_bias:
+            b = torch.empty(B, dtype=torch.float32, device=g.device)
+            scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
+            C.gram_pair_norm(None, None, gb, s2, scratch, None, b, False)
+        if acc:
+            total.add_(w)
+            if b is not None:
+                total.add_(b)
+            return None, None
         return w, b
-    return _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+    w, b = _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
+    if acc:
+        for t in (w, b):
+            if t is not None:
+                total.add_(t)
+        return None, None
+    return w, b
 
 
 def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False, out=None, accumulate=False):
@@ -156,18 +190,23 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
 
 
 # -------------------------------------------------------------------- Embedding
-def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None):
+def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] = None, total=None):
     B = ids.shape[0]
     ids2 = ids.reshape(B, -1)
     T = ids2.shape[1]
     g3 = g.reshape(B, T, -1)
     if padding_idx is not None or g3.dtype != torch.bfloat16 or g3.shape[-1] % 8:
-        return _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+        w = _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
+        if total is not None:
+            total.add_(w)
+            return None
+        return w
     C = load()
-    w = torch.empty(B, dtype=torch.float32, device=g.device)
+    w = total if total is not None else torch.empty(B, dtype=torch.float32, device=g.device)
     scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
-    C.gram_pair_norm(None, ids2.contiguous().long(), g3.contiguous(), float(g_scale) ** 2, scratch, w, None, False)
-    return w
+    C.gram_pair_norm(None, ids2.contiguous().long(), g3.contiguous(), float(g_scale) ** 2, scratch, w, None,
+                     total is not None)
+    return None if total is not None else w
 
 
 def embedding_weighted_grad(ids, g, c, num_embeddings, g_scale: float = 1.0, padding_idx=None, out_dtype=None,
