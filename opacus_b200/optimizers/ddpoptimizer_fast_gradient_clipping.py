@@ -16,12 +16,15 @@ class DistributedDPOptimizerFastGradientClipping(DPOptimizerFastGradientClipping
 
     def __init__(self, optimizer: Optimizer, *, noise_multiplier: float, max_grad_norm: float,
                  expected_batch_size: Optional[int], loss_reduction: str = "mean", generator=None,
-                 secure_mode: bool = False, **kwargs):
+                 secure_mode: bool = False, engine=None, **kwargs):
         super().__init__(optimizer, noise_multiplier=noise_multiplier, max_grad_norm=max_grad_norm,
                          expected_batch_size=expected_batch_size, loss_reduction=loss_reduction,
                          generator=generator, secure_mode=secure_mode, **kwargs)
         self.rank = torch.distributed.get_rank()
         self.world_size = torch.distributed.get_world_size()
+        # With a ShardedDataParallel engine the all-reduce, the single noise draw and the update
+        # run as one kernel over peer memory instead of NCCL + per-parameter kernels.
+        self.engine = engine
 
     def add_noise(self):
         if self.rank == 0:
@@ -38,7 +41,23 @@ class DistributedDPOptimizerFastGradientClipping(DPOptimizerFastGradientClipping
         if closure is not None:
             with torch.enable_grad():
                 closure()
+        if self.engine is not None:
+            return self._engine_step()
         if self.pre_step():
             self.reduce_gradients()
             return self.original_optimizer.step()
         return None
+
+    def _engine_step(self):
+        """Hand the clipped sums to the engine's flat gradient buffer and let its
+        fused kernel do reduce + noise + update + publish."""
+        if self._collect():
+            for p in self.params:
+                dst = getattr(p, "_dp_grad_out", None)
+                if dst is None or p.summed_grad is None:
+                    continue
+                if p.summed_grad.data_ptr() != dst.data_ptr():
+                    dst.copy_(p.summed_grad.view_as(dst))
+                    p.summed_grad = dst          # later physical batches accumulate in place
+                p._dp_grad_fresh = False
+        return self.engine.optimizer_step(self)

@@ -185,10 +185,8 @@ class ShardedDataParallel(nn.Module):
                      bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
             kcode = 2 if kind == "adamw" else 1
 
-        if dpopt.loss_reduction == "mean":
-            denom = float(dpopt.expected_batch_size) * self.world
-        else:
-            denom = 1.0
+        # per-worker expected batch (times accumulated batches in hooks mode), summed over the workers
+        denom = float(dpopt._grad_denominator()) * (self.world if dpopt.loss_reduction == "mean" else 1)
         if dpopt.step_hook:
             dpopt.step_hook(dpopt)
         seed, offset = _cuda._rng_state(dpopt.generator, dev, self.total)

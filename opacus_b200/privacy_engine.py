@@ -200,7 +200,7 @@ class PrivacyEngine:
             expected_batch_size /= torch.distributed.get_world_size()
 
         opt_kwargs = dict(kwargs)
-        if engine is not None and grad_sample_mode == "ghost_fsdp":
+        if engine is not None and clipping == "flat":
             opt_kwargs["engine"] = engine
         optimizer = self._prepare_optimizer(
             optimizer=optimizer, noise_multiplier=noise_multiplier, max_grad_norm=max_grad_norm,

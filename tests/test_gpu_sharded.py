@@ -113,3 +113,35 @@ def test_sharded_engine_noise_and_virtual_steps(pg):
     delta = (eng.master - before) / 1e-2 * 4        # = -(sum of clipped grads + noise)
     assert abs(delta.std().item() - 100.0 * 0.5) / 50.0 < 0.05
     assert g1.abs().sum() > 0
+
+
+def test_engine_serves_hooks_mode_data_parallel(pg):
+    """DistributedDPOptimizer on top of the engine (fp32 compute weights) equals the plain DPOptimizer."""
+    import copy
+
+    from opacus_b200 import PrivacyEngine
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.LayerNorm(64), nn.Linear(64, 8)).cuda()
+    twin = copy.deepcopy(base)
+    x = torch.randn(16, 32, device="cuda")
+    y = torch.randint(0, 8, (16,), device="cuda")
+    dl = DataLoader(TensorDataset(torch.zeros(64, 1)), batch_size=16)
+
+    eng = ShardedDataParallel(base, param_dtype=torch.float32)
+    m1, o1, _ = PrivacyEngine(accountant="rdp").make_private(
+        module=eng, optimizer=torch.optim.SGD(base.parameters(), lr=0.1, momentum=0.9), data_loader=dl,
+        noise_multiplier=0.0, max_grad_norm=0.3, poisson_sampling=False)
+    m2, o2, _ = PrivacyEngine(accountant="rdp").make_private(
+        module=twin, optimizer=torch.optim.SGD(twin.parameters(), lr=0.1, momentum=0.9), data_loader=dl,
+        noise_multiplier=0.0, max_grad_norm=0.3, poisson_sampling=False)
+    assert type(o1).__name__ == "DistributedDPOptimizer" and o1.engine is eng
+    for _ in range(3):
+        for m, o in ((m1, o1), (m2, o2)):
+            o.zero_grad()
+            nn.functional.cross_entropy(m(x), y).backward()
+            o.step()
+    torch.cuda.synchronize()
+    for a, b in zip(base.parameters(), twin.parameters()):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), (a - b).abs().max()
