@@ -254,7 +254,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             norm_sq = {}
         elif self.use_ghost_clipping and not self.force_functorch and mtype in self.NORM_SQ_SAMPLERS:
             fn = self.NORM_SQ_SAMPLERS[mtype]
-            if backprops.shape[0] == self._batch_len and getattr(fn, "_accepts_total", None) is not False:
+            if (self._use_total_fastpath and backprops.shape[0] == self._batch_len
+                    and getattr(fn, "_accepts_total", None) is not False):
                 # built-in rules add straight into the running [B] buffer inside their kernel
                 if self._norm_sq_total is None:
                     self._norm_sq_total = torch.zeros(self._batch_len, dtype=torch.float32, device=backprops.device)
@@ -282,13 +283,21 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             v = v.float()
             if v.shape[0] < (self._batch_len or 0):  # short step of a packed sequence
                 v = torch.cat([v, v.new_zeros(self._batch_len - v.shape[0])])
-            self._norm_sq_total = v.clone() if self._norm_sq_total is None else self._norm_sq_total.add_(
-                v.to(self._norm_sq_total.device))
+            self._add_norm_sq(p, v)
         for _, p in trainable_parameters(module):
             self._uses.setdefault(p, []).append(site)
             p._forward_counter -= uses
         if len(module.activations) == 0 and hasattr(module, "max_batch_len"):
             del module.max_batch_len
+
+    # Built-in rules may add their norms straight into ``_norm_sq_total`` inside the
+    # kernel; subclasses that need to tell parameters apart switch this off.
+    _use_total_fastpath = True
+
+    def _add_norm_sq(self, p, v):
+        """Account the squared per-sample norm ``v`` of parameter ``p``."""
+        self._norm_sq_total = v.clone() if self._norm_sq_total is None else self._norm_sq_total.add_(
+            v.to(self._norm_sq_total.device))
 
     def _add_cross_terms(self):
         """``||sum_i g_i||^2 = sum_i ||g_i||^2 + 2 sum_{i<j} <g_i, g_j>`` for a

@@ -69,10 +69,36 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
                 else:
                     p.merge_flag = True
 
+    # ---- single-pass bookkeeping: sharded and replicated parameters are kept apart
+    _use_total_fastpath = False
+
+    def _reset_single_pass_state(self):
+        super()._reset_single_pass_state()
+        self._norm_sq_replicated = None
+
+    def _add_norm_sq(self, p, v):
+        if getattr(p, "merge_flag", False):
+            super()._add_norm_sq(p, v)
+        else:
+            self._norm_sq_replicated = v.clone() if self._norm_sq_replicated is None else \
+                self._norm_sq_replicated.add_(v)
+
+    def _single_pass_norm_sq(self) -> torch.Tensor:
+        ref = self._norm_sq_total if self._norm_sq_total is not None else self._norm_sq_replicated
+        sharded = self._norm_sq_total.clone() if self._norm_sq_total is not None else torch.zeros_like(ref)
+        torch.distributed.all_reduce(sharded, op=torch.distributed.ReduceOp.SUM, group=self.process_group)
+        if self._norm_sq_replicated is not None:
+            sharded = sharded + self._norm_sq_replicated
+        return sharded
+
     def _group_rank(self) -> int:
         return torch.distributed.get_rank(self.process_group)
 
     def get_norm_sample(self) -> torch.Tensor:
+        if self.single_pass and (self._norm_sq_total is not None or self._norm_sq_replicated is not None):
+            norm = self._single_pass_norm_sq().clamp(min=0).sqrt()
+            self.per_sample_gradient_norms = norm
+            return norm
         first = self._group_rank() == 0
         sq = None
         for p in self.trainable_parameters:
@@ -95,9 +121,10 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
 
 class GradSampleModuleFastGradientClippingTP(GradSampleHooksFastGradientClippingTP, AbstractGradSampleModule):
     def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
-                 force_functorch=False, max_grad_norm=1, process_group=None):
+                 force_functorch=False, max_grad_norm=1, process_group=None, single_pass: bool = False):
         nn.Module.__init__(self)
         GradSampleHooksFastGradientClippingTP.__init__(
             self, m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
-            force_functorch=force_functorch, max_grad_norm=max_grad_norm, process_group=process_group)
+            force_functorch=force_functorch, max_grad_norm=max_grad_norm, process_group=process_group,
+            single_pass=single_pass)
         self.grad_accumulation_hook = None

@@ -108,8 +108,19 @@ def norm_affine_grad_sample(kind, x, g, *, eps, normalized_ndim=1, num_groups=1,
     *input* ``x``: the normalised activation is recomputed inside the kernel, in
     one pass over ``x`` and ``g``.  ``kind`` is ``"layer"``, ``"rms"``,
     ``"group"`` or ``"instance"``."""
-    if _on_gpu(x, g) and _kernel_dtype(g) and g.shape[0] > 0 and _k().supports_norm(kind, x, normalized_ndim):
-        return _k().norm_affine_grad_sample(kind, x, g, eps, normalized_ndim, num_groups, want_weight, want_bias)
+    if _on_gpu(x, g) and _kernel_dtype(g) and g.shape[0] > 0:
+        if kind in ("layer", "rms") and normalized_ndim > 1 and x.dim() > normalized_ndim:
+            # normalising over the last k axes = normalising over one flattened axis
+            lead = x.shape[: x.dim() - normalized_ndim]
+            tail = x.shape[x.dim() - normalized_ndim:]
+            if len(lead) == 1:
+                lead = (lead[0], 1)
+            xf, gf = x.reshape(*lead, -1), g.reshape(*lead, -1)
+            gw, gb = _k().norm_affine_grad_sample(kind, xf, gf, eps, 1, num_groups, want_weight, want_bias)
+            shape = (x.shape[0],) + tuple(tail)
+            return (gw.reshape(shape) if gw is not None else None), (gb.reshape(shape) if gb is not None else None)
+        if _k().supports_norm(kind, x, normalized_ndim):
+            return _k().norm_affine_grad_sample(kind, x, g, eps, normalized_ndim, num_groups, want_weight, want_bias)
     import torch.nn.functional as F
 
     if kind == "layer":

@@ -38,7 +38,13 @@ def get_optimizer_class(clipping: str, distributed: bool, grad_sample_mode: str 
             return _GHOST[key]
         raise ValueError(
             f"Unsupported combination of parameters. Clipping: {clipping} and grad_sample_mode: {grad_sample_mode}")
-    if grad_sample_mode in ("ghost_fsdp", "ghost_tp"):
+    if grad_sample_mode == "ghost_tp":
+        if clipping == "flat":
+            from ..parallel.tensor_parallel import TensorParallelDPOptimizer
+
+            return TensorParallelDPOptimizer
+        raise ValueError(f"Unsupported combination of parameters. Clipping: {clipping} and grad_sample_mode: ghost_tp")
+    if grad_sample_mode == "ghost_fsdp":
         if key == ("flat", True):
             return FSDPOptimizerFastGradientClipping
         raise ValueError(

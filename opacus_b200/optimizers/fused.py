@@ -34,7 +34,9 @@ class _FusedPlan:
             k.fused_dp_step(self.kind, inner, group, ps, noise_std=noise_std, inv_scale=1.0 / denominator,
                             generator=gen)
             for p in ps:
-                p.grad = p.summed_grad.view_as(p)
+                g = p.summed_grad.view_as(p)
+                # the private gradient is kept in fp32; a low-precision parameter gets a rounded view of it
+                p.grad = g if g.dtype == p.dtype else g.to(p.dtype)
 
 
 def plan_for(opt) -> Optional[_FusedPlan]:

@@ -1,0 +1,222 @@
+"""Host-side logic of the multi-process paths on CPU (gloo, 2 ranks): data-parallel
+DP optimizers against a single-process run, tensor-parallel ghost clipping against
+the unsharded model, the distributed Poisson sampler, and failure detection by a
+short process-group timeout when a rank never joins a collective."""
+import datetime
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn as nn
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, fn, out_dir, timeout_s):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+    try:
+        result = fn(rank, world)
+        torch.save(result, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn, world=2, timeout_s=60):
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_worker, args=(world, _free_port(), fn, out_dir, timeout_s), nprocs=world, join=True)
+    return [torch.load(os.path.join(out_dir, f"r{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def _mlp():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(12, 16), nn.Tanh(), nn.LayerNorm(16), nn.Linear(16, 4))
+
+
+def _data():
+    g = torch.Generator().manual_seed(1)
+    return torch.randn(8, 12, generator=g), torch.randint(0, 4, (8,), generator=g)
+
+
+class _DDPJob:
+    def __init__(self, mode):
+        self.mode = mode
+
+    def __call__(self, rank, world):
+        mode = self.mode
+        from torch.utils.data import DataLoader, TensorDataset
+
+        from opacus_b200 import PrivacyEngine
+        from opacus_b200.distributed import DifferentiallyPrivateDistributedDataParallel as DPDDP
+
+        x, y = _data()
+        model = DPDDP(_mlp())
+        opt = torch.optim.SGD(model.parameters(), lr=0.5)
+        dl = DataLoader(TensorDataset(x, y), batch_size=8)
+        out = PrivacyEngine(accountant="rdp").make_private(
+            module=model, optimizer=opt, data_loader=dl, noise_multiplier=0.0, max_grad_norm=0.2,
+            grad_sample_mode=mode, poisson_sampling=False)
+        m, o = out[0], out[1]
+        crit = out[2] if mode == "ghost" else nn.CrossEntropyLoss()
+        xs, ys = x[rank::world], y[rank::world]
+        for _ in range(2):
+            o.zero_grad()
+            crit(m(xs), ys).backward()
+            o.step()
+        return [p.detach().clone() for p in model.parameters()]
+
+
+@pytest.mark.parametrize("mode", ["hooks", "ghost"])
+def test_ddp_equals_single_process(mode):
+    from torch.utils.data import DataLoader, TensorDataset
+
+    from opacus_b200 import PrivacyEngine
+
+    got = _run(_DDPJob(mode))
+    x, y = _data()
+    model = _mlp()
+    opt = torch.optim.SGD(model.parameters(), lr=0.5)
+    m, o, _ = PrivacyEngine(accountant="rdp").make_private(
+        module=model, optimizer=opt, data_loader=DataLoader(TensorDataset(x, y), batch_size=8),
+        noise_multiplier=0.0, max_grad_norm=0.2, poisson_sampling=False)
+    for _ in range(2):
+        o.zero_grad()
+        nn.functional.cross_entropy(m(x), y).backward()
+        o.step()
+    for r in range(2):
+        for a, b in zip(got[r], model.parameters()):
+            assert torch.allclose(a, b, atol=1e-6), mode
+
+
+class _TPNet(nn.Module):
+    def __init__(self, col, row):
+        super().__init__()
+        self.col, self.row = col, row
+        self.ln = nn.LayerNorm(12)
+
+    def forward(self, x):
+        return self.ln(self.row(torch.tanh(self.col(x))))
+
+
+def _tp_reference():
+    torch.manual_seed(0)
+    return _TPNet(nn.Linear(12, 16), nn.Linear(16, 12))
+
+
+def _tp_job(rank, world):
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClippingTP
+    from opacus_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, TensorParallelDPOptimizer
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    full = _tp_reference()
+    net = _TPNet(ColumnParallelLinear.from_linear(full.col), RowParallelLinear.from_linear(full.row))
+    net.ln.load_state_dict(full.ln.state_dict())
+    x, _ = _data()
+    x = x.reshape(4, 2, 12)
+    results = {}
+    for single_pass in (False, True):
+        import copy
+
+        model = copy.deepcopy(net)
+        for p, q in zip(model.parameters(), net.parameters()):
+            if getattr(q, "tp_sharded", False):
+                p.tp_sharded = True
+        gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=0.1, single_pass=single_pass)
+        opt = TensorParallelDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                        max_grad_norm=0.1, expected_batch_size=4)
+        crit = DPLossFastGradientClipping(gsm, opt, nn.MSELoss(), "mean")
+
+        class PerSample:
+            reduction = "mean"
+
+            def __call__(self, out, tgt):
+                per = (out - tgt).pow(2).flatten(1).mean(1)
+                return per if self.reduction == "none" else per.mean()
+
+        crit.criterion = PerSample()
+        opt.zero_grad()
+        crit(gsm(x), torch.zeros(4, 2, 12)).backward()
+        opt.step()
+        results[single_pass] = ({k: v.detach().clone() for k, v in model.state_dict().items()},
+                                gsm.per_sample_gradient_norms.clone())
+    return results
+
+
+def test_tensor_parallel_ghost_matches_unsharded():
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    got = _run(_tp_job)
+    model = _tp_reference()
+    x, _ = _data()
+    x = x.reshape(4, 2, 12)
+    gsm = GradSampleModuleFastGradientClipping(model, max_grad_norm=0.1, single_pass=True)
+    opt = DPOptimizerFastGradientClipping(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                          max_grad_norm=0.1, expected_batch_size=4)
+
+    class PerSample:
+        reduction = "mean"
+
+        def __call__(self, out, tgt):
+            per = (out - tgt).pow(2).flatten(1).mean(1)
+            return per if self.reduction == "none" else per.mean()
+
+    crit = DPLossFastGradientClipping(gsm, opt, PerSample(), "mean")
+    opt.zero_grad()
+    crit(gsm(x), torch.zeros(4, 2, 12)).backward()
+    norms = gsm.per_sample_gradient_norms.clone()
+    opt.step()
+    want = model.state_dict()
+    for rank in range(2):
+        for single_pass in (False, True):
+            sd, n = got[rank][single_pass]
+            assert torch.allclose(n, norms, rtol=1e-4, atol=1e-6), (rank, single_pass)
+            assert torch.allclose(sd["col.weight"], want["col.weight"].chunk(2, 0)[rank], atol=1e-6)
+            assert torch.allclose(sd["col.bias"], want["col.bias"].chunk(2, 0)[rank], atol=1e-6)
+            assert torch.allclose(sd["row.weight"], want["row.weight"].chunk(2, 1)[rank], atol=1e-6)
+            assert torch.allclose(sd["row.bias"], want["row.bias"], atol=1e-6)
+            assert torch.allclose(sd["ln.weight"], want["ln.weight"], atol=1e-6)
+
+
+def _sampler_job(rank, world):
+    from opacus_b200.utils.uniform_sampler import DistributedUniformWithReplacementSampler
+
+    s = DistributedUniformWithReplacementSampler(total_size=101, sample_rate=1.0, steps=1,
+                                                 generator=torch.Generator().manual_seed(rank))
+    return torch.cat(list(s))
+
+
+def test_distributed_sampler_covers_dataset_once():
+    parts = _run(_sampler_job)
+    assert sorted(torch.cat(parts).tolist()) == list(range(101))
+
+
+def _absent_rank_job(rank, world):
+    """Rank 1 leaves between steps without joining the next collective; rank 0's
+    collective must end with an error (short timeout) instead of hanging."""
+    t = torch.ones(4)
+    dist.all_reduce(t)
+    if rank == 1:
+        return "left"
+    try:
+        dist.all_reduce(t)
+        return "no error"
+    except Exception as e:  # gloo reports the missing peer / timeout
+        return f"error: {type(e).__name__}"
+
+
+def test_missing_rank_is_detected_by_timeout():
+    res = _run(_absent_rank_job, timeout_s=5)
+    assert res[1] == "left" and res[0].startswith("error")
