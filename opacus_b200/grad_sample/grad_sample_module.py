@@ -48,10 +48,17 @@ def create_or_accumulate_grad_sample(*, param: torch.Tensor, grad_sample: torch.
     cur = getattr(param, "_current_grad_sample", None)
     if cur is None:
         if n == max_batch_len:
-            param._current_grad_sample = grad_sample.clone() if grad_sample._base is not None else grad_sample
+            # adopted as is (possibly a view of a tensor the sampler made); copied only if
+            # a second contribution has to be added in place
+            param._current_grad_sample = grad_sample
             return
         cur = torch.zeros((max_batch_len,) + tuple(grad_sample.shape[1:]), device=grad_sample.device,
                           dtype=grad_sample.dtype)
+        cur._dp_owned = True
+        param._current_grad_sample = cur
+    elif not getattr(cur, "_dp_owned", False):
+        cur = cur.clone()
+        cur._dp_owned = True
         param._current_grad_sample = cur
     if hasattr(cur, "_dp_norm_sq"):
         del cur._dp_norm_sq          # a norm computed for the first contribution no longer holds

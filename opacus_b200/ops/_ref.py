@@ -147,7 +147,10 @@ def clip_factor(norm_sq: torch.Tensor, max_grad_norm: float) -> torch.Tensor:
 
 def grad_sample_norm_sq(gs: torch.Tensor) -> torch.Tensor:
     acc = torch.float64 if gs.dtype == torch.float64 else torch.float32
-    return gs.reshape(gs.shape[0], -1).to(acc).pow(2).sum(dim=1)
+    if gs.shape[0] == 0:
+        return torch.zeros(0, dtype=acc, device=gs.device)
+    # no temporary of the size of gs
+    return torch.linalg.vector_norm(gs.reshape(gs.shape[0], -1), dim=1, dtype=acc).square()
 
 
 def weighted_sum(gs: torch.Tensor, c: torch.Tensor) -> torch.Tensor:

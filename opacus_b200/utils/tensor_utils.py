@@ -2,8 +2,8 @@
 convolutions with stride, dilation and ``"same"``/``"valid"`` padding.
 
 Behavioural parity: ``opacus/utils/tensor_utils.py:27-336``.  The unfolds here
-are gather-based (one index per kernel tap and output position along each axis)
-rather than strided views, so they work for any number of spatial axes.
+build sliding windows with ``Tensor.unfold`` along each spatial axis (views) and
+materialise once, so one routine serves any number of spatial axes.
 """
 from typing import Iterator, List, Sequence, Tuple, Union
 
@@ -64,25 +64,22 @@ def unfold_nd(x: torch.Tensor, *, kernel_size: Sequence[int], padding, stride: S
     flat_pad = [v for lr in reversed(pads) for v in lr]
     x = F.pad(x, flat_pad)
     B, C = x.shape[:2]
-    # After indexing axis a (at position 2 + 2a) the tensor gains a [k_a, out_a] pair.
-    for a in range(n):
-        size = x.shape[2 + 2 * a]
-        span = dilation[a] * (kernel_size[a] - 1) + 1
-        n_out = (size - span) // stride[a] + 1
-        taps = torch.arange(kernel_size[a], device=x.device) * dilation[a]
-        starts = torch.arange(max(n_out, 0), device=x.device) * stride[a]
-        idx = (taps[:, None] + starts[None, :]).reshape(-1)
-        x = x.index_select(2 + 2 * a, idx)
-        shape = list(x.shape)
-        shape[2 + 2 * a: 3 + 2 * a] = [kernel_size[a], max(n_out, 0)]
-        x = x.reshape(shape)
-    # [B, C, k0, o0, k1, o1, ...] -> [B, C, k0, k1, ..., o0, o1, ...]
-    order = [0, 1] + [2 + 2 * a for a in range(n)] + [3 + 2 * a for a in range(n)]
-    x = x.permute(order)
     k_total = 1
     for k in kernel_size:
         k_total *= k
-    return x.reshape(B, C * k_total, -1)
+    spans = [dilation[a] * (kernel_size[a] - 1) + 1 for a in range(n)]
+    if any(x.shape[2 + a] < spans[a] for a in range(n)):
+        return x.new_zeros(B, C * k_total, 0)
+    # Sliding windows as strided views (no copy): axis a keeps the output positions,
+    # a new trailing axis holds the (dilated) window, thinned to the kernel taps.
+    for a in range(n):
+        x = x.unfold(2 + a, spans[a], stride[a])
+    for a in range(n):
+        if dilation[a] > 1:
+            x = x.narrow(2 + n + a, 0, spans[a])[(slice(None),) * (2 + n + a) + (slice(None, None, dilation[a]),)]
+    # [B, C, o0, o1, ..., k0, k1, ...] -> [B, C, k0, k1, ..., o0, o1, ...]; the reshape is the one copy
+    order = [0, 1] + [2 + n + a for a in range(n)] + [2 + a for a in range(n)]
+    return x.permute(order).reshape(B, C * k_total, -1)
 
 
 def unfold2d(input, *, kernel_size: Tuple[int, int], padding: Union[str, Tuple[int, int]],
