@@ -38,6 +38,26 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
         if want_b:
             out[layer.bias] = torch.zeros_like(layer.bias).unsqueeze(0)
         return out
+    O = layer.out_channels
+    ck = layer.weight[0].numel() * layer.groups
+    if (x.is_cuda and backprops.dtype == torch.bfloat16 and layer.groups == 1 and O % 8 == 0 and ck % 8 == 0):
+        # tensor-core path: both operands with the output positions (the contraction) outermost
+        cols_t = unfold_nd(x, kernel_size=layer.kernel_size, padding=layer.padding, stride=layer.stride,
+                           dilation=layer.dilation, positions_first=True)            # [n, L, C*k]
+        g_t = backprops.reshape(n, O, -1).transpose(1, 2).contiguous()                # [n, L, O]
+        out = {}
+        if layer.weight.requires_grad:
+            from .. import ops
+
+            gs = ops.linear_grad_sample(cols_t, g_t)                                  # [n, O, C*k] + fused norm
+            norm = getattr(gs, "_dp_norm_sq", None)
+            gs = gs.view((n,) + tuple(layer.weight.shape))
+            if norm is not None:
+                gs._dp_norm_sq = norm
+            out[layer.weight] = gs
+        if want_b:
+            out[layer.bias] = g_t.sum(dim=1)
+        return out
     cols = unfold_nd(x, kernel_size=layer.kernel_size, padding=layer.padding, stride=layer.stride,
                      dilation=layer.dilation)                      # [n, C*k, L]
     L = cols.shape[-1]

@@ -51,12 +51,14 @@ def _pads(padding, kernel, dilation) -> List[Tuple[int, int]]:
 
 
 def unfold_nd(x: torch.Tensor, *, kernel_size: Sequence[int], padding, stride: Sequence[int],
-              dilation: Sequence[int]) -> torch.Tensor:
+              dilation: Sequence[int], positions_first: bool = False) -> torch.Tensor:
     """im2col for ``x`` of shape ``[B, C, *spatial]``.
 
     Returns ``[B, C * prod(kernel), L]`` with ``L`` the number of output
     positions; rows are ordered channel-major then kernel taps (row-major),
-    the layout of ``torch.nn.functional.unfold``.
+    the layout of ``torch.nn.functional.unfold``.  ``positions_first`` returns
+    the transpose ``[B, L, C * prod(kernel)]`` (the layout the batched
+    tensor-core GEMM wants: contraction index outermost) at no extra cost.
     """
     n = len(kernel_size)
     kernel_size, stride, dilation = _tuple(kernel_size, n), _tuple(stride, n), _tuple(dilation, n)
@@ -69,7 +71,7 @@ def unfold_nd(x: torch.Tensor, *, kernel_size: Sequence[int], padding, stride: S
         k_total *= k
     spans = [dilation[a] * (kernel_size[a] - 1) + 1 for a in range(n)]
     if any(x.shape[2 + a] < spans[a] for a in range(n)):
-        return x.new_zeros(B, C * k_total, 0)
+        return x.new_zeros(B, 0, C * k_total) if positions_first else x.new_zeros(B, C * k_total, 0)
     # Sliding windows as strided views (no copy): axis a keeps the output positions,
     # a new trailing axis holds the (dilated) window, thinned to the kernel taps.
     for a in range(n):
@@ -78,6 +80,9 @@ def unfold_nd(x: torch.Tensor, *, kernel_size: Sequence[int], padding, stride: S
         if dilation[a] > 1:
             x = x.narrow(2 + n + a, 0, spans[a])[(slice(None),) * (2 + n + a) + (slice(None, None, dilation[a]),)]
     # [B, C, o0, o1, ..., k0, k1, ...] -> [B, C, k0, k1, ..., o0, o1, ...]; the reshape is the one copy
+    if positions_first:
+        order = [0] + [2 + a for a in range(n)] + [1] + [2 + n + a for a in range(n)]
+        return x.permute(order).reshape(B, -1, C * k_total)
     order = [0, 1] + [2 + n + a for a in range(n)] + [2 + a for a in range(n)]
     return x.permute(order).reshape(B, C * k_total, -1)
 

@@ -223,3 +223,26 @@ def test_linear_per_sample_grad_with_fused_norm(B, T, din, dout):
     assert n2 is gs._dp_norm_sq
     assert _rel(n2, want.pow(2).sum(dim=(1, 2))) < 2e-3
     ops._cuda.check_status()
+
+
+def test_conv_per_sample_grad_tensor_core_path():
+    import torch.nn as nn
+
+    from opacus_b200.grad_sample.conv import compute_conv_grad_sample
+
+    torch.manual_seed(0)
+    conv = nn.Conv2d(16, 32, 3, stride=2, padding=1).to(_dev()).bfloat16()
+    x = torch.randn(6, 16, 15, 14, device=_dev()).bfloat16()
+    y = conv(x)
+    g = (torch.randn_like(y) * 0.1)
+    got = compute_conv_grad_sample(conv, [x], g)
+    conv32 = nn.Conv2d(16, 32, 3, stride=2, padding=1).to(_dev())
+    want_w = []
+    for i in range(6):
+        w = torch.nn.grad.conv2d_weight(x[i:i + 1].float(), conv32.weight.shape, g[i:i + 1].float(), stride=2, padding=1)
+        want_w.append(w)
+    want_w = torch.stack(want_w)
+    gw = got[conv.weight]
+    assert gw.shape == want_w.shape and _rel(gw, want_w) < 1e-2
+    assert _rel(ops.grad_sample_norm_sq(gw), want_w.pow(2).sum(dim=(1, 2, 3, 4))) < 5e-3
+    assert _rel(got[conv.bias], g.float().sum(dim=(2, 3))) < 1e-2
