@@ -31,6 +31,14 @@ int dpk_wgrad_tn_ex(const void* gs, const void* a, int K, int M, int N, int batc
                     float beta, float* norm_sq, int force_bm, int force_bn, int force_splits, uint32_t* status,
                     cudaStream_t stream);
 
+// Per-sample (or batch-summed) weight gradient of a 1-d/2-d convolution from channels-last operands, without an
+// unfolded input: x [B, H, W, C] bf16, g [B, OH, OW, O] bf16 -> out [B, O, kh, kw, C] (reduce_batch: [O, kh, kw, C],
+// fp32, beta in {0, 1}); norm_sq (or NULL) receives += ||out[b]||_F^2; out == NULL computes the norms only.
+// C and O must be multiples of 8.
+int dpk_conv_psg(const void* x, const void* g, int B, int C, int H, int W, int O, int OH, int OW, int kh, int kw,
+                 int sh, int sw, int ph, int pw, int dh, int dw, int reduce_batch, void* out, int out_bf16,
+                 float beta, float* norm_sq, uint32_t* status, cudaStream_t stream);
+
 // ---- elementwise / reduction kernels
 // y[r, :] = bf16(x[r, :] * c[r / rows_per_sample] * scale)
 int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, int64_t rows, int64_t cols,

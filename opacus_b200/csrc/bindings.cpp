@@ -156,6 +156,43 @@ void wgrad_tn_ex(at::Tensor gs, at::Tensor a, c10::optional<at::Tensor> out_opt,
         "wgrad_tn_ex");
 }
 
+// x [B, H, W, C], g [B, OH, OW, O] bf16 contiguous (channels-last images); conv = {kh, kw, sh, sw, ph, pw, dh, dw};
+// out [B, O, kh, kw, C] (or [O, kh, kw, C] fp32 when reduce_batch); norm_sq optional fp32 [B]
+void conv_psg(at::Tensor x, at::Tensor g, std::vector<int64_t> conv, bool reduce_batch,
+              c10::optional<at::Tensor> out_opt, double beta, c10::optional<at::Tensor> norm_sq) {
+  c10::cuda::CUDAGuard guard(x.device());
+  raise_if_failed(x.get_device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(g, "g");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16, "bf16 operands expected");
+  TORCH_CHECK(x.dim() == 4 && g.dim() == 4 && x.size(0) == g.size(0), "x [B,H,W,C] and g [B,OH,OW,O] expected");
+  TORCH_CHECK(conv.size() == 8, "conv = {kh, kw, sh, sw, ph, pw, dh, dw}");
+  TORCH_CHECK(out_opt.has_value() || norm_sq.has_value(), "nothing to compute: neither out nor norm_sq given");
+  const int B = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);
+  const int OH = g.size(1), OW = g.size(2), O = g.size(3);
+  const int kh = conv[0], kw = conv[1], sh = conv[2], sw = conv[3], ph = conv[4], pw = conv[5], dh = conv[6], dw = conv[7];
+  TORCH_CHECK((OH - 1) * sh + (kh - 1) * dh - ph < H + ph && (OW - 1) * sw + (kw - 1) * dw - pw < W + pw,
+              "output size does not fit the input for this convolution");
+  void* out_ptr = nullptr;
+  bool out_bf16 = false;
+  if (out_opt.has_value()) {
+    const at::Tensor& out = *out_opt;
+    need_cuda_contig(out, "out");
+    TORCH_CHECK(out.numel() == (int64_t)(reduce_batch ? 1 : B) * O * kh * kw * C, "out has the wrong number of elements");
+    TORCH_CHECK(out.scalar_type() == at::kFloat || out.scalar_type() == at::kBFloat16, "out must be fp32 or bf16");
+    out_ptr = out.data_ptr();
+    out_bf16 = out.scalar_type() == at::kBFloat16;
+  }
+  float* nsq = nullptr;
+  if (norm_sq.has_value()) {
+    TORCH_CHECK(norm_sq->is_cuda() && norm_sq->scalar_type() == at::kFloat && norm_sq->numel() == B, "bad norm_sq");
+    nsq = norm_sq->data_ptr<float>();
+  }
+  check(dpk_conv_psg(x.data_ptr(), g.data_ptr(), B, C, H, W, O, OH, OW, kh, kw, sh, sw, ph, pw, dh, dw, reduce_batch,
+                     out_ptr, out_bf16, (float)beta, nsq, status_for(x.get_device()).dev, stream()),
+        "conv_psg");
+}
+
 at::Tensor scale_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t rows_per_sample, double scale) {
   c10::cuda::CUDAGuard guard(x.device());
   need_cuda_contig(x, "x");
@@ -347,6 +384,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
   m.def("wgrad_tn", &wgrad_tn);
   m.def("wgrad_tn_ex", &wgrad_tn_ex);
+  m.def("conv_psg", &conv_psg);
   m.def("scale_rows", &scale_rows);
   m.def("clip_factor", &clip_factor);
   m.def("row_norm_sq", &row_norm_sq);

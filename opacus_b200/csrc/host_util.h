@@ -52,6 +52,25 @@ inline int make_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t d0, ui
   return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
 }
 
+// [d3][d2][d1][d0] tensor of 16-bit elements, d0 contiguous (an NHWC image batch: d0 = channels, d1 = width,
+// d2 = height, d3 = sample).  The box takes 64 channels and n1 x n2 pixels that are s1 / s2 elements apart
+// (a strided convolution's input positions); 128-byte swizzle; zero fill outside the tensor.
+inline int make_tmap_4d_bf16(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                             uint32_t n1, uint32_t n2, uint32_t s1, uint32_t s2) {
+  auto enc = tmap_encoder();
+  if (!enc) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((d0 * 2) & 15) != 0) return cudaErrorInvalidValue;
+  if (n1 * s1 > 256 || n2 * s2 > 256 || s1 < 1 || s2 < 1 || s1 > 8 || s2 > 8) return cudaErrorInvalidValue;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {d0 * 2, d0 * d1 * 2, d0 * d1 * d2 * 2};
+  cuuint32_t box[4] = {64, n1 * s1, n2 * s2, 1};
+  cuuint32_t estr[4] = {1, s1, s2, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
+}
+
 inline int num_sms() {
   static int cached[64] = {0};
   int dev = 0;

@@ -14,7 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..utils.tensor_utils import unfold_nd
-from .utils import register_grad_sampler, register_wgrad_sampler
+from .utils import register_grad_sampler, register_norm_sq_sampler, register_wgrad_sampler
 
 _CONVS = [nn.Conv1d, nn.Conv2d, nn.Conv3d]
 
@@ -40,6 +40,17 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
         return out
     O = layer.out_channels
     ck = layer.weight[0].numel() * layer.groups
+    geom = _implicit_geometry(layer, x, backprops)
+    if geom is not None:
+        # implicit-unfold tensor-core kernel: no unfolded copy, norm from the accumulators
+        from ..ops import _cuda
+
+        out = {}
+        if layer.weight.requires_grad:
+            out[layer.weight] = _cuda.conv_grad_sample(x, backprops, geom)
+        if want_b:
+            out[layer.bias] = backprops.reshape(n, O, -1).sum(dim=2)
+        return out
     if (x.is_cuda and backprops.dtype == torch.bfloat16 and layer.groups == 1 and O % 8 == 0 and ck % 8 == 0):
         # tensor-core path: both operands with the output positions (the contraction) outermost
         cols_t = unfold_nd(x, kernel_size=layer.kernel_size, padding=layer.padding, stride=layer.stride,
@@ -75,9 +86,61 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
     return out
 
 
+def _implicit_geometry(layer, x, backprops):
+    """Geometry tuple when the implicit-unfold CUDA kernel covers this call, else None."""
+    if not (x.is_cuda and backprops.dtype == torch.bfloat16) or _base_type(layer) is nn.Conv3d:
+        return None
+    from ..ops import _cuda
+
+    return _cuda.conv_geometry(layer, x, backprops)
+
+
+@register_norm_sq_sampler(_CONVS)
+def compute_conv_norm_sq(layer, activations, backprops, g_scale: float = 1.0, total=None):
+    """Squared per-sample gradient norms of a conv layer.  On the GPU (bf16, ungrouped,
+    1-d/2-d) the per-sample gradient tiles are formed in tensor memory and squared
+    there, never written; otherwise the gradients are instantiated
+    (``opacus/grad_sample/grad_sample_module_fast_gradient_clipping.py:226-250``)."""
+    x = activations[0]
+    n = x.shape[0]
+    want_w = layer.weight.requires_grad
+    want_b = layer.bias is not None and layer.bias.requires_grad
+    out = {}
+    geom = _implicit_geometry(layer, x, backprops) if n else None
+    if geom is not None:
+        from ..ops import _cuda
+
+        if want_w:
+            out[layer.weight] = _cuda.conv_grad_sample(x, backprops, geom, want_out=False) * (g_scale * g_scale)
+        if want_b:
+            out[layer.bias] = (backprops.reshape(n, layer.out_channels, -1).sum(dim=2).float() * g_scale).square().sum(dim=1)
+    else:
+        from .. import ops
+
+        scaled = backprops * g_scale if g_scale != 1.0 else backprops
+        for p, gs in compute_conv_grad_sample(layer, activations, scaled).items():
+            out[p] = ops.grad_sample_norm_sq(gs)
+    if total is not None:
+        for v in out.values():
+            total.add_(v.to(total.dtype))
+        return {}
+    return out
+
+
 @register_wgrad_sampler(_CONVS)
 def compute_conv_weighted_grad(layer, activations, backprops, coef, g_scale: float = 1.0):
     x = activations[0]
+    geom = _implicit_geometry(layer, x, backprops) if x.shape[0] else None
+    if geom is not None:
+        from ..ops import _cuda
+
+        out = {}
+        if layer.weight.requires_grad:
+            out[layer.weight] = _cuda.conv_weighted_grad(x, backprops, coef, geom, g_scale)
+        if layer.bias is not None and layer.bias.requires_grad:
+            per = backprops.reshape(backprops.shape[0], backprops.shape[1], -1).sum(dim=2).float()
+            out[layer.bias] = (per * (coef.float() * g_scale)[:, None]).sum(dim=0)
+        return out
     shape = (-1,) + (1,) * (backprops.dim() - 1)
     gw = backprops * (coef.to(backprops.dtype) * g_scale).reshape(shape)
     out = {}

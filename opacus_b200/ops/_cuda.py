@@ -264,9 +264,99 @@ def grad_sample_norm_sq(gs):
     return load().row_norm_sq(gs.contiguous())
 
 
+def _dense_order(t):
+    """Axis order (sample axis first) in which ``t`` is laid out densely, or None."""
+    if t.is_contiguous():
+        return None
+    order = [0] + sorted(range(1, t.dim()), key=lambda d: -t.stride(d))
+    return order if t.permute(order).is_contiguous() else None
+
+
 def weighted_sum(gs, c):
+    order = _dense_order(gs)
+    if order is not None:
+        # a permuted view of a dense buffer (e.g. the channels-last conv gradient): sum in storage
+        # order, then hand back the result in the logical axis order
+        phys = gs.permute(order)
+        out = load().weighted_sum(phys, c.float().contiguous()).view(phys.shape[1:])
+        inv = [0] * (gs.dim() - 1)
+        for pos, d in enumerate(order[1:]):
+            inv[d - 1] = pos
+        return out.permute(inv).contiguous().to(gs.dtype)
     out = load().weighted_sum(gs.contiguous(), c.float().contiguous())
     return out.view(gs.shape[1:]).to(gs.dtype)
+
+
+# ------------------------------------------------------------------- convolution (implicit unfold)
+def conv_geometry(layer, x, backprops):
+    """``(kh, kw, sh, sw, ph, pw, dh, dw)`` when the implicit-unfold kernel covers this
+    Conv1d / Conv2d call, else None (grouped, 3-d, string or non-zero-mode padding,
+    channel counts that are not multiples of 8, non-bf16 data)."""
+    nsp = x.dim() - 2
+    if nsp not in (1, 2) or backprops.dtype != torch.bfloat16 or not x.is_cuda:
+        return None
+    if layer.groups != 1 or getattr(layer, "padding_mode", "zeros") != "zeros":
+        return None
+    if layer.in_channels % 8 or layer.out_channels % 8:
+        return None
+    pad = layer.padding
+    if isinstance(pad, str):
+        if pad == "valid":
+            pad = (0,) * nsp
+        else:
+            tot = [d * (k - 1) for k, d in zip(layer.kernel_size, layer.dilation)]
+            if any(t % 2 for t in tot):
+                return None
+            pad = tuple(t // 2 for t in tot)
+    k, s, d = tuple(layer.kernel_size), tuple(layer.stride), tuple(layer.dilation)
+    if nsp == 1:
+        k, s, pad, d = (1,) + k, (1,) + s, (0,) + tuple(pad), (1,) + d
+    ow = backprops.shape[-1]
+    bw = 1
+    while bw < ow and bw < 64:
+        bw *= 2
+    if max(s) > 8 or bw * s[1] > 256 or (64 // bw) * s[0] > 256:
+        return None
+    return (k[0], k[1], s[0], s[1], int(pad[0]), int(pad[1]), d[0], d[1])
+
+
+def _nhwc(t):
+    """[B, C, H, W] (or [B, C, W]) -> contiguous [B, H, W, C]; free for channels-last tensors."""
+    if t.dim() == 3:
+        return t.transpose(1, 2).contiguous().unsqueeze(1)
+    return t.permute(0, 2, 3, 1).contiguous()
+
+
+def conv_grad_sample(x, backprops, geom, want_out=True, norm_total=None):
+    """Per-sample conv weight gradients ``[B, O, C, kh, kw]`` (a permuted view of the
+    kernel's ``[B, O, kh, kw, C]`` output, ``_dp_norm_sq`` attached) and/or their
+    squared norms added into ``norm_total``."""
+    xh, gh = _nhwc(x.to(torch.bfloat16)), _nhwc(backprops)
+    B, O, C = xh.shape[0], gh.shape[3], xh.shape[3]
+    kh, kw = geom[0], geom[1]
+    out = torch.empty((B, O, kh, kw, C), dtype=torch.bfloat16, device=x.device) if want_out else None
+    norm = norm_total if norm_total is not None else torch.zeros(B, dtype=torch.float32, device=x.device)
+    load().conv_psg(xh, gh, list(geom), False, out, 0.0, norm)
+    if out is None:
+        return norm
+    gs = out.permute(0, 1, 4, 2, 3)
+    if x.dim() == 3:
+        gs = gs.squeeze(3)
+    if norm_total is None:
+        gs._dp_norm_sq = norm
+    return gs
+
+
+def conv_weighted_grad(x, backprops, coef, geom, g_scale=1.0):
+    """``sum_b coef_b * grad_b`` of a conv weight as one implicit GEMM over all samples' pixels; fp32 ``[O, C, kh, kw]``."""
+    xh, gh = _nhwc(x.to(torch.bfloat16)), _nhwc(backprops)
+    B, OH, OW, O = gh.shape
+    C = xh.shape[3]
+    gsc = load().scale_rows(gh.view(B * OH * OW, O), coef.float().contiguous(), OH * OW, float(g_scale)).view(gh.shape)
+    out = torch.empty((O, geom[0], geom[1], C), dtype=torch.float32, device=x.device)
+    load().conv_psg(xh, gsc, list(geom), True, out, 0.0, None)
+    w = out.permute(0, 3, 1, 2).contiguous()
+    return w.squeeze(2) if x.dim() == 3 else w
 
 
 # ------------------------------------------------------------------- fused step

@@ -246,3 +246,87 @@ def test_conv_per_sample_grad_tensor_core_path():
     assert gw.shape == want_w.shape and _rel(gw, want_w) < 1e-2
     assert _rel(ops.grad_sample_norm_sq(gw), want_w.pow(2).sum(dim=(1, 2, 3, 4))) < 5e-3
     assert _rel(got[conv.bias], g.float().sum(dim=(2, 3))) < 1e-2
+
+
+def _conv_oracle(conv, x, g):
+    """fp32 per-sample weight gradients by one autograd call per sample."""
+    out = []
+    w = conv.weight.detach().float().requires_grad_(True)
+    for b in range(x.shape[0]):
+        y = torch.nn.functional.conv2d(x[b:b + 1].float(), w, None, conv.stride, conv.padding, conv.dilation) \
+            if x.dim() == 4 else \
+            torch.nn.functional.conv1d(x[b:b + 1].float(), w, None, conv.stride, conv.padding, conv.dilation)
+        (gw,) = torch.autograd.grad(y, w, g[b:b + 1].float())
+        out.append(gw)
+    return torch.stack(out)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [
+    dict(C=64, O=64, H=32, W=32, k=3, s=1, p=1, d=1),
+    dict(C=128, O=256, H=8, W=8, k=3, s=1, p=1, d=1),
+    dict(C=24, O=40, H=14, W=14, k=3, s=1, p=1, d=1),     # partial channel block, odd width
+    dict(C=64, O=128, H=16, W=16, k=1, s=1, p=0, d=1),
+    dict(C=64, O=128, H=32, W=32, k=3, s=2, p=1, d=1),    # strided
+    dict(C=64, O=128, H=17, W=17, k=1, s=2, p=0, d=1),
+    dict(C=32, O=32, H=20, W=20, k=3, s=1, p=2, d=2),     # dilated
+    dict(C=16, O=32, H=9, W=70, k=(3, 5), s=(1, 2), p=(1, 2), d=1),
+])
+def test_conv_implicit_per_sample_grad(cfg):
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    B = 5
+    conv = torch.nn.Conv2d(cfg["C"], cfg["O"], cfg["k"], stride=cfg["s"], padding=cfg["p"], dilation=cfg["d"],
+                           bias=False).cuda().to(torch.bfloat16)
+    x = torch.randn(B, cfg["C"], cfg["H"], cfg["W"], device="cuda", dtype=torch.bfloat16)
+    y = conv(x)
+    g = torch.randn_like(y)
+    geom = _cuda.conv_geometry(conv, x, g)
+    assert geom is not None
+    gs = _cuda.conv_grad_sample(x, g, geom)
+    ref = _conv_oracle(conv, x, g)
+    assert gs.shape == ref.shape
+    scale = ref.abs().max()
+    assert (gs.float() - ref).abs().max() <= 1e-2 * scale
+    nref = ref.flatten(1).square().sum(1)
+    torch.testing.assert_close(gs._dp_norm_sq, nref, rtol=2e-3, atol=0)
+    # norm only
+    n2 = _cuda.conv_grad_sample(x, g, geom, want_out=False)
+    torch.testing.assert_close(n2, nref, rtol=2e-3, atol=0)
+    # clipped sum as one GEMM over the batch
+    coef = torch.rand(B, device="cuda")
+    ws = _cuda.conv_weighted_grad(x, g, coef, geom, g_scale=2.0)
+    wref = (ref * (2.0 * coef)[:, None, None, None, None]).sum(0)
+    assert (ws - wref).abs().max() <= 1e-2 * wref.abs().max()
+    # weighted sum of the permuted per-sample view
+    s = _cuda.weighted_sum(gs, coef)
+    sref = (gs.float() * coef[:, None, None, None, None]).sum(0)
+    assert s.shape == sref.shape and (s.float() - sref).abs().max() <= 2e-2 * sref.abs().max()
+    _cuda.check_status()
+
+
+@pytest.mark.gpu
+def test_conv1d_implicit_and_rules():
+    from opacus_b200.grad_sample.conv import compute_conv_grad_sample, compute_conv_norm_sq, compute_conv_weighted_grad
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(1)
+    conv = torch.nn.Conv1d(16, 24, 5, padding=2).cuda().to(torch.bfloat16)
+    x = torch.randn(4, 16, 100, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(4, 24, 100, device="cuda", dtype=torch.bfloat16)
+    assert _cuda.conv_geometry(conv, x, g) is not None
+    ref = _conv_oracle(conv, x, g)
+    out = compute_conv_grad_sample(conv, [x], g)
+    assert out[conv.weight].shape == ref.shape
+    assert (out[conv.weight].float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    torch.testing.assert_close(out[conv.bias].float(), g.float().sum(2), rtol=2e-2, atol=2e-1)
+    nsq = compute_conv_norm_sq(conv, [x], g, 3.0)
+    torch.testing.assert_close(nsq[conv.weight], 9.0 * ref.flatten(1).square().sum(1), rtol=2e-3, atol=0)
+    coef = torch.rand(4, device="cuda")
+    wg = compute_conv_weighted_grad(conv, [x], g, coef, 1.0)
+    wref = (ref * coef[:, None, None, None]).sum(0)
+    assert (wg[conv.weight] - wref).abs().max() <= 1e-2 * wref.abs().max()
+    bref = (g.float().sum(2) * coef[:, None]).sum(0)
+    torch.testing.assert_close(wg[conv.bias], bref, rtol=1e-2, atol=1e-1)
+    _cuda.check_status()
