@@ -3,6 +3,7 @@
     python -m opacus_b200.benchmarks.kernels --op ghost_norm --B 8 --T 1024 --din 2048 --dout 8192
     python -m opacus_b200.benchmarks.kernels --op wgrad --B 8 --T 1024 --din 2048 --dout 8192
     python -m opacus_b200.benchmarks.kernels --op all
+    python -m opacus_b200.benchmarks.kernels --op conv --B 512 --C 64 --O 64 --HW 32 --k 3
 
 Reports time per call, achieved TFLOP/s (or GB/s) and the fraction of the
 measured peak: ``MEASURED_PEAKS.json`` next to the repository root if present,
@@ -114,8 +115,49 @@ def run(op, B, T, din, dout, iters=20):
     return rows
 
 
+def run_conv(B, C, O, HW, k, stride=1, iters=20):
+    """Conv2d per-sample weight gradient kernels at one layer shape (3x3 pad 1 or 1x1 pad 0)."""
+    dev = torch.device("cuda")
+    flush = torch.zeros(64 << 20, device=dev)
+    conv = torch.nn.Conv2d(C, O, k, stride=stride, padding=k // 2, bias=False).to(dev).bfloat16()
+    x = torch.randn(B, C, HW, HW, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+    OHW = (HW + 2 * (k // 2) - k) // stride + 1
+    g = (torch.randn(B, O, OHW, OHW, device=dev) * 0.1).bfloat16().contiguous(memory_format=torch.channels_last)
+    coef = torch.rand(B, device=dev)
+    geom = _cuda.conv_geometry(conv, x, g)
+    tf_peak, bw_peak, src = _peaks()
+    flops = 2.0 * B * OHW * OHW * O * C * k * k
+    in_bytes = (x.numel() + g.numel()) * 2.0
+    out_bytes = B * O * C * k * k * 2.0
+    rows = []
+    ms = _time(lambda: _cuda.conv_grad_sample(x, g, geom), iters, flush)
+    rows.append(("conv per-sample grad + norm (implicit)", ms, flops / ms / 1e9, (in_bytes + out_bytes) / ms / 1e6))
+    ms = _time(lambda: _cuda.conv_grad_sample(x, g, geom, want_out=False), iters, flush)
+    rows.append(("conv ghost norm (no output)", ms, flops / ms / 1e9, in_bytes / ms / 1e6))
+    ms = _time(lambda: _cuda.conv_weighted_grad(x, g, coef, geom), iters, flush)
+    rows.append(("conv clipped sum (one GEMM over the batch)", ms, flops / ms / 1e9, in_bytes / ms / 1e6))
+
+    def unfold_bmm():
+        cols = torch.nn.functional.unfold(x, k, padding=k // 2, stride=stride)
+        return torch.bmm(g.reshape(B, O, -1), cols.transpose(1, 2))
+
+    ms = _time(unfold_bmm, iters, flush)
+    rows.append(("unfold + bmm (library, for scale)", ms, flops / ms / 1e9, (in_bytes + out_bytes) / ms / 1e6))
+    _cuda.check_status()
+    print(f"conv B={B} C={C} O={O} {HW}x{HW} k={k} stride={stride}; peaks: {tf_peak} TFLOP/s bf16, {bw_peak} GB/s ({src})")
+    for name, ms, tf, gb in rows:
+        print(f"{name:48s} {ms:9.4f} ms  {tf:8.1f} TFLOP/s ({tf / tf_peak:5.3f})  {gb:8.1f} GB/s algorithmic "
+              f"({gb / bw_peak:5.3f} of {src} copy peak)")
+    return rows
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
+    ap.add_argument("--C", type=int, default=64)
+    ap.add_argument("--O", type=int, default=64)
+    ap.add_argument("--HW", type=int, default=32)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--op", default="all")
     ap.add_argument("--B", type=int, default=8)
     ap.add_argument("--T", type=int, default=1024)
@@ -123,4 +165,7 @@ if __name__ == "__main__":
     ap.add_argument("--dout", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
-    run(args.op, args.B, args.T, args.din, args.dout, args.iters)
+    if args.op == "conv":
+        run_conv(args.B, args.C, args.O, args.HW, args.k, args.stride, args.iters)
+    else:
+        run(args.op, args.B, args.T, args.din, args.dout, args.iters)

@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--physical", type=int, default=512)
     ap.add_argument("--steps", type=int, default=2, help="timed logical steps")
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--channels-last", action="store_true", help="NHWC model and inputs (both libraries)")
     args = ap.parse_args()
     import warnings
 
@@ -50,6 +51,8 @@ def main():
 
     torch.manual_seed(0)
     model = resnet18_gn().cuda()
+    if args.channels_last:
+        model = model.to(memory_format=torch.channels_last)
     n_batches = args.steps + args.warmup
     n_data = args.logical * world * n_batches
     # the loader only fixes the sampling rate and batch structure; samples are synthetic
@@ -90,6 +93,8 @@ def main():
                 y = y.cuda(non_blocking=True)
                 if not autocast:
                     x = x.to(torch.bfloat16)
+                if args.channels_last:
+                    x = x.contiguous(memory_format=torch.channels_last)
                 opt.zero_grad()
                 if len(x):
                     if autocast:
@@ -121,7 +126,8 @@ def main():
         print(json.dumps({"impl": args.impl, "metric": "dp_resnet18gn_samples_per_s", "n_gpus": world,
                           "value": total_seen / (float(tmax[0]) / 1e3), "logical_batch_per_gpu": args.logical,
                           "physical_batch": args.physical, "logical_steps": args.steps, "samples": total_seen,
-                          "ms": float(tmax[0]), "epsilon_delta_1e-5": pe.get_epsilon(1e-5), "dtype": "bf16"}))
+                          "ms": float(tmax[0]), "channels_last": bool(args.channels_last),
+                          "epsilon_delta_1e-5": pe.get_epsilon(1e-5), "dtype": "bf16"}))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -211,36 +211,60 @@ __global__ void lastdim_grad_kernel(const void* x, const void* g, const float2* 
 }
 
 // ---------------------------------------------------------------- GroupNorm / InstanceNorm
-// One block per (sample, group).  x, g: [B, C, S].
+// One block per (sample, group).  x, g: [B, C, S].  The group's statistics come from one 8-wide sweep
+// of its (contiguous) data; then each warp takes whole channels, so the per-channel sums need no block barrier
+// and the second read of x hits L1/L2.
 template <int KIND>
-__global__ void channel_grad_kernel(const void* x, const void* g, int64_t C, int64_t S, int groups, float eps,
-                                    float* gw, float* gb) {
+__global__ void __launch_bounds__(256)
+channel_grad_kernel(const void* x, const void* g, int64_t C, int64_t S, int groups, float eps, float* gw, float* gb) {
   __shared__ float sh[32];
   const int64_t n = blockIdx.x / groups;
   const int grp = blockIdx.x % groups;
   const int64_t cpg = C / groups;
   const int64_t base = (n * C + grp * cpg) * S;
   const int64_t cnt = cpg * S;
+  // 8-wide loads need every channel row to start on a 16-byte boundary
+  const bool vec = (S & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
   float s = 0.f, ss = 0.f;
-  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) {
-    const float v = load1<KIND>(x, base + i);
-    s += v; ss = fmaf(v, v, ss);
+  if (vec) {
+    for (int64_t i = (int64_t)threadIdx.x * 8; i < cnt; i += (int64_t)blockDim.x * 8) {
+      float v[8];
+      load8<KIND>(x, base + i, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { s += v[q]; ss = fmaf(v[q], v[q], ss); }
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const float v = load1<KIND>(x, base + i);
+      s += v; ss = fmaf(v, v, ss);
+    }
   }
   s = block_sum(s, sh);
   ss = block_sum(ss, sh);
   const float mean = s / cnt;
   const float rstd = rsqrtf(fmaxf(ss / cnt - mean * mean, 0.f) + eps);
-  for (int64_t c = 0; c < cpg; ++c) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int64_t c = warp; c < cpg; c += nwarps) {
+    const int64_t row = base + c * S;
     float aw = 0.f, ab = 0.f;
-    for (int64_t i = threadIdx.x; i < S; i += blockDim.x) {
-      const float xv = load1<KIND>(x, base + c * S + i);
-      const float gv = load1<KIND>(g, base + c * S + i);
-      aw = fmaf((xv - mean) * rstd, gv, aw);
-      ab += gv;
+    if (vec) {
+      for (int64_t i = (int64_t)lane * 8; i < S; i += 32 * 8) {
+        float xv[8], gv[8];
+        load8<KIND>(x, row + i, xv);
+        load8<KIND>(g, row + i, gv);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { aw = fmaf((xv[q] - mean) * rstd, gv[q], aw); ab += gv[q]; }
+      }
+    } else {
+      for (int64_t i = lane; i < S; i += 32) {
+        const float gv = load1<KIND>(g, row + i);
+        aw = fmaf((load1<KIND>(x, row + i) - mean) * rstd, gv, aw);
+        ab += gv;
+      }
     }
-    aw = block_sum(aw, sh);
-    ab = block_sum(ab, sh);
-    if (threadIdx.x == 0) {
+    aw = warp_sum(aw);
+    ab = warp_sum(ab);
+    if (lane == 0) {
       if (gw) gw[n * C + grp * cpg + c] = aw;
       if (gb) gb[n * C + grp * cpg + c] = ab;
     }
