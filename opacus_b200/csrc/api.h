@@ -111,6 +111,47 @@ struct DpkShardedStep {
 };
 int dpk_sharded_dp_step(const struct DpkShardedStep* p, cudaStream_t stream);
 
+// Sum of per-rank [n] fp32 vectors over a group of <= 8 ranks through symmetric memory, plus the clip factor
+// min(1, max_norm / (sqrt(total) + 1e-6)), identical bits on every rank.  slots[r]: rank r's symmetric buffer of
+// 2 * world * capacity floats; flags[r]: rank r's symmetric flag words, of which [flag_base, flag_base + world) are
+// used; epoch: 1, 2, 3, ... on successive calls of the same group (all ranks pass the same value).
+struct DpkNormAllReduce {
+  float* slots[8];
+  uint32_t* flags[8];
+  const float* sharded;      // [n] partial sums of this rank, or NULL (zeros)
+  const float* replicated;   // [n] added once, unreduced, or NULL
+  float* total_out;          // [n] or NULL
+  float* clip_out;           // [n] or NULL
+  int32_t n, capacity, world, rank, flag_base, pad;
+  uint32_t epoch;
+  float max_norm;
+  uint32_t* status;
+};
+int dpk_norm_allreduce_clip(const struct DpkNormAllReduce* p, cudaStream_t stream);
+
+// C[M, N] = A[M, K] B[N, K]^T (bf16, K contiguous) alone or fused with a collective over <= 8 NVLink peers:
+//   mode 0 plain; mode 1 all-gather of A's rows first; mode 2 all-gather of B's rows first;
+//   mode 3 reduce-scatter of C's rows afterwards (out = this rank's M / world rows).
+// Gather modes: `a` (mode 1) / `b` (mode 2) is the LOCAL buffer for the whole operand, which the kernel fills
+// from shard[r] (rank r's rows, symmetric memory) while it computes; rows must be a multiple of
+// world * 128 (mode 1) or world * 256 (mode 2); `ready` = one zero-initialised counter per 128 / 256 rows.
+// Mode 3: slots[r] = rank r's symmetric buffer of 2 * M * N bf16; M a multiple of world * 128.
+// flags[r]: rank r's symmetric flag words (>= 32, zero-initialised, private to this call site);
+// epoch: 1, 2, 3, ... on successive calls with the same buffers.  Modes 1-3 launch cooperatively.
+struct DpkTpGemm {
+  const void* a;
+  const void* b;
+  void* out;
+  int32_t M, N, K, mode, world, rank, producers;
+  uint32_t epoch;
+  const void* shard[8];
+  void* slots[8];
+  uint32_t* flags[8];
+  uint32_t* ready;
+  uint32_t* status;
+};
+int dpk_tp_gemm(const struct DpkTpGemm* p, cudaStream_t stream);
+
 // Standard normal samples (testing the generator): out[i] for i < n.
 int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream);
 

@@ -365,6 +365,77 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
   check(dpk_sharded_dp_step(&p, stream()), "sharded_dp_step");
 }
 
+// Peer-memory all-reduce of a [n] fp32 vector + clip factor.  Returns {total, clip}.
+std::vector<at::Tensor> norm_allreduce_clip(std::vector<int64_t> slot_ptrs, std::vector<int64_t> flag_ptrs,
+                                            c10::optional<at::Tensor> sharded, c10::optional<at::Tensor> replicated,
+                                            int64_t n, int64_t capacity, int64_t rank, int64_t flag_base, int64_t epoch,
+                                            double max_norm, at::Device device) {
+  c10::cuda::CUDAGuard guard(device);
+  raise_if_failed(device.index());
+  const int world = (int)slot_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)flag_ptrs.size() == world, "norm_allreduce_clip supports 1..8 ranks");
+  DpkNormAllReduce p{};
+  for (int r = 0; r < world; ++r) {
+    p.slots[r] = reinterpret_cast<float*>(slot_ptrs[r]);
+    p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  auto vec = [&](const c10::optional<at::Tensor>& t, const char* what) -> const float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == n, what);
+    return t->data_ptr<float>();
+  };
+  p.sharded = vec(sharded, "sharded must be a contiguous fp32 CUDA vector of n elements");
+  p.replicated = vec(replicated, "replicated must be a contiguous fp32 CUDA vector of n elements");
+  at::Tensor total = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  at::Tensor clip = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  p.total_out = total.data_ptr<float>();
+  p.clip_out = clip.data_ptr<float>();
+  p.n = (int)n; p.capacity = (int)capacity; p.world = world; p.rank = (int)rank; p.flag_base = (int)flag_base;
+  p.epoch = (uint32_t)epoch; p.max_norm = (float)max_norm;
+  p.status = status_for(device.index()).dev;
+  check(dpk_norm_allreduce_clip(&p, stream()), "norm_allreduce_clip");
+  return {total, clip};
+}
+
+// a [M, K], b [N, K] bf16 contiguous; see DpkTpGemm for the modes.  out: [M, N] (modes 0-2) or [M / world, N].
+void tp_gemm(at::Tensor a, at::Tensor b, at::Tensor out, int64_t mode, std::vector<int64_t> shard_ptrs,
+             std::vector<int64_t> slot_ptrs, std::vector<int64_t> flag_ptrs, c10::optional<at::Tensor> ready,
+             int64_t rank, int64_t world, int64_t epoch, int64_t producers) {
+  c10::cuda::CUDAGuard guard(a.device());
+  raise_if_failed(a.get_device());
+  need_cuda_contig(a, "a");
+  need_cuda_contig(b, "b");
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+              out.scalar_type() == at::kBFloat16, "bf16 tensors expected");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "a [M, K] and b [N, K] expected");
+  TORCH_CHECK(world >= 1 && world <= 8, "1..8 ranks");
+  DpkTpGemm p{};
+  p.a = a.data_ptr(); p.b = b.data_ptr(); p.out = out.data_ptr();
+  p.M = (int)a.size(0); p.N = (int)b.size(0); p.K = (int)a.size(1);
+  p.mode = (int)mode; p.world = (int)world; p.rank = (int)rank; p.producers = (int)producers;
+  p.epoch = (uint32_t)epoch;
+  TORCH_CHECK(out.numel() == (int64_t)(mode == 3 ? p.M / world : p.M) * p.N, "out has the wrong size");
+  if (mode != 0) {
+    TORCH_CHECK((int64_t)flag_ptrs.size() == world, "one flag pointer per rank");
+    for (int r = 0; r < world; ++r) p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  if (mode == 1 || mode == 2) {
+    TORCH_CHECK((int64_t)shard_ptrs.size() == world, "one shard pointer per rank");
+    for (int r = 0; r < world; ++r) p.shard[r] = reinterpret_cast<const void*>(shard_ptrs[r]);
+    const int64_t units = mode == 1 ? p.M / 128 : p.N / 256;
+    TORCH_CHECK(ready.has_value() && ready->is_cuda() && ready->scalar_type() == at::kInt && ready->is_contiguous() &&
+                ready->numel() >= units, "ready must be an int32 CUDA vector with one entry per unit");
+    p.ready = reinterpret_cast<uint32_t*>(ready->data_ptr<int>());
+  }
+  if (mode == 3) {
+    TORCH_CHECK((int64_t)slot_ptrs.size() == world, "one slot pointer per rank");
+    for (int r = 0; r < world; ++r) p.slots[r] = reinterpret_cast<void*>(slot_ptrs[r]);
+  }
+  p.status = status_for(a.get_device()).dev;
+  check(dpk_tp_gemm(&p, stream()), "tp_gemm");
+}
+
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
   at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
@@ -395,6 +466,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_scatter", &embedding_scatter);
   m.def("fused_dp_step", &fused_dp_step);
   m.def("sharded_dp_step", &sharded_dp_step);
+  m.def("norm_allreduce_clip", &norm_allreduce_clip);
+  m.def("tp_gemm", &tp_gemm);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
   m.def("tensor_entry_size", &tensor_entry_size);

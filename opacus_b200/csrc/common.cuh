@@ -131,6 +131,28 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes); never multicast.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gmem_dst)), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait() {          // at most N groups still pending (writes complete)
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {     // at most N groups still reading their source
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -218,6 +240,30 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t a
                                                   uint32_t M, uint32_t N) {
   return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
          ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// ----------------------------------------------------------------------------- flag waits between ranks / blocks
+// Epoch flags: a word holds the number of the last step its writer reached.  The high bit tells waiters to give up.
+constexpr uint32_t kAbortBit = 0x80000000u;
+
+// Spins until *word >= epoch (wrap-safe) for at most kWaitLimitNs; on expiry records (site, epoch, value seen).
+__device__ __forceinline__ bool spin_until_epoch(volatile uint32_t* word, uint32_t epoch, uint32_t* status,
+                                                 uint32_t site) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    const uint32_t v = *word;
+    if (v & kAbortBit) return false;
+    if (static_cast<int32_t>(v - epoch) >= 0) return true;
+    if ((++spins & 0xffu) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        report_error(status, site, ERR_WAIT_TIMEOUT, epoch, v);
+        return false;
+      }
+    }
+  }
 }
 
 // ----------------------------------------------------------------------------- Philox4x32-10

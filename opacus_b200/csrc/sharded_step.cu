@@ -30,27 +30,7 @@ constexpr int kSlotStart = 0;     // flags[kSlotStart + r]  : rank r reached the
 constexpr int kSlotDone = 8;      // flags[kSlotDone + r]   : rank r finished its stores (epoch)
 constexpr int kSlotGo = 16;       // local: block 0 -> other blocks
 constexpr int kSlotCount = 17;    // local: finished-block counter
-constexpr uint32_t kAbortBit = 0x80000000u;
 constexpr int kShThreads = 512;
-
-__device__ __forceinline__ bool spin_until_epoch(volatile uint32_t* word, uint32_t epoch, uint32_t* status,
-                                                 uint32_t site) {
-  uint32_t spins = 0;
-  uint64_t t0 = 0;
-  while (true) {
-    const uint32_t v = *word;
-    if (v & kAbortBit) return false;
-    if (static_cast<int32_t>(v - epoch) >= 0) return true;
-    if ((++spins & 0xffu) == 0) {
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
-        report_error(status, site, ERR_WAIT_TIMEOUT, epoch, v);
-        return false;
-      }
-    }
-  }
-}
 
 __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep p) {
   __shared__ uint32_t sh_ok;

@@ -83,13 +83,39 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
             self._norm_sq_replicated = v.clone() if self._norm_sq_replicated is None else \
                 self._norm_sq_replicated.add_(v)
 
+    def _group_sum(self, sharded, replicated) -> torch.Tensor:
+        """``sum_ranks sharded + replicated``.  On NVLink-connected GPUs this is one
+        peer-memory kernel that also yields the clip factors (kept in
+        ``_peer_clip``), bit-identical on all ranks; elsewhere an all-reduce."""
+        ref = sharded if sharded is not None else replicated
+        self._peer_clip = None
+        reducer = self._peer_reducer(ref)
+        if reducer is not None:
+            total, clip = reducer(sharded, replicated, float(self.max_grad_norm))
+            self._peer_clip = clip
+            return total
+        total = sharded.clone() if sharded is not None else torch.zeros_like(ref)
+        torch.distributed.all_reduce(total, op=torch.distributed.ReduceOp.SUM, group=self.process_group)
+        if replicated is not None:
+            total = total + replicated
+        return total
+
+    def _peer_reducer(self, ref):
+        """The peer-memory reducer, created on first use (collectively), or None."""
+        if getattr(self, "_reducer", None) is None:
+            self._reducer = False
+            if ref.is_cuda and self.use_peer_memory:
+                from ..parallel import symm
+
+                if symm.available(self.process_group) is None:
+                    self._reducer = symm.PeerNormReducer(ref.device, self.process_group)
+        r = self._reducer
+        return r if r and ref.numel() <= r.capacity else None
+
+    use_peer_memory = True
+
     def _single_pass_norm_sq(self) -> torch.Tensor:
-        ref = self._norm_sq_total if self._norm_sq_total is not None else self._norm_sq_replicated
-        sharded = self._norm_sq_total.clone() if self._norm_sq_total is not None else torch.zeros_like(ref)
-        torch.distributed.all_reduce(sharded, op=torch.distributed.ReduceOp.SUM, group=self.process_group)
-        if self._norm_sq_replicated is not None:
-            sharded = sharded + self._norm_sq_replicated
-        return sharded
+        return self._group_sum(self._norm_sq_total, self._norm_sq_replicated)
 
     def _group_rank(self) -> int:
         return torch.distributed.get_rank(self.process_group)
@@ -99,23 +125,22 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
             norm = self._single_pass_norm_sq().clamp(min=0).sqrt()
             self.per_sample_gradient_norms = norm
             return norm
-        first = self._group_rank() == 0
-        sq = None
+        sharded = replicated = None
         for p in self.trainable_parameters:
-            if not p.merge_flag and not first:
-                continue
             v = p._norm_sample.float().square()
-            sq = v if sq is None else sq + v
-        if sq is None:
-            ref = self.trainable_parameters[0]._norm_sample
-            sq = torch.zeros_like(ref, dtype=torch.float32)
-        torch.distributed.all_reduce(sq, op=torch.distributed.ReduceOp.SUM, group=self.process_group)
-        norm = sq.sqrt()
+            if p.merge_flag:
+                sharded = v if sharded is None else sharded + v
+            else:
+                replicated = v if replicated is None else replicated + v
+        norm = self._group_sum(sharded, replicated).sqrt()
         self.per_sample_gradient_norms = norm
         return norm
 
     def get_clipping_coef(self) -> torch.Tensor:
         norm = self.get_norm_sample()
+        clip = getattr(self, "_peer_clip", None)
+        if clip is not None and clip.shape == norm.shape:
+            return clip
         return (self.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
 
 

@@ -63,3 +63,36 @@ def available(group=None) -> Optional[str]:
     if dist.get_backend(group) != "nccl":
         return "process group backend is not nccl"
     return None
+
+
+class PeerNormReducer:
+    """All-reduce of a per-sample ``[B]`` fp32 vector over the group plus the clip
+    factor, as one single-block kernel per rank over peer memory
+    (``csrc/peer_collectives.cu``); every rank obtains the same bits.  ``capacity``
+    bounds ``B``.  Construction is collective (symmetric allocation)."""
+
+    def __init__(self, device, group=None, capacity: int = 8192):
+        self.group = group
+        self.rank, self.world = world_info(group)
+        self.capacity = int(capacity)
+        self.device = torch.device(device)
+        self._slots = alloc(2 * self.world * self.capacity, torch.float32, self.device, group)
+        self._flags = alloc(64, torch.int32, self.device, group)
+        self._epoch = 0
+        if self.world > 1:
+            dist.barrier(group=group)       # every rank's buffers are zeroed before anyone's first kernel
+
+    def __call__(self, sharded: Optional[torch.Tensor], replicated: Optional[torch.Tensor], max_norm: float):
+        """-> ``(total, clip)`` with ``total = sum_ranks sharded + replicated``."""
+        from ..ops import _cuda
+
+        ref = sharded if sharded is not None else replicated
+        n = ref.numel()
+        if n > self.capacity:
+            raise ValueError(f"batch of {n} exceeds the reducer's capacity {self.capacity}")
+        self._epoch += 1
+        prep = lambda t: None if t is None else t.float().contiguous()
+        total, clip = _cuda.load().norm_allreduce_clip(self._slots.ptrs, self._flags.ptrs, prep(sharded), prep(replicated),
+                                                       n, self.capacity, self.rank, 0, self._epoch, float(max_norm),
+                                                       self.device)
+        return total, clip

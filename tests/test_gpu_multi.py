@@ -23,3 +23,9 @@ def _launch(script, nproc, timeout=420):
 def test_sharded_engine_multi_gpu():
     out = _launch("dist_sharded_check.py", min(torch.cuda.device_count(), 8))
     assert "sharded check ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_peer_collectives_multi_gpu():
+    out = _launch("dist_tp_check.py", min(torch.cuda.device_count(), 8))
+    assert "tp check ok" in out

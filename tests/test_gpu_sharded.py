@@ -145,3 +145,64 @@ def test_engine_serves_hooks_mode_data_parallel(pg):
     torch.cuda.synchronize()
     for a, b in zip(base.parameters(), twin.parameters()):
         assert torch.allclose(a, b, rtol=1e-4, atol=1e-5), (a - b).abs().max()
+
+
+@pytest.mark.gpu
+def test_peer_norm_reducer_single_rank():
+    from opacus_b200.ops import _cuda
+    from opacus_b200.parallel import symm
+
+    red = symm.PeerNormReducer(torch.device("cuda", 0), capacity=256)
+    a, b = torch.rand(200, device="cuda"), torch.rand(200, device="cuda")
+    for _ in range(3):          # both slot parities
+        total, clip = red(a, b, 1.5)
+        assert torch.equal(total, a + b)
+        torch.testing.assert_close(clip, (1.5 / ((a + b).sqrt() + 1e-6)).clamp(max=1.0))
+    total, _ = red(None, b, 1.0)
+    assert torch.equal(total, b)
+    with pytest.raises(ValueError):
+        red(torch.rand(300, device="cuda"), None, 1.0)
+    _cuda.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 520, 200), (1024, 2048, 1024)])
+def test_gemm_nt_kernel(M, N, K):
+    from opacus_b200.ops import _cuda
+    from opacus_b200.parallel.fused_tp import gemm_nt
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    out = gemm_nt(a, b)
+    assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    _cuda.check_status()
+
+
+@pytest.mark.gpu
+def test_fused_collective_gemms_single_rank():
+    """One-rank group: the copier / slot / flag machinery runs, the collective is the identity."""
+    from opacus_b200.ops import _cuda
+    from opacus_b200.parallel.fused_tp import AllGatherGemm, GemmReduceScatter
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(512, 320, device=dev).bfloat16()
+    w = torch.randn(768, 320, device=dev).bfloat16()
+    ref = x.float() @ w.float().t()
+    ag = AllGatherGemm(512, 320, dev, gather="a")
+    for _ in range(2):
+        ag.shard.copy_(x)
+        y = ag(w)
+        assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+        assert torch.equal(ag.full, x)
+    agb = AllGatherGemm(768, 320, dev, gather="b")
+    agb.shard.copy_(w)
+    y = agb(x)
+    assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    rs = GemmReduceScatter(512, 768, dev)
+    for _ in range(3):
+        y = rs(x, w)
+        assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    _cuda.check_status()
