@@ -142,7 +142,7 @@ struct DpkTpGemm {
   const void* a;
   const void* b;
   void* out;
-  int32_t M, N, K, mode, world, rank, producers;
+  int32_t M, N, K, mode, world, rank, reserved;
   uint32_t epoch;
   const void* shard[8];
   void* slots[8];

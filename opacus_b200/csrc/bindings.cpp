@@ -413,7 +413,7 @@ void tp_gemm(at::Tensor a, at::Tensor b, at::Tensor out, int64_t mode, std::vect
   DpkTpGemm p{};
   p.a = a.data_ptr(); p.b = b.data_ptr(); p.out = out.data_ptr();
   p.M = (int)a.size(0); p.N = (int)b.size(0); p.K = (int)a.size(1);
-  p.mode = (int)mode; p.world = (int)world; p.rank = (int)rank; p.producers = (int)producers;
+  p.mode = (int)mode; p.world = (int)world; p.rank = (int)rank; p.reserved = 0; (void)producers;
   p.epoch = (uint32_t)epoch;
   TORCH_CHECK(out.numel() == (int64_t)(mode == 3 ? p.M / world : p.M) * p.N, "out has the wrong size");
   if (mode != 0) {

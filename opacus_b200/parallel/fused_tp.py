@@ -42,21 +42,17 @@ class AllGatherGemm:
     """``gather="a"``: ``__call__(w)`` returns ``full_x @ w.T`` where rank ``r``'s rows of
     ``full_x`` are what rank ``r`` wrote into its ``shard`` (``[rows_per_rank, K]``).
     ``gather="b"``: ``__call__(x)`` returns ``x @ full_w.T`` likewise for weight rows.
-    ``rows_per_rank`` must be a multiple of 128 (``"a"``) or 256 (``"b"``)."""
+    ``rows_per_rank`` must be a multiple of 128 (``"a"``) or 256 (``"b"``), ``K`` of 32 / 16."""
 
-    def __init__(self, rows_per_rank: int, K: int, device, group=None, gather: str = "a", copiers: int = 12):
+    def __init__(self, rows_per_rank: int, K: int, device, group=None, gather: str = "a"):
         if gather not in ("a", "b"):
             raise ValueError("gather must be 'a' or 'b'")
         self.group = group
         self.rank, self.world = symm.world_info(group)
         self.gather = gather
         self.unit = 128 if gather == "a" else 256
-        if rows_per_rank % self.unit or K % 8:
-            raise ValueError(f"rows_per_rank must be a multiple of {self.unit} and K of 8")
-        unit_bytes = self.unit * K * 2
-        while copiers > 1 and unit_bytes % (copiers * 16):
-            copiers -= 1
-        self.copiers = copiers
+        if rows_per_rank % self.unit or (self.unit * K * 2) % 8192:
+            raise ValueError(f"rows_per_rank must be a multiple of {self.unit} and K of {8192 // (2 * self.unit)}")
         self.rows_per_rank, self.K = rows_per_rank, K
         self.device = torch.device(device)
         self._shard = symm.alloc(rows_per_rank * K, torch.bfloat16, self.device, group)
@@ -76,7 +72,7 @@ class AllGatherGemm:
         self._epoch += 1
         a, b = (self.full, other) if self.gather == "a" else (other, self.full)
         _kernels().tp_gemm(a, b, out, 1 if self.gather == "a" else 2, self._shard.ptrs, [], self._flags.ptrs,
-                           self._ready, self.rank, self.world, self._epoch, self.copiers)
+                           self._ready, self.rank, self.world, self._epoch, 0)
         return out
 
 
