@@ -206,5 +206,81 @@ class TensorParallelDPOptimizer(DPOptimizerFastGradientClipping):
                                     secure_mode=self.secure_mode)
             if not getattr(p, "tp_sharded", False) and std != 0:
                 dist.broadcast(noise, src, group=group)
-            p.grad = (p.summed_grad + noise).view_as(p)
+            p.grad = (p.summed_grad + noise).view_as(p).to(p.dtype)
             _mark_as_processed(p.summed_grad)
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    """Token-wise cross entropy over logits whose vocabulary axis is split across the group."""
+
+    @staticmethod
+    def forward(ctx, logits, target, group, vocab_start):
+        lf = logits.float()
+        m = lf.max(dim=-1).values
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+        e = torch.exp(lf - m[:, None])
+        z = e.sum(dim=-1)
+        local = target - vocab_start
+        mine = (local >= 0) & (local < logits.shape[-1])
+        picked = torch.where(mine, lf.gather(1, local.clamp(0, logits.shape[-1] - 1)[:, None])[:, 0],
+                             torch.zeros_like(m))
+        packed = torch.stack([z, picked])
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        z, picked = packed[0], packed[1]
+        ctx.save_for_backward(e, z, local, mine)
+        ctx.dtype = logits.dtype
+        return torch.log(z) + m - picked
+
+    @staticmethod
+    def backward(ctx, g):
+        e, z, local, mine = ctx.saved_tensors
+        grad = e / z[:, None]
+        rows = torch.nonzero(mine)[:, 0]
+        grad[rows, local[rows]] -= 1.0
+        return (grad * g[:, None]).to(ctx.dtype), None, None, None
+
+
+class VocabParallelCrossEntropy(nn.Module):
+    """``CrossEntropyLoss`` for logits ``[tokens, vocab / world]`` produced by a
+    column-parallel output layer without gathering: only per-token maxima, partition
+    sums and target logits (three ``[tokens]`` vectors) cross the group.  Works as the
+    criterion of ``DPLossFastGradientClipping`` (has ``reduction``)."""
+
+    def __init__(self, process_group=None, reduction: str = "mean"):
+        super().__init__()
+        self.process_group = process_group
+        self.reduction = reduction
+
+    def forward(self, logits, target):
+        rank = dist.get_rank(self.process_group)
+        loss = _VocabParallelCE.apply(logits, target, self.process_group, rank * logits.shape[-1])
+        if self.reduction == "none":
+            return loss
+        return loss.mean() if self.reduction == "mean" else loss.sum()
+
+
+def parallelize_llama(model, process_group=None, shard_lm_head: bool = True):
+    """Turn a :class:`opacus_b200.models.Llama` (replicated, identical on all ranks) into its
+    1-d tensor-parallel form in place: q/k/v/gate/up become column-parallel, o/down
+    row-parallel, heads are divided over the ranks; embedding and norm weights stay
+    replicated; with ``shard_lm_head`` the output layer is split over the vocabulary
+    (use :class:`VocabParallelCrossEntropy`).  Same layout as the reference's plan
+    (``examples/tensor_parallelism_llama.py:104-152``)."""
+    world = _group_size(process_group)
+    for blk in model.layers:
+        att, mlp = blk.self_attn, blk.mlp
+        if att.n_heads % world or att.n_kv % world:
+            raise ValueError(f"{att.n_heads} query / {att.n_kv} key-value heads do not divide over {world} ranks")
+        for name in ("q_proj", "k_proj", "v_proj"):
+            setattr(att, name, ColumnParallelLinear.from_linear(getattr(att, name), process_group))
+        att.o_proj = RowParallelLinear.from_linear(att.o_proj, process_group)
+        att.n_heads //= world
+        att.n_kv //= world
+        for name in ("gate_proj", "up_proj"):
+            setattr(mlp, name, ColumnParallelLinear.from_linear(getattr(mlp, name), process_group))
+        mlp.down_proj = RowParallelLinear.from_linear(mlp.down_proj, process_group)
+    if shard_lm_head:
+        if model.lm_head.weight is model.embed_tokens.weight:
+            raise ValueError("a tied output layer cannot be sharded over the vocabulary")
+        model.lm_head = ColumnParallelLinear.from_linear(model.lm_head, process_group)
+    return model

@@ -220,3 +220,72 @@ def _absent_rank_job(rank, world):
 def test_missing_rank_is_detected_by_timeout():
     res = _run(_absent_rank_job, timeout_s=5)
     assert res[1] == "left" and res[0].startswith("error")
+
+
+# ------------------------------------------------------------------ tensor-parallel Llama + vocabulary-parallel loss
+def _tiny_llama():
+    from opacus_b200.models import Llama, LlamaConfig
+
+    torch.manual_seed(3)
+    return Llama(LlamaConfig(vocab_size=96, d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=64,
+                             tie_embeddings=False))
+
+
+def _llama_ids():
+    g = torch.Generator().manual_seed(11)
+    return torch.randint(0, 96, (3, 9), generator=g)
+
+
+def _tp_llama_job(rank, world):
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClippingTP
+    from opacus_b200.parallel.tensor_parallel import (TensorParallelDPOptimizer, VocabParallelCrossEntropy,
+                                                      parallelize_llama)
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    model = parallelize_llama(_tiny_llama())
+    ids = _llama_ids()
+    gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=0.05, single_pass=True)
+    opt = TensorParallelDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                    max_grad_norm=0.05, expected_batch_size=3)
+    crit = DPLossFastGradientClipping(gsm, opt, VocabParallelCrossEntropy(), "mean")
+    opt.zero_grad()
+    logits = gsm(ids[:, :-1])
+    loss = crit(logits.flatten(0, 1), ids[:, 1:].reshape(-1), shape=(3, 8))
+    value = loss.item()
+    loss.backward()
+    opt.step()
+    return value, gsm.per_sample_gradient_norms.clone(), {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def test_tensor_parallel_llama_matches_unsharded():
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    got = _run(_tp_llama_job, timeout_s=120)
+    model = _tiny_llama()
+    ids = _llama_ids()
+    gsm = GradSampleModuleFastGradientClipping(model, max_grad_norm=0.05, single_pass=True)
+    opt = DPOptimizerFastGradientClipping(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                          max_grad_norm=0.05, expected_batch_size=3)
+    crit = DPLossFastGradientClipping(gsm, opt, nn.CrossEntropyLoss(), "mean")
+    opt.zero_grad()
+    loss = crit(gsm(ids[:, :-1]).flatten(0, 1), ids[:, 1:].reshape(-1), shape=(3, 8))
+    value = loss.item()
+    loss.backward()
+    norms = gsm.per_sample_gradient_norms.clone()
+    opt.step()
+    want = model.state_dict()
+    for rank in range(2):
+        v, n, sd = got[rank]
+        assert abs(v - value) < 1e-5
+        assert torch.allclose(n, norms, rtol=1e-4, atol=1e-6), rank
+        for name, full in want.items():
+            mine = sd[name]
+            if mine.shape == full.shape:
+                ref = full
+            elif mine.shape[0] != full.shape[0]:
+                ref = full.chunk(2, 0)[rank]          # column-parallel: output features split
+            else:
+                ref = full.chunk(2, 1)[rank]          # row-parallel: input features split
+            assert torch.allclose(mine, ref, atol=2e-6), (rank, name)
