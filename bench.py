@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--engine", default="sharded", choices=["sharded", "plain"],
                     help="ours: sharded data-parallel engine (default) or, on one GPU, the plain ghost path")
+    ap.add_argument("--ce", default="fused", choices=["fused", "torch"],
+                    help="ours: FusedCrossEntropyLoss on bf16 logits, or nn.CrossEntropyLoss on logits.float()")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a benchmark)")
     ap.add_argument("--vocab", type=int, default=None, help="debug only")
     ap.add_argument("--seq", type=int, default=SEQ, help="debug only")
@@ -153,15 +155,24 @@ def build_ours(args, rank, world):
     ds = TensorDataset(torch.zeros(n_data, 1, dtype=torch.long))     # only its length matters (sample rate)
     dl = DataLoader(ds, batch_size=args.batch * world)
     engine = PrivacyEngine(accountant="rdp")
+    fused_ce = args.ce == "fused"
+    if fused_ce:
+        from opacus_b200.layers import FusedCrossEntropyLoss
+
+        base_criterion = FusedCrossEntropyLoss()      # fp32 loss straight from the bf16 logits, bf16 gradient
+    else:
+        base_criterion = nn.CrossEntropyLoss()
     module, optimizer, criterion, _ = engine.make_private(
-        module=module, optimizer=optimizer, criterion=nn.CrossEntropyLoss(), data_loader=dl,
+        module=module, optimizer=optimizer, criterion=base_criterion, data_loader=dl,
         noise_multiplier=SIGMA, max_grad_norm=CLIP, grad_sample_mode=mode, poisson_sampling=False)
 
     def step(ids, labels):
         optimizer.zero_grad(set_to_none=True)
         with torch.autocast("cuda", dtype=torch.bfloat16):
             logits = module(ids)
-        loss = criterion(logits.float().view(-1, logits.shape[-1]), labels.reshape(-1), shape=(ids.shape[0], ids.shape[1]))
+        if not fused_ce:
+            logits = logits.float()
+        loss = criterion(logits.view(-1, logits.shape[-1]), labels.reshape(-1), shape=(ids.shape[0], ids.shape[1]))
         loss.backward()
         optimizer.step()
         return loss.detach()

@@ -152,6 +152,15 @@ struct DpkTpGemm {
 };
 int dpk_tp_gemm(const struct DpkTpGemm* p, cudaStream_t stream);
 
+// Token-wise cross entropy from [rows, V] logits (kind: 0 fp32, 1 bf16, 2 fp16).  forward: loss[r], lse[r];
+// backward: dlogits = (softmax - onehot) * grad_loss[r] in the logits' precision.  Rows with target ==
+// ignore_index give loss 0 / gradient 0.
+int dpk_cross_entropy_forward(const void* logits, int kind, const int64_t* target, int64_t rows, int64_t V,
+                              int64_t ignore_index, float* loss, float* lse, cudaStream_t stream);
+int dpk_cross_entropy_backward(const void* logits, int kind, const int64_t* target, const float* lse,
+                               const float* grad_loss, int64_t rows, int64_t V, int64_t ignore_index, void* dlogits,
+                               cudaStream_t stream);
+
 // Standard normal samples (testing the generator): out[i] for i < n.
 int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream);
 

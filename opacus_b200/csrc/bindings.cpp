@@ -436,6 +436,38 @@ void tp_gemm(at::Tensor a, at::Tensor b, at::Tensor out, int64_t mode, std::vect
   check(dpk_tp_gemm(&p, stream()), "tp_gemm");
 }
 
+// logits [rows, V] (fp32 / bf16 / fp16, contiguous), target int64 [rows] -> {loss fp32 [rows], lse fp32 [rows]}
+std::vector<at::Tensor> cross_entropy_forward(at::Tensor logits, at::Tensor target, int64_t ignore_index) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  need_cuda_contig(logits, "logits");
+  need_cuda_contig(target, "target");
+  TORCH_CHECK(logits.dim() == 2 && target.dim() == 1 && target.size(0) == logits.size(0), "logits [rows, V], target [rows]");
+  TORCH_CHECK(target.scalar_type() == at::kLong, "target must be int64");
+  at::Tensor loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  at::Tensor lse = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  check(dpk_cross_entropy_forward(logits.data_ptr(), elem_kind(logits), target.data_ptr<int64_t>(), logits.size(0),
+                                  logits.size(1), ignore_index, loss.data_ptr<float>(), lse.data_ptr<float>(), stream()),
+        "cross_entropy_forward");
+  return {loss, lse};
+}
+
+at::Tensor cross_entropy_backward(at::Tensor logits, at::Tensor target, at::Tensor lse, at::Tensor grad_loss,
+                                  int64_t ignore_index) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  need_cuda_contig(logits, "logits");
+  need_cuda_contig(target, "target");
+  need_cuda_contig(lse, "lse");
+  need_cuda_contig(grad_loss, "grad_loss");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && grad_loss.scalar_type() == at::kFloat &&
+              lse.numel() == logits.size(0) && grad_loss.numel() == logits.size(0), "lse / grad_loss: fp32 [rows]");
+  at::Tensor dx = at::empty_like(logits);
+  check(dpk_cross_entropy_backward(logits.data_ptr(), elem_kind(logits), target.data_ptr<int64_t>(),
+                                   lse.data_ptr<float>(), grad_loss.data_ptr<float>(), logits.size(0), logits.size(1),
+                                   ignore_index, dx.data_ptr(), stream()),
+        "cross_entropy_backward");
+  return dx;
+}
+
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
   at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
@@ -468,6 +500,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sharded_dp_step", &sharded_dp_step);
   m.def("norm_allreduce_clip", &norm_allreduce_clip);
   m.def("tp_gemm", &tp_gemm);
+  m.def("cross_entropy_forward", &cross_entropy_forward);
+  m.def("cross_entropy_backward", &cross_entropy_backward);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
   m.def("tensor_entry_size", &tensor_entry_size);

@@ -84,3 +84,15 @@ def test_dp_mha_matches_torch():
         ya, wa = a(x, x, x, need_weights=need)
         yb, wb = b(x, x, x, need_weights=need)
         assert torch.allclose(ya, yb, atol=1e-5)
+
+
+def test_fused_cross_entropy_cpu_fallback():
+    from opacus_b200.layers import FusedCrossEntropyLoss
+
+    torch.manual_seed(0)
+    logits = torch.randn(6, 11, requires_grad=True)
+    target = torch.tensor([1, 2, -100, 4, 0, 10])
+    for red in ("none", "mean", "sum"):
+        got = FusedCrossEntropyLoss(reduction=red)(logits, target)
+        want = torch.nn.functional.cross_entropy(logits, target, reduction=red)
+        torch.testing.assert_close(got, want)

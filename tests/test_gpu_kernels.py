@@ -330,3 +330,31 @@ def test_conv1d_implicit_and_rules():
     bref = (g.float().sum(2) * coef[:, None]).sum(0)
     torch.testing.assert_close(wg[conv.bias], bref, rtol=1e-2, atol=1e-1)
     _cuda.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,V", [(torch.bfloat16, 4096), (torch.float32, 1000), (torch.bfloat16, 1003), (torch.float16, 512)])
+def test_fused_cross_entropy_matches_fp32(dtype, V):
+    from opacus_b200.layers import FusedCrossEntropyLoss
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    N = 37
+    logits = (torch.randn(N, V, device="cuda") * 3).to(dtype).requires_grad_(True)
+    target = torch.randint(0, V, (N,), device="cuda")
+    target[5] = -100
+    crit = FusedCrossEntropyLoss(reduction="none")
+    loss = crit(logits, target)
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, target, reduction="none")
+    torch.testing.assert_close(loss, ref, rtol=1e-4, atol=1e-4)
+    w = torch.rand(N, device="cuda")
+    (loss * w).sum().backward()
+    (ref * w).sum().backward()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert logits.grad.dtype == dtype
+    assert (logits.grad.float() - ref_in.grad).abs().max() <= tol
+    assert logits.grad[5].abs().max() == 0
+    mean = FusedCrossEntropyLoss()(logits.detach(), target)
+    torch.testing.assert_close(mean, torch.nn.functional.cross_entropy(ref_in.detach(), target), rtol=1e-4, atol=1e-4)
+    _cuda.check_status()
