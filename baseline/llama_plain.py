@@ -1,0 +1,121 @@
+"""Plain-PyTorch Llama-3 style decoder used ONLY by the reference arm of ``bench.py``
+(``--impl reference``): nn.Embedding / nn.Linear / nn.RMSNorm modules, rotary embeddings in the
+usual rotate-half form, ``scaled_dot_product_attention``, SwiGLU.  It imports nothing from
+``opacus_b200`` so that the reference library runs on stock PyTorch modules only.
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 128256
+    d_model: int = 2048
+    n_layers: int = 16
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    ffn_dim: int = 8192
+    rope_theta: float = 500000.0
+    norm_eps: float = 1e-5
+    tie_embeddings: bool = True
+
+
+def llama_1b_config(**kw) -> LlamaConfig:
+    """Llama-3.2-1B shape."""
+    return LlamaConfig(**kw)
+
+
+def llama_8b_config(**kw) -> LlamaConfig:
+    """Llama-3-8B shape."""
+    base = dict(d_model=4096, n_layers=32, n_heads=32, n_kv_heads=8, ffn_dim=14336, tie_embeddings=False)
+    base.update(kw)
+    return LlamaConfig(**base)
+
+
+def _rope_tables(T: int, head_dim: int, theta: float, device, dtype):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.outer(torch.arange(T, device=device, dtype=torch.float32), inv)      # [T, hd/2]
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
+def _apply_rope(x, cos, sin):
+    # x: [B, H, T, hd]; rotate pairs (first half, second half)
+    h = x.shape[-1] // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.n_heads, self.n_kv = cfg.n_heads, cfg.n_kv_heads
+        self.hd = cfg.d_model // cfg.n_heads
+        self.theta = cfg.rope_theta
+        self.q_proj = nn.Linear(cfg.d_model, cfg.n_heads * self.hd, bias=False)
+        self.k_proj = nn.Linear(cfg.d_model, cfg.n_kv_heads * self.hd, bias=False)
+        self.v_proj = nn.Linear(cfg.d_model, cfg.n_kv_heads * self.hd, bias=False)
+        self.o_proj = nn.Linear(cfg.n_heads * self.hd, cfg.d_model, bias=False)
+
+    def forward(self, x):
+        B, T, _ = x.shape
+        q = self.q_proj(x).view(B, T, self.n_heads, self.hd).transpose(1, 2)
+        k = self.k_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
+        v = self.v_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
+        cos, sin = _rope_tables(T, self.hd, self.theta, x.device, q.dtype)
+        q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv != self.n_heads)
+        return self.o_proj(y.transpose(1, 2).reshape(B, T, self.n_heads * self.hd))
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.gate_proj = nn.Linear(cfg.d_model, cfg.ffn_dim, bias=False)
+        self.up_proj = nn.Linear(cfg.d_model, cfg.ffn_dim, bias=False)
+        self.down_proj = nn.Linear(cfg.ffn_dim, cfg.d_model, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.input_layernorm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.self_attn = Attention(cfg)
+        self.post_attention_layernorm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.mlp = MLP(cfg)
+
+    def forward(self, x):
+        x = x + self.self_attn(self.input_layernorm(x))
+        return x + self.mlp(self.post_attention_layernorm(x))
+
+
+class Llama(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.layers = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
+        self.norm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.lm_head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+        self.apply(self._init)
+        if cfg.tie_embeddings:
+            self.lm_head.weight = self.embed_tokens.weight
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, std=0.02)
+
+    def forward(self, ids):
+        x = self.embed_tokens(ids)
+        for blk in self.layers:
+            x = blk(x)
+        return self.lm_head(self.norm(x))
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())

@@ -107,9 +107,15 @@ def setup_dist(n):
     return rank, local, world
 
 
-def make_model(args, tie: bool):
-    sys.path.insert(0, REPO)
-    from opacus_b200.models import Llama, llama_1b_config
+def make_model(args, tie: bool, plain: bool = False):
+    """Llama-3.2-1B-shaped model.  ``plain``: the stand-alone stock-PyTorch definition under
+    ``baseline/`` (reference arm: nothing of this package on its path); otherwise this package's model."""
+    if plain:
+        sys.path.insert(0, os.path.join(REPO, "baseline"))
+        from llama_plain import Llama, llama_1b_config
+    else:
+        sys.path.insert(0, REPO)
+        from opacus_b200.models import Llama, llama_1b_config
 
     kw = {}
     if args.layers:
@@ -190,7 +196,7 @@ def build_reference(args, rank, world):
     from torch.utils.data import DataLoader, TensorDataset
 
     # ghost clipping in the reference rejects shared parameters, so the embedding is untied
-    model, cfg = make_model(args, tie=False)
+    model, cfg = make_model(args, tie=False, plain=True)
     mode = "ghost"
     module = model
     if world > 1:

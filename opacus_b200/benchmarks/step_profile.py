@@ -19,6 +19,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--engine", default="sharded", choices=["sharded", "plain"])
+    ap.add_argument("--ce", default="fused", choices=["fused", "torch"])
     ap.add_argument("--cprofile", type=int, default=0, help="profile the host side of this many steps instead")
     args = ap.parse_args()
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))

@@ -468,6 +468,45 @@ at::Tensor cross_entropy_backward(at::Tensor logits, at::Tensor target, at::Tens
   return dx;
 }
 
+// x contiguous 4-d: [B, T, H, hd] (to_heads) or [B, H, T, hd]; returns the other layout, rotated
+at::Tensor rope(at::Tensor x, double theta, bool to_heads, double sign) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 4, "x must be 4-d");
+  const int64_t B = x.size(0), hd = x.size(3);
+  const int64_t T = to_heads ? x.size(1) : x.size(2), H = to_heads ? x.size(2) : x.size(1);
+  at::Tensor out = to_heads ? at::empty({B, H, T, hd}, x.options()) : at::empty({B, T, H, hd}, x.options());
+  check(dpk_rope(x.data_ptr(), out.data_ptr(), elem_kind(x), B, T, H, (int)hd, (float)theta, to_heads ? 1 : 0,
+                 (float)sign, stream()),
+        "rope");
+  return out;
+}
+
+at::Tensor swiglu_forward(at::Tensor gate, at::Tensor up) {
+  c10::cuda::CUDAGuard guard(gate.device());
+  need_cuda_contig(gate, "gate");
+  need_cuda_contig(up, "up");
+  TORCH_CHECK(gate.sizes() == up.sizes() && gate.scalar_type() == up.scalar_type(), "gate and up must match");
+  at::Tensor h = at::empty_like(gate);
+  check(dpk_swiglu_forward(gate.data_ptr(), up.data_ptr(), h.data_ptr(), elem_kind(gate), gate.numel(), stream()),
+        "swiglu_forward");
+  return h;
+}
+
+std::vector<at::Tensor> swiglu_backward(at::Tensor gate, at::Tensor up, at::Tensor dh) {
+  c10::cuda::CUDAGuard guard(gate.device());
+  need_cuda_contig(gate, "gate");
+  need_cuda_contig(up, "up");
+  need_cuda_contig(dh, "dh");
+  TORCH_CHECK(gate.sizes() == up.sizes() && gate.sizes() == dh.sizes() && gate.scalar_type() == up.scalar_type() &&
+              gate.scalar_type() == dh.scalar_type(), "gate, up and dh must match");
+  at::Tensor dg = at::empty_like(gate), du = at::empty_like(gate);
+  check(dpk_swiglu_backward(gate.data_ptr(), up.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(),
+                            elem_kind(gate), gate.numel(), stream()),
+        "swiglu_backward");
+  return {dg, du};
+}
+
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
   at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
@@ -502,6 +541,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_gemm", &tp_gemm);
   m.def("cross_entropy_forward", &cross_entropy_forward);
   m.def("cross_entropy_backward", &cross_entropy_backward);
+  m.def("rope", &rope);
+  m.def("swiglu_forward", &swiglu_forward);
+  m.def("swiglu_backward", &swiglu_backward);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
   m.def("tensor_entry_size", &tensor_entry_size);

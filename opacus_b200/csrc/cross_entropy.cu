@@ -10,70 +10,13 @@
 // reduction="none").  Rows whose target equals ignore_index give loss 0 and gradient 0.
 #include "api.h"
 #include "common.cuh"
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
+#include "vec8.cuh"
 
 namespace dpk {
 
 namespace {
 
 constexpr int CE_THREADS = 512;
-
-template <int KIND>
-__device__ __forceinline__ void ce_load8(const void* base, int64_t idx, float (&v)[8]) {
-  if constexpr (KIND == 0) {
-    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
-    const float4 a = p[0], b = p[1];
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      if constexpr (KIND == 1) {
-        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[q]);
-        v[2 * q] = __bfloat162float(h.x); v[2 * q + 1] = __bfloat162float(h.y);
-      } else {
-        const __half2 h = *reinterpret_cast<const __half2*>(&w[q]);
-        v[2 * q] = __half2float(h.x); v[2 * q + 1] = __half2float(h.y);
-      }
-    }
-  }
-}
-template <int KIND>
-__device__ __forceinline__ float ce_load1(const void* base, int64_t idx) {
-  if constexpr (KIND == 0) return reinterpret_cast<const float*>(base)[idx];
-  else if constexpr (KIND == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
-  else return __half2float(reinterpret_cast<const __half*>(base)[idx]);
-}
-template <int KIND>
-__device__ __forceinline__ void ce_store8(void* base, int64_t idx, const float (&v)[8]) {
-  if constexpr (KIND == 0) {
-    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx);
-    p[0] = make_float4(v[0], v[1], v[2], v[3]);
-    p[1] = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-    uint4 pk;
-    uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      if constexpr (KIND == 1) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-        w[q] = *reinterpret_cast<const uint32_t*>(&h);
-      } else {
-        const __half2 h = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
-        w[q] = *reinterpret_cast<const uint32_t*>(&h);
-      }
-    }
-    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + idx) = pk;
-  }
-}
-template <int KIND>
-__device__ __forceinline__ void ce_store1(void* base, int64_t idx, float v) {
-  if constexpr (KIND == 0) reinterpret_cast<float*>(base)[idx] = v;
-  else if constexpr (KIND == 1) reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16(v);
-  else reinterpret_cast<__half*>(base)[idx] = __float2half(v);
-}
 
 // (m, s) <- combination of two partial softmax states: value = s * exp(m)
 __device__ __forceinline__ void ce_merge(float& m, float& s, float m2, float s2) {
@@ -93,7 +36,7 @@ ce_forward_kernel(const void* x, const int64_t* target, int64_t V, int64_t ignor
   if (vec) {
     for (int64_t i = (int64_t)threadIdx.x * 8; i < V; i += (int64_t)CE_THREADS * 8) {
       float v[8];
-      ce_load8<KIND>(x, base + i, v);
+      vload8<KIND>(x, base + i, v);
       float mx = v[0];
 #pragma unroll
       for (int q = 1; q < 8; ++q) mx = fmaxf(mx, v[q]);
@@ -103,7 +46,7 @@ ce_forward_kernel(const void* x, const int64_t* target, int64_t V, int64_t ignor
     }
   } else {
     for (int64_t i = threadIdx.x; i < V; i += CE_THREADS) {
-      const float v = ce_load1<KIND>(x, base + i);
+      const float v = vload1<KIND>(x, base + i);
       if (v > m) { s *= __expf(m - v); m = v; }
       s += __expf(v - m);
     }
@@ -128,7 +71,7 @@ ce_forward_kernel(const void* x, const int64_t* target, int64_t V, int64_t ignor
       const float l = m + __logf(s);
       const int64_t t = target[row];
       lse[row] = l;
-      loss[row] = (t == ignore_index || t < 0 || t >= V) ? 0.f : l - ce_load1<KIND>(x, base + t);
+      loss[row] = (t == ignore_index || t < 0 || t >= V) ? 0.f : l - vload1<KIND>(x, base + t);
     }
   }
 }
@@ -147,14 +90,14 @@ ce_backward_kernel(const void* x, const int64_t* target, const float* lse, const
   if (vec) {
     for (int64_t i = (int64_t)threadIdx.x * 8; i < V; i += (int64_t)CE_THREADS * 8) {
       float v[8];
-      ce_load8<KIND>(x, base + i, v);
+      vload8<KIND>(x, base + i, v);
 #pragma unroll
       for (int q = 0; q < 8; ++q) v[q] = (__expf(v[q] - l) - ((i + q == t) ? 1.f : 0.f)) * gr;
-      ce_store8<KIND>(dx, base + i, v);
+      vstore8<KIND>(dx, base + i, v);
     }
   } else {
     for (int64_t i = threadIdx.x; i < V; i += CE_THREADS)
-      ce_store1<KIND>(dx, base + i, (__expf(ce_load1<KIND>(x, base + i) - l) - ((i == t) ? 1.f : 0.f)) * gr);
+      vstore1<KIND>(dx, base + i, (__expf(vload1<KIND>(x, base + i) - l) - ((i == t) ? 1.f : 0.f)) * gr);
   }
 }
 

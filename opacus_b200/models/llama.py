@@ -1,7 +1,9 @@
 """Llama-3 style decoder (RMSNorm, rotary embeddings, grouped-query attention,
 SwiGLU) written so that DP training applies directly: every parameter lives in
 an ``nn.Linear``, ``nn.Embedding`` or ``nn.RMSNorm``, and there are no buffers
-(the rotary tables are recomputed on the fly, which costs microseconds).
+(the rotary angles are evaluated on the fly).  On CUDA the rotary embedding
+(with the head transpose) and the SwiGLU gate run as fused kernels of this
+package (``csrc/rope.cu``, ``csrc/swiglu.cu``); on CPU as plain PyTorch.
 
 The same definition is used for this package and for the reference library in
 the benchmarks; only ``tie_embeddings`` differs (ghost clipping in the
@@ -52,6 +54,60 @@ def _apply_rope(x, cos, sin):
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
 
 
+class _FusedRope(torch.autograd.Function):
+    """Rotary embedding + ``[B, T, H, hd] -> [B, H, T, hd]`` in one kernel each way (``csrc/rope.cu``)."""
+
+    @staticmethod
+    def forward(ctx, x, theta):
+        from ..ops import _cuda
+
+        ctx.theta = float(theta)
+        return _cuda.load().rope(x.contiguous(), ctx.theta, True, 1.0)
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops import _cuda
+
+        return _cuda.load().rope(g.contiguous(), ctx.theta, False, -1.0), None
+
+
+class _FusedSwiGLU(torch.autograd.Function):
+    """``silu(gate) * up`` and its gradient as one kernel each (``csrc/swiglu.cu``)."""
+
+    @staticmethod
+    def forward(ctx, gate, up):
+        from ..ops import _cuda
+
+        gate, up = gate.contiguous(), up.contiguous()
+        ctx.save_for_backward(gate, up)
+        return _cuda.load().swiglu_forward(gate, up)
+
+    @staticmethod
+    def backward(ctx, dh):
+        from ..ops import _cuda
+
+        gate, up = ctx.saved_tensors
+        dg, du = _cuda.load().swiglu_backward(gate, up, dh.contiguous())
+        return dg, du
+
+
+_KERNEL_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
+
+
+def rope_to_heads(x, theta: float):
+    """``x [B, T, H, hd]`` -> rotated ``[B, H, T, hd]``."""
+    if x.is_cuda and x.dtype in _KERNEL_DTYPES and x.shape[-1] % 16 == 0:
+        return _FusedRope.apply(x, theta)
+    cos, sin = _rope_tables(x.shape[1], x.shape[-1], theta, x.device, x.dtype)
+    return _apply_rope(x.transpose(1, 2), cos, sin)
+
+
+def swiglu(gate, up):
+    if gate.is_cuda and gate.dtype in _KERNEL_DTYPES and gate.dtype == up.dtype and gate.numel() % 8 == 0:
+        return _FusedSwiGLU.apply(gate, up)
+    return F.silu(gate) * up
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
@@ -65,11 +121,9 @@ class Attention(nn.Module):
 
     def forward(self, x):
         B, T, _ = x.shape
-        q = self.q_proj(x).view(B, T, self.n_heads, self.hd).transpose(1, 2)
-        k = self.k_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
+        q = rope_to_heads(self.q_proj(x).view(B, T, self.n_heads, self.hd), self.theta)
+        k = rope_to_heads(self.k_proj(x).view(B, T, self.n_kv, self.hd), self.theta)
         v = self.v_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
-        cos, sin = _rope_tables(T, self.hd, self.theta, x.device, q.dtype)
-        q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv != self.n_heads)
         return self.o_proj(y.transpose(1, 2).reshape(B, T, self.n_heads * self.hd))
 
@@ -82,7 +136,7 @@ class MLP(nn.Module):
         self.down_proj = nn.Linear(cfg.ffn_dim, cfg.d_model, bias=False)
 
     def forward(self, x):
-        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        return self.down_proj(swiglu(self.gate_proj(x), self.up_proj(x)))
 
 
 class Block(nn.Module):

@@ -358,3 +358,37 @@ def test_fused_cross_entropy_matches_fp32(dtype, V):
     mean = FusedCrossEntropyLoss()(logits.detach(), target)
     torch.testing.assert_close(mean, torch.nn.functional.cross_entropy(ref_in.detach(), target), rtol=1e-4, atol=1e-4)
     _cuda.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_rope_and_swiglu_match_torch(dtype):
+    from opacus_b200.models.llama import _apply_rope, _rope_tables, rope_to_heads, swiglu
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    B, T, H, hd = 2, 37, 4, 64
+    x = torch.randn(B, T, H, hd, device="cuda", dtype=dtype, requires_grad=True)
+    y = rope_to_heads(x, 500000.0)
+    xr = x.detach().float().requires_grad_(True)
+    cos, sin = _rope_tables(T, hd, 500000.0, x.device, torch.float32)
+    yr = _apply_rope(xr.transpose(1, 2), cos, sin)
+    assert y.shape == yr.shape and y.is_contiguous()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert (y.float() - yr).abs().max() <= tol
+    w = torch.randn_like(yr)
+    (y.float() * w).sum().backward()
+    (yr * w).sum().backward()
+    assert x.grad.shape == x.shape and (x.grad.float() - xr.grad).abs().max() <= tol
+
+    g = torch.randn(5, 7, 64, device="cuda", dtype=dtype, requires_grad=True)
+    u = torch.randn(5, 7, 64, device="cuda", dtype=dtype, requires_grad=True)
+    h = swiglu(g, u)
+    gr, ur = g.detach().float().requires_grad_(True), u.detach().float().requires_grad_(True)
+    hr = torch.nn.functional.silu(gr) * ur
+    assert (h.float() - hr).abs().max() <= tol * 4
+    w = torch.randn_like(hr)
+    (h.float() * w).sum().backward()
+    (hr * w).sum().backward()
+    assert (g.grad.float() - gr.grad).abs().max() <= tol * 4 and (u.grad.float() - ur.grad).abs().max() <= tol * 4
+    _cuda.check_status()
