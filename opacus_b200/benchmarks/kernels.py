@@ -108,6 +108,33 @@ def run(op, B, T, din, dout, iters=20):
         byts = n * 4.0 * 8        # read+write of param, grad, exp_avg, exp_avg_sq
         ms = _time(one, iters, flush)
         rows.append(("fused_dp_adamw_step", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    if op in ("cross_entropy", "all"):
+        from ..layers import fused_cross_entropy
+
+        V = 128256
+        logits = torch.randn(B * T, V, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        tgt = torch.randint(0, V, (B * T,), device=dev)
+        gl = torch.rand(B * T, device=dev)
+        ms = _time(lambda: C.cross_entropy_forward(logits.detach(), tgt, -100), iters, flush)
+        byts = logits.numel() * 2.0
+        rows.append(("cross_entropy forward (bf16 logits, V=128256)", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+        loss, lse = C.cross_entropy_forward(logits.detach(), tgt, -100)
+        ms = _time(lambda: C.cross_entropy_backward(logits.detach(), tgt, lse, gl, -100), iters, flush)
+        rows.append(("cross_entropy backward", ms, 2 * byts / ms / 1e6, "GB/s", 2 * byts / ms / 1e6 / bw_peak))
+        del logits
+    if op in ("rope", "all"):
+        x = torch.randn(B, T, 32, 64, device=dev, dtype=torch.bfloat16)
+        byts = x.numel() * 4.0
+        ms = _time(lambda: C.rope(x, 500000.0, False, False, 1.0), iters, flush)
+        rows.append(("rope (32 heads x 64)", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    if op in ("swiglu", "all"):
+        ga = torch.randn(B * T, dout, device=dev, dtype=torch.bfloat16)
+        up = torch.randn(B * T, dout, device=dev, dtype=torch.bfloat16)
+        byts = ga.numel() * 2.0
+        ms = _time(lambda: C.swiglu_forward(ga, up), iters, flush)
+        rows.append(("swiglu forward", ms, 3 * byts / ms / 1e6, "GB/s", 3 * byts / ms / 1e6 / bw_peak))
+        ms = _time(lambda: C.swiglu_backward(ga, up, ga), iters, flush)
+        rows.append(("swiglu backward", ms, 5 * byts / ms / 1e6, "GB/s", 5 * byts / ms / 1e6 / bw_peak))
     _cuda.check_status()
     print(f"shape B={B} T={T} d_in={din} d_out={dout}; peaks: {tf_peak} TFLOP/s bf16, {bw_peak} GB/s ({src})")
     for name, ms, rate, unit, frac in rows:

@@ -161,11 +161,10 @@ int dpk_cross_entropy_backward(const void* logits, int kind, const int64_t* targ
                                const float* grad_loss, int64_t rows, int64_t V, int64_t ignore_index, void* dlogits,
                                cudaStream_t stream);
 
-// Rotary embedding fused with the head transpose.  to_heads = 1: in [B, T, H, hd] -> out [B, H, T, hd];
-// to_heads = 0: in [B, H, T, hd] -> out [B, T, H, hd].  sign = +1 rotates, -1 rotates back (the gradient).
-// hd must be a multiple of 16; both pointers 16-byte aligned.
-int dpk_rope(const void* in, void* out, int kind, int64_t B, int64_t T, int64_t H, int hd, float theta, int to_heads,
-             float sign, cudaStream_t stream);
+// Rotary embedding.  Source / destination are token-major [B, T, H, hd] (flag 0) or head-major [B, H, T, hd]
+// (flag 1).  sign = +1 rotates, -1 rotates back (the gradient).  hd a multiple of 16; pointers 16-byte aligned.
+int dpk_rope(const void* in, void* out, int kind, int64_t B, int64_t T, int64_t H, int hd, float theta, int src_heads,
+             int dst_heads, float sign, cudaStream_t stream);
 
 // SwiGLU: h = silu(gate) * up over n elements (n a multiple of 8, 16-byte aligned), and its gradient.
 int dpk_swiglu_forward(const void* gate, const void* up, void* h, int kind, int64_t n, cudaStream_t stream);

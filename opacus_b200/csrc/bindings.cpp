@@ -468,16 +468,17 @@ at::Tensor cross_entropy_backward(at::Tensor logits, at::Tensor target, at::Tens
   return dx;
 }
 
-// x contiguous 4-d: [B, T, H, hd] (to_heads) or [B, H, T, hd]; returns the other layout, rotated
-at::Tensor rope(at::Tensor x, double theta, bool to_heads, double sign) {
+// x contiguous 4-d, token-major [B, T, H, hd] or (src_heads) head-major [B, H, T, hd]; returns the rotated tensor
+// in token-major or (dst_heads) head-major layout
+at::Tensor rope(at::Tensor x, double theta, bool src_heads, bool dst_heads, double sign) {
   c10::cuda::CUDAGuard guard(x.device());
   need_cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 4, "x must be 4-d");
   const int64_t B = x.size(0), hd = x.size(3);
-  const int64_t T = to_heads ? x.size(1) : x.size(2), H = to_heads ? x.size(2) : x.size(1);
-  at::Tensor out = to_heads ? at::empty({B, H, T, hd}, x.options()) : at::empty({B, T, H, hd}, x.options());
-  check(dpk_rope(x.data_ptr(), out.data_ptr(), elem_kind(x), B, T, H, (int)hd, (float)theta, to_heads ? 1 : 0,
-                 (float)sign, stream()),
+  const int64_t T = src_heads ? x.size(2) : x.size(1), H = src_heads ? x.size(1) : x.size(2);
+  at::Tensor out = dst_heads ? at::empty({B, H, T, hd}, x.options()) : at::empty({B, T, H, hd}, x.options());
+  check(dpk_rope(x.data_ptr(), out.data_ptr(), elem_kind(x), B, T, H, (int)hd, (float)theta, src_heads ? 1 : 0,
+                 dst_heads ? 1 : 0, (float)sign, stream()),
         "rope");
   return out;
 }

@@ -177,7 +177,14 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
   const DpkShardedStep& p = *ph;
   if (p.world < 1 || p.world > 8 || p.rank < 0 || p.rank >= p.world || (p.slice_len & 7) || (p.slice_begin & 7))
     return cudaErrorInvalidValue;
-  int grid = num_sms();                       // one resident block per SM: every block can spin safely
+  // every block spins on flags, so all of them must be resident at once: as many per SM as fit
+  static int per_sm_cached = 0;
+  if (per_sm_cached == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sharded_step_kernel, kShThreads, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm_cached = n > 4 ? 4 : n;
+  }
+  int grid = num_sms() * per_sm_cached;
   const int64_t nvec = p.slice_len >> 3;
   const int64_t need = (nvec + kShThreads - 1) / kShThreads;
   if (need < grid) grid = need < 1 ? 1 : (int)need;

@@ -55,20 +55,26 @@ def _apply_rope(x, cos, sin):
 
 
 class _FusedRope(torch.autograd.Function):
-    """Rotary embedding + ``[B, T, H, hd] -> [B, H, T, hd]`` in one kernel each way (``csrc/rope.cu``)."""
+    """Rotary embedding of a token-major ``[B, T, H, hd]`` tensor in one kernel each way (``csrc/rope.cu``)."""
 
     @staticmethod
     def forward(ctx, x, theta):
         from ..ops import _cuda
 
         ctx.theta = float(theta)
-        return _cuda.load().rope(x.contiguous(), ctx.theta, True, 1.0)
+        return _cuda.load().rope(x.contiguous(), ctx.theta, False, False, 1.0)
 
     @staticmethod
     def backward(ctx, g):
         from ..ops import _cuda
 
-        return _cuda.load().rope(g.contiguous(), ctx.theta, False, -1.0), None
+        C = _cuda.load()
+        if g.is_contiguous():
+            return C.rope(g, ctx.theta, False, False, -1.0), None
+        gh = g.transpose(1, 2)                 # attention may hand the gradient back head-major
+        if gh.is_contiguous():
+            return C.rope(gh, ctx.theta, True, False, -1.0), None
+        return C.rope(g.contiguous(), ctx.theta, False, False, -1.0), None
 
 
 class _FusedSwiGLU(torch.autograd.Function):
@@ -94,12 +100,12 @@ class _FusedSwiGLU(torch.autograd.Function):
 _KERNEL_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 
-def rope_to_heads(x, theta: float):
-    """``x [B, T, H, hd]`` -> rotated ``[B, H, T, hd]``."""
+def rope(x, theta: float):
+    """Rotary embedding of ``x [B, T, H, hd]`` (token-major in, token-major out)."""
     if x.is_cuda and x.dtype in _KERNEL_DTYPES and x.shape[-1] % 16 == 0:
         return _FusedRope.apply(x, theta)
     cos, sin = _rope_tables(x.shape[1], x.shape[-1], theta, x.device, x.dtype)
-    return _apply_rope(x.transpose(1, 2), cos, sin)
+    return _apply_rope(x.transpose(1, 2), cos, sin).transpose(1, 2)
 
 
 def swiglu(gate, up):
@@ -121,8 +127,10 @@ class Attention(nn.Module):
 
     def forward(self, x):
         B, T, _ = x.shape
-        q = rope_to_heads(self.q_proj(x).view(B, T, self.n_heads, self.hd), self.theta)
-        k = rope_to_heads(self.k_proj(x).view(B, T, self.n_kv, self.hd), self.theta)
+        # everything stays token-major in memory; attention gets [B, H, T, hd] *views*, so neither the
+        # inputs nor the output of attention are ever transposed by a copy
+        q = rope(self.q_proj(x).view(B, T, self.n_heads, self.hd), self.theta).transpose(1, 2)
+        k = rope(self.k_proj(x).view(B, T, self.n_kv, self.hd), self.theta).transpose(1, 2)
         v = self.v_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv != self.n_heads)
         return self.o_proj(y.transpose(1, 2).reshape(B, T, self.n_heads * self.hd))

@@ -363,20 +363,20 @@ def test_fused_cross_entropy_matches_fp32(dtype, V):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_fused_rope_and_swiglu_match_torch(dtype):
-    from opacus_b200.models.llama import _apply_rope, _rope_tables, rope_to_heads, swiglu
+    from opacus_b200.models.llama import _apply_rope, _rope_tables, rope, swiglu
     from opacus_b200.ops import _cuda
 
     torch.manual_seed(0)
     B, T, H, hd = 2, 37, 4, 64
     x = torch.randn(B, T, H, hd, device="cuda", dtype=dtype, requires_grad=True)
-    y = rope_to_heads(x, 500000.0)
+    y = rope(x, 500000.0)
     xr = x.detach().float().requires_grad_(True)
     cos, sin = _rope_tables(T, hd, 500000.0, x.device, torch.float32)
-    yr = _apply_rope(xr.transpose(1, 2), cos, sin)
+    yr = _apply_rope(xr.transpose(1, 2), cos, sin).transpose(1, 2)
     assert y.shape == yr.shape and y.is_contiguous()
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     assert (y.float() - yr).abs().max() <= tol
-    w = torch.randn_like(yr)
+    w = torch.randn(yr.shape, device="cuda")
     (y.float() * w).sum().backward()
     (yr * w).sum().backward()
     assert x.grad.shape == x.shape and (x.grad.float() - xr.grad).abs().max() <= tol
