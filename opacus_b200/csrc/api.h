@@ -39,6 +39,13 @@ int dpk_conv_psg(const void* x, const void* g, int B, int C, int H, int W, int O
                  int sh, int sw, int ph, int pw, int dh, int dw, int reduce_batch, void* out, int out_bf16,
                  float beta, float* norm_sq, uint32_t* status, cudaStream_t stream);
 
+// Cross term of the per-sample gradient norm for a weight tied between an embedding and an output projection:
+// out[n] (+)= scale * sum_{t,s} g_h[n, s, ids[n, t]] * <g_e[n, t, :], a_h[n, s, :]>   (g_e, a_h bf16 [B, T, D];
+// g_h bf16 or fp32 [B, T, V]).  scratch: 2 * B * ceil(T/128)^2 floats.  D a multiple of 8.
+int dpk_tied_cross_norm(const int64_t* ids, const void* g_e, const void* a_h, const void* g_h, int g_h_fp32, int B,
+                        int T, int D, int64_t V, float scale, float* scratch, float* out, int accumulate,
+                        uint32_t* status, cudaStream_t stream);
+
 // ---- elementwise / reduction kernels
 // y[r, :] = bf16(x[r, :] * c[r / rows_per_sample] * scale)
 int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, int64_t rows, int64_t cols,

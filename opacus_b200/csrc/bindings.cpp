@@ -193,6 +193,43 @@ void conv_psg(at::Tensor x, at::Tensor g, std::vector<int64_t> conv, bool reduce
         "conv_psg");
 }
 
+// ids [B, T] int64; g_e, a_h [B, T, D] bf16; g_h [B, T, V] bf16 / fp32 -> out [B] fp32 (added to `total` if given)
+at::Tensor tied_cross_norm(at::Tensor ids, at::Tensor g_e, at::Tensor a_h, at::Tensor g_h, double scale,
+                           c10::optional<at::Tensor> total) {
+  c10::cuda::CUDAGuard guard(g_e.device());
+  raise_if_failed(g_e.get_device());
+  need_cuda_contig(ids, "ids");
+  need_cuda_contig(g_e, "g_e");
+  need_cuda_contig(a_h, "a_h");
+  need_cuda_contig(g_h, "g_h");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.dim() == 2, "ids must be int64 [B, T]");
+  TORCH_CHECK(g_e.scalar_type() == at::kBFloat16 && a_h.scalar_type() == at::kBFloat16, "g_e and a_h must be bf16");
+  TORCH_CHECK(g_h.scalar_type() == at::kBFloat16 || g_h.scalar_type() == at::kFloat, "g_h must be bf16 or fp32");
+  const int B = ids.size(0), T = ids.size(1);
+  TORCH_CHECK(g_e.dim() == 3 && a_h.dim() == 3 && g_h.dim() == 3 && g_e.size(0) == B && g_e.size(1) == T &&
+              a_h.size(0) == B && a_h.size(1) == T && g_h.size(0) == B && g_h.size(1) == T &&
+              a_h.size(2) == g_e.size(2), "shapes: g_e, a_h [B, T, D], g_h [B, T, V]");
+  const int D = g_e.size(2);
+  const int64_t V = g_h.size(2);
+  const int64_t nT = (T + 127) / 128;
+  at::Tensor scratch = at::empty({2 * (int64_t)B * nT * nT}, g_e.options().dtype(at::kFloat));
+  at::Tensor out;
+  int accumulate = 0;
+  if (total.has_value()) {
+    TORCH_CHECK(total->is_cuda() && total->scalar_type() == at::kFloat && total->is_contiguous() && total->numel() == B,
+                "total must be a contiguous fp32 CUDA vector of B elements");
+    out = *total;
+    accumulate = 1;
+  } else {
+    out = at::empty({B}, g_e.options().dtype(at::kFloat));
+  }
+  check(dpk_tied_cross_norm(ids.data_ptr<int64_t>(), g_e.data_ptr(), a_h.data_ptr(), g_h.data_ptr(),
+                            g_h.scalar_type() == at::kFloat, B, T, D, V, (float)scale, scratch.data_ptr<float>(),
+                            out.data_ptr<float>(), accumulate, status_for(g_e.get_device()).dev, stream()),
+        "tied_cross_norm");
+  return out;
+}
+
 at::Tensor scale_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t rows_per_sample, double scale) {
   c10::cuda::CUDAGuard guard(x.device());
   need_cuda_contig(x, "x");
@@ -528,6 +565,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wgrad_tn", &wgrad_tn);
   m.def("wgrad_tn_ex", &wgrad_tn_ex);
   m.def("conv_psg", &conv_psg);
+  m.def("tied_cross_norm", &tied_cross_norm);
   m.def("scale_rows", &scale_rows);
   m.def("clip_factor", &clip_factor);
   m.def("row_norm_sq", &row_norm_sq);

@@ -35,6 +35,11 @@ struct GramParams {
   int B, T, nT, pairs, items;
   int kb_x, kb_g;          // k-blocks for the two Grams (kb_x == 0: no X operand)
   int mask_mode;           // X X^T := [id_t == id_s]
+  int cross_mode;          // tied embedding / output layer: rows from map_x (G_E), columns from map_g (A_H),
+                           // every (t-block, s-block) pair, product weighted by gather_src[n, s, ids[n, t]]
+  const void* gather_src;  // [B, T, V] output-layer gradient (cross_mode)
+  int64_t V;
+  int gather_fp32;
   int want_w, want_b;
   float* scratch;          // [items][2]
   const int64_t* ids;      // [B, T] when mask_mode
@@ -68,9 +73,14 @@ __device__ __forceinline__ bool group_all_ok(bool mine) {
   return any_bad == 0;
 }
 
-__device__ __forceinline__ void decode_item(int item, int pairs, int nT, int& n, int& tb, int& sb) {
+__device__ __forceinline__ void decode_item(int item, int pairs, int nT, int cross, int& n, int& tb, int& sb) {
   n = item / pairs;
   int p = item - n * pairs;
+  if (cross) {
+    tb = p / nT;
+    sb = p - tb * nT;
+    return;
+  }
   tb = 0;
   while (p >= nT - tb) {
     p -= nT - tb;
@@ -121,7 +131,7 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         int n, tb, sb;
-        decode_item(item, p.pairs, p.nT, n, tb, sb);
+        decode_item(item, p.pairs, p.nT, p.cross_mode, n, tb, sb);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           const CUtensorMap* map = kb < p.kb_x ? &map_x : &map_g;
@@ -129,7 +139,7 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           uint8_t* dst = smem + stage * kStageBytes;
           mbar_expect_tx(&bars->full[stage], kStageBytes);
           tma_load_3d(dst, map, &bars->full[stage], k0, tb * kTile, n);
-          tma_load_3d(dst + kTileBytes, map, &bars->full[stage], k0, sb * kTile, n);
+          tma_load_3d(dst + kTileBytes, p.cross_mode ? &map_g : map, &bars->full[stage], k0, sb * kTile, n);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -182,9 +192,13 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       int n, tb, sb;
-      decode_item(item, p.pairs, p.nT, n, tb, sb);
+      decode_item(item, p.pairs, p.nT, p.cross_mode, n, tb, sb);
       int64_t my_id = -1;
-      if (p.mask_mode) {
+      if (p.cross_mode) {
+        const int t = tb * kTile + row;
+        my_id = t < p.T ? p.ids[(int64_t)n * p.T + t] : -1;
+        if (my_id >= p.V) my_id = -1;
+      } else if (p.mask_mode) {
         const int t = tb * kTile + row;
         const int s = sb * kTile + row;
         my_id = t < p.T ? p.ids[(int64_t)n * p.T + t] : -1 - (int64_t)t;
@@ -202,6 +216,24 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
         uint32_t rg[32];
+        if (p.cross_mode) {
+          tmem_ld_32x32(t_x + c0, rg);
+          tmem_ld_wait();
+          if (my_id >= 0) {
+            const int s0 = sb * kTile + c0;
+            const int64_t base = ((int64_t)n * p.T + s0) * p.V + my_id;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (s0 + j < p.T) {
+                const float w = p.gather_fp32
+                                    ? reinterpret_cast<const float*>(p.gather_src)[base + (int64_t)j * p.V]
+                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.gather_src)[base + (int64_t)j * p.V]);
+                sum_w = fmaf(__uint_as_float(rg[j]), w, sum_w);
+              }
+            }
+          }
+          continue;
+        }
         tmem_ld_32x32(t_g + c0, rg);
         if (p.mask_mode) {
           tmem_ld_wait();
@@ -241,7 +273,7 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (ew == 0 && lane == 0) {
-        const float wgt = (tb == sb) ? 1.f : 2.f;
+        const float wgt = (tb == sb || p.cross_mode) ? 1.f : 2.f;
         float w = 0.f, b = 0.f;
         for (int i = 0; i < 4; ++i) {
           w += bars->warp_sum[i][0];
@@ -264,7 +296,7 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
 // out[n] (+)= scale * sum over the sample's items, in item order.
 __global__ void gram_reduce_kernel(const float* scratch, int B, int pairs, float scale, float* out_w, float* out_b,
-                                   int accumulate, const uint32_t* status) {
+                                   int accumulate, const uint32_t* status, int signed_sum = 0) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= B) return;
   float w = 0.f, b = 0.f;
@@ -273,7 +305,7 @@ __global__ void gram_reduce_kernel(const float* scratch, int B, int pairs, float
     b += scratch[2 * ((int64_t)n * pairs + j) + 1];
   }
   if (status != nullptr && status[0] != 0) { w = nanf(""); b = nanf(""); }
-  if (out_w) out_w[n] = (accumulate ? out_w[n] : 0.f) + fmaxf(w, 0.f) * scale + (w != w ? w : 0.f);
+  if (out_w) out_w[n] = (accumulate ? out_w[n] : 0.f) + (signed_sum ? w : fmaxf(w, 0.f)) * scale + (w != w ? w : 0.f);
   if (out_b) out_b[n] = (accumulate ? out_b[n] : 0.f) + fmaxf(b, 0.f) * scale + (b != b ? b : 0.f);
 }
 
@@ -338,4 +370,43 @@ extern "C" int dpk_gram_pair_norm(const void* x, const int64_t* ids, const void*
                                   float scale, float* scratch, float* out_w, float* out_b, int accumulate,
                                   uint32_t* status, cudaStream_t stream) {
   return dpk_gram_pair_launch(x, ids, g, B, T, d_x, d_g, scale, scratch, out_w, out_b, accumulate, status, stream);
+}
+
+// 2 <g_E, g_H> of a weight shared by an embedding (ids, output gradient g_e [B, T, D]) and an output projection
+// (input a_h [B, T, D], output gradient g_h [B, T, V]):  out[n] (+)= scale * sum_{t,s} g_h[n, s, ids[n, t]] * <g_e[n, t], a_h[n, s]>.
+// scratch: 2 * B * ceil(T/128)^2 floats.
+extern "C" int dpk_tied_cross_norm(const int64_t* ids, const void* g_e, const void* a_h, const void* g_h, int g_h_fp32,
+                                   int B, int T, int D, int64_t V, float scale, float* scratch, float* out,
+                                   int accumulate, uint32_t* status, cudaStream_t stream) {
+  if (B <= 0 || T <= 0 || D <= 0 || (D % 8) != 0 || V <= 0) return cudaErrorInvalidValue;
+  GramParams p{};
+  p.B = B;
+  p.T = T;
+  p.nT = (T + kTile - 1) / kTile;
+  p.pairs = p.nT * p.nT;
+  p.items = B * p.pairs;
+  p.kb_x = (D + kBK - 1) / kBK;
+  p.kb_g = 0;
+  p.cross_mode = 1;
+  p.want_w = 1;
+  p.scratch = scratch;
+  p.ids = ids;
+  p.gather_src = g_h;
+  p.gather_fp32 = g_h_fp32;
+  p.V = V;
+  p.status = status;
+  CUtensorMap map_x, map_g;
+  int rc = make_tmap_3d_bf16(&map_x, g_e, D, T, B, kBK, kTile);
+  if (rc) return rc;
+  rc = make_tmap_3d_bf16(&map_g, a_h, D, T, B, kBK, kTile);
+  if (rc) return rc;
+  const size_t smem = 1024 + kStages * kStageBytes + sizeof(GramBarriers);
+  cudaError_t e = cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int grid = p.items < num_sms() ? p.items : num_sms();
+  gram_pair_kernel<<<grid, kThreads, smem, stream>>>(map_x, map_g, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  gram_reduce_kernel<<<(B + 127) / 128, 128, 0, stream>>>(scratch, B, p.pairs, scale, out, nullptr, accumulate, status, 1);
+  return cudaGetLastError();
 }

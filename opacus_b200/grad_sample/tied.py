@@ -43,6 +43,13 @@ def _embedding_linear(p, s_emb, s_lin):
     ids = ids.reshape(B, -1)                                  # [B, T]
     g_e = s_emb.backprops.reshape(B, ids.shape[1], -1)        # [B, T, D]
     a_h, g_h = _bt(s_lin.inputs[0]), _bt(s_lin.backprops)     # [B, S, D], [B, S, V]
+    if (g_e.is_cuda and g_e.dtype == torch.bfloat16 and a_h.shape[:2] == g_e.shape[:2] and g_h.shape[:2] == g_e.shape[:2]
+            and g_e.shape[2] % 8 == 0 and g_h.dtype in (torch.bfloat16, torch.float32)):
+        # one tensor-core kernel: tiles of G_E A_H^T weighted by gathered output-layer gradients, nothing materialised
+        from ..ops import _cuda
+
+        return _cuda.load().tied_cross_norm(ids.contiguous(), g_e.contiguous(), a_h.to(torch.bfloat16).contiguous(),
+                                            g_h.contiguous(), float(s_emb.g_scale * s_lin.g_scale), None)
     picked = torch.gather(g_h, 2, ids[:, None, :].expand(-1, g_h.shape[1], -1))   # [B, S, T]
     inner = torch.bmm(a_h.to(g_e.dtype), g_e.transpose(1, 2))                     # [B, S, T]
     return (picked.float() * inner.float()).sum(dim=(1, 2)) * (s_emb.g_scale * s_lin.g_scale)

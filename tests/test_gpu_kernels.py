@@ -392,3 +392,27 @@ def test_fused_rope_and_swiglu_match_torch(dtype):
     (hr * w).sum().backward()
     assert (g.grad.float() - gr.grad).abs().max() <= tol * 4 and (u.grad.float() - ur.grad).abs().max() <= tol * 4
     _cuda.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,D,V", [(3, 128, 64, 500), (2, 200, 72, 1000), (4, 384, 256, 4096)])
+def test_tied_cross_norm_kernel(B, T, D, V):
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    ids = torch.randint(0, V, (B, T), device="cuda")
+    g_e = torch.randn(B, T, D, device="cuda").bfloat16()
+    a_h = torch.randn(B, T, D, device="cuda").bfloat16()
+    g_h = (torch.randn(B, T, V, device="cuda") * 0.1).bfloat16()
+    got = _cuda.load().tied_cross_norm(ids, g_e, a_h, g_h, 1.5, None)
+    # dense oracle: <scatter(G_E by ids), G_H^T A_H> per sample, fp32
+    want = torch.empty(B, device="cuda")
+    for b in range(B):
+        ge = torch.zeros(V, D, device="cuda").index_add_(0, ids[b], g_e[b].float())
+        gh = g_h[b].float().t() @ a_h[b].float()
+        want[b] = 1.5 * (ge * gh).sum()
+    torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    total = torch.ones(B, device="cuda")
+    _cuda.load().tied_cross_norm(ids, g_e, a_h, g_h, 1.5, total)
+    torch.testing.assert_close(total, want + 1.0, rtol=2e-2, atol=2e-2 * want.abs().max().item())
+    _cuda.check_status()
