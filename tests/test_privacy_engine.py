@@ -1,6 +1,7 @@
 """End-to-end behaviour of PrivacyEngine / DPOptimizer on CPU
 (model of ``opacus/tests/privacy_engine_test.py``)."""
 import io
+import os
 import math
 
 import pytest
@@ -286,3 +287,62 @@ def test_dp_optimizer_is_transparent_to_state_dict():
     _train((m, opt, dl), 1)
     assert isinstance(opt, DPOptimizer)
     assert opt.state_dict().keys() == opt.original_optimizer.state_dict().keys()
+
+
+# ------------------------------------------------------------------ checkpoint interchange with the reference library
+_REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+
+_INTERCHANGE_SCRIPT = r"""
+import sys, torch, torch.nn as nn
+from torch.utils.data import DataLoader, TensorDataset
+lib, action, path = sys.argv[1], sys.argv[2], sys.argv[3]
+if lib == "reference":
+    sys.path.insert(0, sys.argv[4])
+    from opacus import PrivacyEngine
+else:
+    from opacus_b200 import PrivacyEngine
+torch.manual_seed(0)
+model = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 3))
+opt = torch.optim.Adam(model.parameters(), lr=0.01)
+g = torch.Generator().manual_seed(1)
+ds = TensorDataset(torch.randn(32, 6, generator=g), torch.randint(0, 3, (32,), generator=g))
+pe = PrivacyEngine(accountant="rdp")
+m, o, dl = pe.make_private(module=model, optimizer=opt, data_loader=DataLoader(ds, batch_size=8),
+                           noise_multiplier=1.1, max_grad_norm=1.0, poisson_sampling=False)
+if action == "save":
+    for x, y in dl:
+        o.zero_grad(); nn.functional.cross_entropy(m(x), y).backward(); o.step()
+    pe.save_checkpoint(path=path, module=m, optimizer=o, checkpoint_dict={"epoch": 7})
+    print("EPS", pe.get_epsilon(1e-5), "W", float(m._module[0].weight.sum()))
+else:
+    rest = pe.load_checkpoint(path=path, module=m, optimizer=o)
+    st = o.state_dict()["state"]
+    print("EPS", pe.get_epsilon(1e-5), "W", float(m._module[0].weight.sum()), "EPOCH", rest["epoch"],
+          "STEPS", int(st[0]["step"]) if len(st) else -1)
+"""
+
+
+def _interchange(lib, action, path):
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    res = subprocess.run([sys.executable, "-c", _INTERCHANGE_SCRIPT, lib, action, path, _REF], capture_output=True,
+                         text=True, timeout=300, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("EPS")][-1].split()
+    return {line[i]: float(line[i + 1]) for i in range(0, len(line), 2)}
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(_REF, "opacus")), reason="reference library not installed")
+@pytest.mark.parametrize("writer,reader", [("reference", "ours"), ("ours", "reference")])
+def test_checkpoint_interchange_with_reference(tmp_path, writer, reader):
+    """A checkpoint written by either library restores weights, optimizer state, the
+    accountant history (same epsilon) and the user's entries in the other."""
+    path = str(tmp_path / "ckpt.pt")
+    saved = _interchange(writer, "save", path)
+    loaded = _interchange(reader, "load", path)
+    assert abs(saved["EPS"] - loaded["EPS"]) < 1e-9
+    assert abs(saved["W"] - loaded["W"]) < 1e-6
+    assert loaded["EPOCH"] == 7 and loaded["STEPS"] == 4
