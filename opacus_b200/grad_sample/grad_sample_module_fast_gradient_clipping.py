@@ -225,7 +225,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             from .grad_sample_module import _get_batch_size
 
             module.max_batch_len = _get_batch_size(module=module, batch_dim=batch_dim)
-        n = module.max_batch_len
+        # the module may see only a share of the batch (activations sharded over samples)
+        n = module.max_batch_len * self._batch_share(module)
         activations = module.activations.pop()
         if self.loss_reduction == "mean":
             g_scale = float(n)
@@ -238,6 +239,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             activations = [t.transpose(0, batch_dim) if isinstance(t, torch.Tensor) else t for t in activations]
             backprops = backprops.transpose(0, batch_dim)
         activations = [t.to_local() if hasattr(t, "to_local") else t for t in activations]
+
+        activations, backprops = self._prepare_site(module, activations, backprops)
 
         uses = 1
         if isinstance(module, _STACKED_TYPES) and self._has_rule(module):
@@ -280,10 +283,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         for p, v in norm_sq.items():
             if not p.requires_grad:
                 continue
-            v = v.float()
-            if v.shape[0] < (self._batch_len or 0):  # short step of a packed sequence
-                v = torch.cat([v, v.new_zeros(self._batch_len - v.shape[0])])
-            self._add_norm_sq(p, v)
+            self._add_norm_sq(p, self._align_norm(p, v.float()))
         for _, p in trainable_parameters(module):
             self._uses.setdefault(p, []).append(site)
             p._forward_counter -= uses
@@ -293,6 +293,25 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
     # Built-in rules may add their norms straight into ``_norm_sq_total`` inside the
     # kernel; subclasses that need to tell parameters apart switch this off.
     _use_total_fastpath = True
+
+    # ---- extension points for parallel layouts (identity here)
+    def _batch_share(self, module) -> int:
+        """How many times larger the whole batch is than what ``module`` sees."""
+        return 1
+
+    def _prepare_site(self, module, activations, backprops):
+        """Last chance to exchange the captured tensors (e.g. gather a sharded output gradient)."""
+        return activations, backprops
+
+    def _align_norm(self, p, v):
+        """Bring a squared-norm vector to batch length (a short step of a packed sequence is padded at the end)."""
+        if v.shape[0] < (self._batch_len or 0):
+            v = torch.cat([v, v.new_zeros(self._batch_len - v.shape[0])])
+        return v
+
+    def _site_coef(self, site, coef):
+        """Clip factors of the samples that ``site`` holds."""
+        return coef[: site.backprops.shape[0]].to(site.backprops.device)
 
     def _add_norm_sq(self, p, v):
         """Account the squared per-sample norm ``v`` of parameter ``p``."""
@@ -344,7 +363,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         coef = self.get_clipping_coef()
         for site in self._sites:
             mtype = self._get_module_type(site.module)
-            c = coef[: site.backprops.shape[0]].to(site.backprops.device)
+            c = self._site_coef(site, coef)
             if site.kept_grad_samples is not None:
                 grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]]) for p, gs in site.kept_grad_samples.items()}
             elif mtype in self.WGRAD_SAMPLERS and not self.force_functorch:

@@ -72,12 +72,48 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
     # ---- single-pass bookkeeping: sharded and replicated parameters are kept apart
     _use_total_fastpath = False
 
+    # ---- activations sharded over samples between the tensor-parallel blocks (sequence parallelism)
+    def _world(self) -> int:
+        return torch.distributed.get_world_size(self.process_group)
+
+    def _batch_share(self, module) -> int:
+        return self._world() if getattr(module, "sp_local_input", False) else 1
+
+    def _prepare_site(self, module, activations, backprops):
+        full_in = module.__dict__.pop("_dp_activation", None)
+        if full_in is not None:                       # the layer gathered its input itself
+            activations = [full_in.detach()] + list(activations[1:])
+        if getattr(module, "scatter_output", False):  # the output gradient arrives for this rank's samples only
+            from ..parallel.tensor_parallel import _all_gather0
+
+            backprops = _all_gather0(backprops, self.process_group)
+            module.__dict__["_sp_grad_full"] = backprops
+        return activations, backprops
+
+    def _local_slice(self, n_local: int) -> slice:
+        r = self._group_rank()
+        return slice(r * n_local, (r + 1) * n_local)
+
+    def _align_norm(self, p, v):
+        if getattr(p, "sp_local", False) and self._batch_len and v.shape[0] * self._world() == self._batch_len:
+            out = v.new_zeros(self._batch_len)
+            out[self._local_slice(v.shape[0])] = v
+            return out
+        return super()._align_norm(p, v)
+
+    def _site_coef(self, site, coef):
+        n = site.backprops.shape[0]
+        if getattr(site.module, "sp_local_region", False) and n * self._world() == coef.shape[0]:
+            return coef[self._local_slice(n)].to(site.backprops.device)
+        return super()._site_coef(site, coef)
+
     def _reset_single_pass_state(self):
         super()._reset_single_pass_state()
         self._norm_sq_replicated = None
 
     def _add_norm_sq(self, p, v):
-        if getattr(p, "merge_flag", False):
+        if getattr(p, "merge_flag", False) or getattr(p, "sp_local", False):
+            # sharded weights and sample-local parameters: every rank holds a partial value, sum over the group
             super()._add_norm_sq(p, v)
         else:
             self._norm_sq_replicated = v.clone() if self._norm_sq_replicated is None else \

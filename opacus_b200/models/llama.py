@@ -124,8 +124,11 @@ class Attention(nn.Module):
         self.k_proj = nn.Linear(cfg.d_model, cfg.n_kv_heads * self.hd, bias=False)
         self.v_proj = nn.Linear(cfg.d_model, cfg.n_kv_heads * self.hd, bias=False)
         self.o_proj = nn.Linear(cfg.n_heads * self.hd, cfg.d_model, bias=False)
+        self.sp_gather = None     # set by parallelize_llama(sequence_parallel=True): [B / world, T, D] -> [B, T, D]
 
     def forward(self, x):
+        if self.sp_gather is not None:
+            x = self.sp_gather(x)
         B, T, _ = x.shape
         # everything stays token-major in memory; attention gets [B, H, T, hd] *views*, so neither the
         # inputs nor the output of attention are ever transposed by a copy
@@ -142,8 +145,11 @@ class MLP(nn.Module):
         self.gate_proj = nn.Linear(cfg.d_model, cfg.ffn_dim, bias=False)
         self.up_proj = nn.Linear(cfg.d_model, cfg.ffn_dim, bias=False)
         self.down_proj = nn.Linear(cfg.ffn_dim, cfg.d_model, bias=False)
+        self.sp_gather = None
 
     def forward(self, x):
+        if self.sp_gather is not None:
+            x = self.sp_gather(x)
         return self.down_proj(swiglu(self.gate_proj(x), self.up_proj(x)))
 
 
@@ -168,6 +174,7 @@ class Llama(nn.Module):
         self.layers = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
         self.norm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
         self.lm_head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+        self.sp_slice = None      # set by parallelize_llama(sequence_parallel=True): this rank's samples
         self.apply(self._init)
         if cfg.tie_embeddings:
             self.lm_head.weight = self.embed_tokens.weight
@@ -178,6 +185,8 @@ class Llama(nn.Module):
             nn.init.normal_(m.weight, std=0.02)
 
     def forward(self, ids):
+        if self.sp_slice is not None:
+            ids = self.sp_slice(ids)
         x = self.embed_tokens(ids)
         for blk in self.layers:
             x = blk(x)

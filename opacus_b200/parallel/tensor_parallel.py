@@ -90,34 +90,209 @@ def _group_size(group) -> int:
     return dist.get_world_size(group)
 
 
+def _all_gather0(x: torch.Tensor, group) -> torch.Tensor:
+    """Concatenation of every rank's ``x`` along dim 0."""
+    x = x.contiguous()
+    world = _group_size(group)
+    if x.is_cuda:
+        out = x.new_empty((world * x.shape[0],) + tuple(x.shape[1:]))
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x, group=group)
+    return torch.cat(parts, dim=0)
+
+
+def _reduce_scatter0(x: torch.Tensor, group) -> torch.Tensor:
+    """This rank's dim-0 chunk of the sum of every rank's ``x``."""
+    x = x.contiguous()
+    world, rank = _group_size(group), dist.get_rank(group)
+    if x.is_cuda:
+        out = x.new_empty((x.shape[0] // world,) + tuple(x.shape[1:]))
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+    x = x.clone()
+    dist.all_reduce(x, group=group)
+    return x.chunk(world, dim=0)[rank].contiguous()
+
+
+class _GatherSamples(torch.autograd.Function):
+    """All-gather over the sample axis in forward, reduce-scatter of the gradient in backward:
+    the boundary from the sample-sharded region (residual stream, norms) into a tensor-parallel block."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _all_gather0(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter0(g, ctx.group), None
+
+
+class SampleGather(nn.Module):
+    """``[B / world, ...] -> [B, ...]`` (see :class:`_GatherSamples`)."""
+
+    def __init__(self, process_group=None):
+        super().__init__()
+        self.process_group = process_group
+
+    def forward(self, x):
+        return _GatherSamples.apply(x, self.process_group)
+
+
+class SampleSlice(nn.Module):
+    """This rank's share of the batch: ``[B, ...] -> [B / world, ...]`` (no gradient flows through token ids)."""
+
+    def __init__(self, process_group=None):
+        super().__init__()
+        self.process_group = process_group
+
+    def forward(self, x):
+        world, rank = _group_size(self.process_group), dist.get_rank(self.process_group)
+        if x.shape[0] % world:
+            raise ValueError(f"batch of {x.shape[0]} does not divide over {world} tensor-parallel ranks")
+        return x.chunk(world, dim=0)[rank]
+
+
+def _fused_ok(x: torch.Tensor, rows: int, unit: int, world: int) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and rows % (unit * world) == 0
+
+
+class _GatherLinear(torch.autograd.Function):
+    """``y = all_gather(x_local) W^T`` as ONE kernel on NVLink-connected GPUs (``AllGatherGemm``): the peers'
+    rows are pulled while the tensor cores already work on the rows that arrived.  Backward: input
+    gradient by GEMM + reduce-scatter; the weight gradient only when autograd asks for it."""
+
+    @staticmethod
+    def forward(ctx, x, weight, layer):
+        group = layer.process_group
+        world = _group_size(group)
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        rows, K = x2.shape
+        full = None
+        if layer.fused and _fused_ok(x2, rows * world, 128, world) and weight.dtype == torch.bfloat16 \
+                and (128 * K * 2) % 8192 == 0 and weight.shape[0] % 8 == 0:
+            from .fused_tp import AllGatherGemm
+
+            ag = layer.__dict__.get("_ag")
+            if ag is None or ag.rows_per_rank != rows or ag.K != K:
+                ag = AllGatherGemm(rows, K, x.device, group, gather="a")
+                layer.__dict__["_ag"] = ag
+            ag.shard.copy_(x2)
+            y = ag(weight.detach().contiguous())
+            full = ag.full
+        else:
+            full = _all_gather0(x2, group)
+            y = full @ weight.t()
+        full_shape = (lead[0] * world,) + tuple(lead[1:])
+        layer.__dict__["_dp_activation"] = full.view(full_shape + (K,))
+        ctx.save_for_backward(full, weight)
+        ctx.group, ctx.x_shape = group, x.shape
+        return y.view(full_shape + (weight.shape[0],))
+
+    @staticmethod
+    def backward(ctx, gy):
+        full, weight = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = _reduce_scatter0(g2 @ weight, ctx.group).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = g2.t() @ full
+        return gx, gw, None
+
+
+class _LinearScatter(torch.autograd.Function):
+    """``y_local = reduce_scatter(x W^T)`` over the sample axis as ONE kernel (``GemmReduceScatter``): finished
+    output tiles are pushed to their owner while the rest is computed.  Backward gathers the output gradient
+    (or takes the copy the per-sample-gradient rule already gathered)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, layer):
+        group = layer.process_group
+        world = _group_size(group)
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        M = x2.shape[0]
+        if layer.fused and _fused_ok(x2, M, 128, world) and weight.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 \
+                and x2.shape[1] % 8 == 0:
+            from .fused_tp import GemmReduceScatter
+
+            rs = layer.__dict__.get("_rs")
+            if rs is None or rs.M != M or rs.N != weight.shape[0]:
+                rs = GemmReduceScatter(M, weight.shape[0], x.device, group)
+                layer.__dict__["_rs"] = rs
+            y = rs(x2.contiguous(), weight.detach().contiguous())
+        else:
+            y = _reduce_scatter0(x2 @ weight.t(), group)
+        ctx.save_for_backward(x2, weight)
+        ctx.group, ctx.layer, ctx.x_shape = group, layer, x.shape
+        return y.view((lead[0] // world,) + tuple(lead[1:]) + (weight.shape[0],))
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        g_full = ctx.layer.__dict__.pop("_sp_grad_full", None)
+        if g_full is None:
+            g_full = _all_gather0(gy.reshape(-1, gy.shape[-1]), ctx.group)
+        g2 = g_full.reshape(-1, g_full.shape[-1])
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = (g2 @ weight).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = g2.t() @ x2
+        return gx, gw, None
+
+
 class ColumnParallelLinear(nn.Linear):
     """``y[..., shard] = x W_shard^T + b_shard``: this rank owns rows
     ``[rank*out/W, (rank+1)*out/W)`` of the full weight.  ``x`` is replicated.
     With ``gather_output`` the shards of ``y`` are concatenated on every rank."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, process_group=None,
-                 gather_output: bool = False, device=None, dtype=None):
+                 gather_output: bool = False, input_mode: str = "replicated", fused: bool = True, device=None,
+                 dtype=None):
         world = _group_size(process_group)
         if out_features % world:
             raise ValueError(f"out_features={out_features} is not divisible by the group size {world}")
+        if input_mode not in ("replicated", "gathered", "local"):
+            raise ValueError("input_mode must be 'replicated', 'gathered' or 'local'")
         super().__init__(in_features, out_features // world, bias=bias, device=device, dtype=dtype)
         self.process_group = process_group
         self.gather_output = gather_output
         self.full_out_features = out_features
+        # "replicated": every rank holds the same input, the input gradient is all-reduced;
+        # "gathered":   the input was produced by SampleGather (its backward reduce-scatters), nothing to add;
+        # "local":      the input holds this rank's samples only and the layer gathers it itself, fused with
+        #               the GEMM when ``fused`` and the shapes allow
+        self.input_mode = input_mode
+        self.fused = fused
+        self.sp_local_input = input_mode == "local"
         self.weight.tp_sharded = True
         if self.bias is not None:
             self.bias.tp_sharded = True
 
     def forward(self, x):
-        y = F.linear(_CopyToGroup.apply(x, self.process_group), self.weight, self.bias)
+        if self.input_mode == "local":
+            y = _GatherLinear.apply(x, self.weight, self)
+            if self.bias is not None:
+                y = y + self.bias
+        elif self.input_mode == "gathered":
+            y = F.linear(x, self.weight, self.bias)
+        else:
+            y = F.linear(_CopyToGroup.apply(x, self.process_group), self.weight, self.bias)
         return _GatherLastDim.apply(y, self.process_group) if self.gather_output else y
 
     @classmethod
-    def from_linear(cls, lin: nn.Linear, process_group=None, gather_output: bool = False):
+    def from_linear(cls, lin: nn.Linear, process_group=None, gather_output: bool = False,
+                    input_mode: str = "replicated", fused: bool = True):
         """Shard an existing (replicated) ``nn.Linear``."""
         rank, world = dist.get_rank(process_group), _group_size(process_group)
         out = cls(lin.in_features, lin.out_features, lin.bias is not None, process_group=process_group,
-                  gather_output=gather_output, device=lin.weight.device, dtype=lin.weight.dtype)
+                  gather_output=gather_output, input_mode=input_mode, fused=fused, device=lin.weight.device,
+                  dtype=lin.weight.dtype)
         with torch.no_grad():
             out.weight.copy_(lin.weight.chunk(world, dim=0)[rank])
             if lin.bias is not None:
@@ -132,13 +307,18 @@ class RowParallelLinear(nn.Linear):
     output.  The bias is replicated and added once, after the reduction."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, process_group=None,
-                 input_is_parallel: bool = True, device=None, dtype=None):
+                 input_is_parallel: bool = True, scatter_output: bool = False, fused: bool = True, device=None,
+                 dtype=None):
         world = _group_size(process_group)
         if in_features % world:
             raise ValueError(f"in_features={in_features} is not divisible by the group size {world}")
         super().__init__(in_features // world, out_features, bias=bias, device=device, dtype=dtype)
         self.process_group = process_group
         self.input_is_parallel = input_is_parallel
+        # scatter_output: the sum over ranks is reduce-scattered over the sample axis (each rank keeps its
+        # own samples) instead of all-reduced; fused with the GEMM when ``fused`` and the shapes allow
+        self.scatter_output = scatter_output
+        self.fused = fused
         self.full_in_features = in_features
         self.weight.tp_sharded = True
 
@@ -146,14 +326,19 @@ class RowParallelLinear(nn.Linear):
         if not self.input_is_parallel:
             rank, world = dist.get_rank(self.process_group), _group_size(self.process_group)
             x = x.chunk(world, dim=-1)[rank]
-        y = _ReduceFromGroup.apply(F.linear(x, self.weight, None), self.process_group)
+        if self.scatter_output:
+            y = _LinearScatter.apply(x, self.weight, self)
+        else:
+            y = _ReduceFromGroup.apply(F.linear(x, self.weight, None), self.process_group)
         return y if self.bias is None else y + self.bias
 
     @classmethod
-    def from_linear(cls, lin: nn.Linear, process_group=None, input_is_parallel: bool = True):
+    def from_linear(cls, lin: nn.Linear, process_group=None, input_is_parallel: bool = True,
+                    scatter_output: bool = False, fused: bool = True):
         rank, world = dist.get_rank(process_group), _group_size(process_group)
         out = cls(lin.in_features, lin.out_features, lin.bias is not None, process_group=process_group,
-                  input_is_parallel=input_is_parallel, device=lin.weight.device, dtype=lin.weight.dtype)
+                  input_is_parallel=input_is_parallel, scatter_output=scatter_output, fused=fused,
+                  device=lin.weight.device, dtype=lin.weight.dtype)
         with torch.no_grad():
             out.weight.copy_(lin.weight.chunk(world, dim=1)[rank])
             if lin.bias is not None:
@@ -202,6 +387,9 @@ class TensorParallelDPOptimizer(DPOptimizerFastGradientClipping):
         src = dist.get_global_rank(group, 0) if group is not None else 0
         for p in self.params:
             _check_processed_flag(p.summed_grad)
+            if getattr(p, "sp_local", False):
+                # each rank clipped and summed its own samples only: complete the sum over the group
+                dist.all_reduce(p.summed_grad, op=dist.ReduceOp.SUM, group=group)
             noise = _generate_noise(std=std, reference=p.summed_grad, generator=self.generator,
                                     secure_mode=self.secure_mode)
             if not getattr(p, "tp_sharded", False) and std != 0:
@@ -259,28 +447,59 @@ class VocabParallelCrossEntropy(nn.Module):
         return loss.mean() if self.reduction == "mean" else loss.sum()
 
 
-def parallelize_llama(model, process_group=None, shard_lm_head: bool = True):
+def parallelize_llama(model, process_group=None, shard_lm_head: bool = True, sequence_parallel: bool = False,
+                      fused: bool = True):
     """Turn a :class:`opacus_b200.models.Llama` (replicated, identical on all ranks) into its
     1-d tensor-parallel form in place: q/k/v/gate/up become column-parallel, o/down
     row-parallel, heads are divided over the ranks; embedding and norm weights stay
     replicated; with ``shard_lm_head`` the output layer is split over the vocabulary
     (use :class:`VocabParallelCrossEntropy`).  Same layout as the reference's plan
-    (``examples/tensor_parallelism_llama.py:104-152``)."""
+    (``examples/tensor_parallelism_llama.py:104-152``).
+
+    ``sequence_parallel``: between the tensor-parallel blocks (embedding, residual stream, norms) every rank
+    keeps only its ``B / world`` samples.  Attention and MLP gather their input (``SampleGather``), their output
+    projections reduce-scatter instead of all-reduce -- fused into the GEMM (``GemmReduceScatter``) -- and the
+    output layer gathers inside its GEMM (``AllGatherGemm``) when ``fused`` and the shapes allow.  Embedding and
+    norm weights then see only local samples: their per-sample norms are partial (``sp_local``) and their
+    clipped sums are completed by an all-reduce in :class:`TensorParallelDPOptimizer`.  Needs
+    ``shard_lm_head`` and a batch divisible by the group size."""
     world = _group_size(process_group)
+    sp = sequence_parallel
+    if sp and not shard_lm_head:
+        raise ValueError("sequence_parallel needs the output layer sharded over the vocabulary")
+    col_mode = "gathered" if sp else "replicated"
     for blk in model.layers:
         att, mlp = blk.self_attn, blk.mlp
         if att.n_heads % world or att.n_kv % world:
             raise ValueError(f"{att.n_heads} query / {att.n_kv} key-value heads do not divide over {world} ranks")
         for name in ("q_proj", "k_proj", "v_proj"):
-            setattr(att, name, ColumnParallelLinear.from_linear(getattr(att, name), process_group))
-        att.o_proj = RowParallelLinear.from_linear(att.o_proj, process_group)
+            setattr(att, name, ColumnParallelLinear.from_linear(getattr(att, name), process_group, input_mode=col_mode))
+        att.o_proj = RowParallelLinear.from_linear(att.o_proj, process_group, scatter_output=sp, fused=fused)
         att.n_heads //= world
         att.n_kv //= world
         for name in ("gate_proj", "up_proj"):
-            setattr(mlp, name, ColumnParallelLinear.from_linear(getattr(mlp, name), process_group))
-        mlp.down_proj = RowParallelLinear.from_linear(mlp.down_proj, process_group)
+            setattr(mlp, name, ColumnParallelLinear.from_linear(getattr(mlp, name), process_group, input_mode=col_mode))
+        mlp.down_proj = RowParallelLinear.from_linear(mlp.down_proj, process_group, scatter_output=sp, fused=fused)
+        if sp:
+            att.sp_gather = SampleGather(process_group)
+            mlp.sp_gather = SampleGather(process_group)
+            for norm in (blk.input_layernorm, blk.post_attention_layernorm):
+                _mark_sample_local(norm)
     if shard_lm_head:
         if model.lm_head.weight is model.embed_tokens.weight:
             raise ValueError("a tied output layer cannot be sharded over the vocabulary")
-        model.lm_head = ColumnParallelLinear.from_linear(model.lm_head, process_group)
+        model.lm_head = ColumnParallelLinear.from_linear(model.lm_head, process_group,
+                                                         input_mode="local" if sp else "replicated", fused=fused)
+    if sp:
+        model.sp_slice = SampleSlice(process_group)
+        _mark_sample_local(model.embed_tokens)
+        _mark_sample_local(model.norm)
     return model
+
+
+def _mark_sample_local(module):
+    """``module`` runs on this rank's samples only: its per-sample quantities are partial over the group."""
+    module.sp_local_input = True
+    module.sp_local_region = True
+    for p in module.parameters(recurse=False):
+        p.sp_local = True

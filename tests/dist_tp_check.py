@@ -83,6 +83,53 @@ def check_fused_gemms(rank, world):
     _cuda.check_status()
 
 
+def check_sequence_parallel_llama(rank, world):
+    """Tensor-parallel Llama with sample-sharded activations: fused collective GEMMs against NCCL + cuBLAS."""
+    import torch.nn as nn  # noqa: F401
+
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClippingTP
+    from opacus_b200.models import Llama, LlamaConfig
+    from opacus_b200.parallel.tensor_parallel import (TensorParallelDPOptimizer, VocabParallelCrossEntropy,
+                                                      parallelize_llama)
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    B, T = 2 * world, 128
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 1024, (B, T + 1), generator=g).to(dev)
+    results = {}
+    for fused in (False, True):
+        torch.manual_seed(0)
+        cfg = LlamaConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=8, n_kv_heads=8, ffn_dim=512,
+                          tie_embeddings=False)
+        model = Llama(cfg).to(dev).bfloat16()
+        parallelize_llama(model, sequence_parallel=True, fused=fused)
+        gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=1.0, single_pass=True)
+        opt = TensorParallelDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.1), noise_multiplier=0.0,
+                                        max_grad_norm=1.0, expected_batch_size=B)
+        crit = DPLossFastGradientClipping(gsm, opt, VocabParallelCrossEntropy(), "mean")
+        for _ in range(2):
+            opt.zero_grad()
+            logits = gsm(ids[:, :-1])
+            loss = crit(logits.flatten(0, 1), ids[:, 1:].reshape(-1), shape=(B, T))
+            value = loss.item()
+            loss.backward()
+            norms = gsm.per_sample_gradient_norms.clone()
+            opt.step()
+        torch.cuda.synchronize()
+        _cuda.check_status()
+        results[fused] = (value, norms, model.layers[0].mlp.down_proj.weight.detach().float().clone(),
+                          model.embed_tokens.weight.detach().float().clone())
+        if fused:
+            assert "_ag" in model.lm_head.__dict__, "the output layer did not take the fused all-gather GEMM"
+            assert "_rs" in model.layers[0].self_attn.o_proj.__dict__, "o_proj did not take the fused reduce-scatter GEMM"
+    (v0, n0, w0, e0), (v1, n1, w1, e1) = results[False], results[True]
+    assert abs(v0 - v1) < 2e-2, (v0, v1)
+    torch.testing.assert_close(n0, n1, rtol=3e-2, atol=1e-3)
+    assert (w0 - w1).abs().max() <= 2e-2 * w0.abs().max() + 1e-3
+    assert (e0 - e1).abs().max() <= 2e-2 * e0.abs().max() + 1e-3
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -90,6 +137,7 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     check_norm_reducer(rank, world)
     check_fused_gemms(rank, world)
+    check_sequence_parallel_llama(rank, world)
     dist.barrier()
     if rank == 0:
         print("tp check ok")

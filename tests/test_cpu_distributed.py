@@ -289,3 +289,72 @@ def test_tensor_parallel_llama_matches_unsharded():
             else:
                 ref = full.chunk(2, 1)[rank]          # row-parallel: input features split
             assert torch.allclose(mine, ref, atol=2e-6), (rank, name)
+
+
+def _llama_ids4():
+    g = torch.Generator().manual_seed(12)
+    return torch.randint(0, 96, (4, 9), generator=g)
+
+
+def _tp_sp_llama_job(rank, world):
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClippingTP
+    from opacus_b200.parallel.tensor_parallel import (TensorParallelDPOptimizer, VocabParallelCrossEntropy,
+                                                      parallelize_llama)
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    model = parallelize_llama(_tiny_llama(), sequence_parallel=True)
+    ids = _llama_ids4()
+    gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=0.05, single_pass=True)
+    opt = TensorParallelDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                    max_grad_norm=0.05, expected_batch_size=4)
+    crit = DPLossFastGradientClipping(gsm, opt, VocabParallelCrossEntropy(), "mean")
+    out = []
+    for _ in range(2):                       # two steps: buffers and flags are reused
+        opt.zero_grad()
+        logits = gsm(ids[:, :-1])
+        loss = crit(logits.flatten(0, 1), ids[:, 1:].reshape(-1), shape=(4, 8))
+        value = loss.item()
+        loss.backward()
+        norms = gsm.per_sample_gradient_norms.clone()
+        opt.step()
+        out.append((value, norms))
+    return out, {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def test_sequence_parallel_llama_matches_unsharded():
+    """Activations sharded over samples between the tensor-parallel blocks: same losses, per-sample norms
+    and updated weights as the unsharded model (embedding / norm weights get their partial sums all-reduced)."""
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
+    from opacus_b200.optimizers import DPOptimizerFastGradientClipping
+    from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientClipping
+
+    got = _run(_tp_sp_llama_job, timeout_s=180)
+    model = _tiny_llama()
+    ids = _llama_ids4()
+    gsm = GradSampleModuleFastGradientClipping(model, max_grad_norm=0.05, single_pass=True)
+    opt = DPOptimizerFastGradientClipping(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0,
+                                          max_grad_norm=0.05, expected_batch_size=4)
+    crit = DPLossFastGradientClipping(gsm, opt, nn.CrossEntropyLoss(), "mean")
+    ref = []
+    for _ in range(2):
+        opt.zero_grad()
+        loss = crit(gsm(ids[:, :-1]).flatten(0, 1), ids[:, 1:].reshape(-1), shape=(4, 8))
+        value = loss.item()
+        loss.backward()
+        ref.append((value, gsm.per_sample_gradient_norms.clone()))
+        opt.step()
+    want = model.state_dict()
+    for rank in range(2):
+        steps, sd = got[rank]
+        for (v, n), (rv, rn) in zip(steps, ref):
+            assert abs(v - rv) < 1e-5
+            assert torch.allclose(n, rn, rtol=1e-4, atol=1e-6), rank
+        for name, full in want.items():
+            mine = sd[name]
+            if mine.shape == full.shape:
+                refw = full
+            elif mine.shape[0] != full.shape[0]:
+                refw = full.chunk(2, 0)[rank]
+            else:
+                refw = full.chunk(2, 1)[rank]
+            assert torch.allclose(mine, refw, atol=3e-6), (rank, name)
