@@ -45,8 +45,9 @@ def main():
     opt = torch.optim.SGD(model.parameters(), lr=0.1)
     pe = PrivacyEngine(accountant="rdp")
     # batch_size 256 -> len(loader) = 235, sample rate 1/235 ~ 256/60000
+    extra = {"skip_param_grads": True} if args.impl == "ours" else {}   # autograd skips the non-private weight gradients
     model, opt, dl = pe.make_private(module=model, optimizer=opt, data_loader=DataLoader(ds, batch_size=256),
-                                     noise_multiplier=1.0, max_grad_norm=1.0)
+                                     noise_multiplier=1.0, max_grad_norm=1.0, **extra)
     crit = nn.CrossEntropyLoss()
     seen, steps, t0 = 0, 0, time.perf_counter()
     for x, y in dl:

@@ -133,7 +133,8 @@ def time_layer(lib, impl, name, make, make_input, mode, dtype, iters, flush):
             loss_fn(model(x), None).backward()
             opt.step()
     else:
-        model = lib["wrap_model"](layer, grad_sample_mode="hooks")
+        kw = {"skip_param_grads": True} if impl == "ours" else {}     # no wasted batch-gradient GEMM in autograd
+        model = lib["wrap_model"](layer, grad_sample_mode="hooks", **kw)
         opt = lib["DPOptimizer"](torch.optim.SGD(layer.parameters(), lr=0.01), noise_multiplier=1.0,
                                  max_grad_norm=1.0, expected_batch_size=B)
 

@@ -6,7 +6,8 @@
 All ranks form one tensor-parallel group and see the same batch.  Linear layers are
 column / row parallel, the output layer is split over the vocabulary and feeds
 ``VocabParallelCrossEntropy``; embedding and norm weights are replicated and
-trained (identical noise on every rank).  The logical batch is processed in
+trained (identical noise on every rank).  ``--sp`` shards the activations between the
+blocks over samples and uses the fused all-gather / reduce-scatter GEMMs.  The logical batch is processed in
 micro-batches with ``signal_skip_step``.  Per-sample norms are summed over the
 group by the peer-memory kernel (``csrc/peer_collectives.cu``); C = 1.0,
 sigma = 1.0, DP-AdamW, bf16, synthetic token ids copied from pinned host memory
@@ -29,6 +30,9 @@ def main():
     ap.add_argument("--micro", type=int, default=8, help="samples per micro-step")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--sp", action="store_true",
+                    help="sequence parallel: activations sharded over samples between the blocks, fused collective GEMMs")
+    ap.add_argument("--no-fused", action="store_true", help="with --sp: NCCL + cuBLAS instead of the fused GEMMs")
     ap.add_argument("--no-peer-norm", action="store_true", help="reduce the norms with NCCL instead of the peer kernel")
     args = ap.parse_args()
     import warnings
@@ -57,7 +61,7 @@ def main():
     with torch.device(dev):
         model = Llama(cfg)                       # same weights on every rank, then sharded in place
     torch.set_default_dtype(torch.float32)
-    parallelize_llama(model)
+    parallelize_llama(model, sequence_parallel=args.sp, fused=not args.no_fused)
     torch.cuda.empty_cache()
     gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=1.0, single_pass=True)
     gsm.use_peer_memory = not args.no_peer_norm
@@ -98,7 +102,8 @@ def main():
     if rank == 0:
         print(json.dumps({"metric": "dp_llama8b_tp_tokens_per_s", "value": args.batch * T / (ms / 1e3), "n_gpus": world,
                           "ms_per_logical_step": ms, "config": {"layers": args.layers, "seq": T, "global_batch": args.batch,
-                                                                "micro_batch": args.micro, "parallelism": f"tp{world}"},
+                                                                "micro_batch": args.micro, "parallelism": f"tp{world}" + ("+sp" if args.sp else ""),
+                                                                "fused_collective_gemms": bool(args.sp and not args.no_fused)},
                           "peer_norm_kernel": not args.no_peer_norm, "loss": last, "dtype": "bf16",
                           "max_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}))
     dist.barrier()

@@ -85,11 +85,34 @@ def _pad_rows(t: torch.Tensor, n: int) -> torch.Tensor:
     return torch.cat([t, t.new_zeros((n - t.shape[0],) + tuple(t.shape[1:]))], dim=0)
 
 
+class _OutputTap(torch.autograd.Function):
+    """Identity on a layer's output whose backward hands the output gradient to
+    the controller.  ``anchor`` is a dummy that requires grad so that the tap is
+    part of the graph even when nothing upstream requires grad (first layer)."""
+
+    @staticmethod
+    def forward(ctx, out, anchor, controller, module):
+        ctx.controller = controller
+        ctx.module = module
+        return out.view_as(out)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ctx.controller._on_output_grad(ctx.module, grad_out)
+        return grad_out, None, None, None
+
+
 class GradSampleHooks(AbstractGradSampleHooks):
     GRAD_SAMPLERS = {}
 
     def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
-                 force_functorch=False):
+                 force_functorch=False, skip_param_grads: bool = False):
+        # skip_param_grads: layers run with detached parameters, so autograd never computes the (non-private)
+        # batch gradient of the weights -- a whole GEMM per layer that DP-SGD throws away.  ``p.grad`` then
+        # stays None until the DP optimizer writes the private gradient.  Off by default (reference behaviour).
+        self.skip_param_grads = skip_param_grads
+        self._hook_args = dict(loss_reduction=loss_reduction, batch_first=batch_first)
+        self._anchor = None
         super().__init__(m, batch_first=batch_first, loss_reduction=loss_reduction)
         errors = self.validate(module=m, strict=strict)
         if errors and not strict:
@@ -131,10 +154,51 @@ class GradSampleHooks(AbstractGradSampleHooks):
                 continue
             if force_functorch or self._get_module_type(sub) not in self.GRAD_SAMPLERS:
                 prepare_layer(sub, batch_first=batch_first)
+            if self.skip_param_grads:
+                handles.append(sub.register_forward_pre_hook(self._detach_params_pre_hook))
+                handles.append(sub.register_forward_hook(self._tap_forward_hook, always_call=True))
+                continue
             handles.append(sub.register_forward_hook(self.capture_activations_hook))
             handles.append(sub.register_full_backward_hook(
                 partial(self.capture_backprops_hook, loss_reduction=loss_reduction, batch_first=batch_first)))
         self.enable_hooks()
+
+    # ---- skip_param_grads: detached parameters in forward, a tap on the output instead of a backward hook
+    def _capturing(self, module) -> bool:
+        return self.hooks_enabled and module.training and torch.is_grad_enabled() and requires_grad(module)
+
+    def _detach_params_pre_hook(self, module, _inputs):
+        if not self._capturing(module):
+            return
+        saved = []
+        for sub in module.modules():
+            for name, p in sub._parameters.items():
+                if p is not None and p.requires_grad:
+                    saved.append((sub, name, p))
+                    sub._parameters[name] = p.detach()
+        module.__dict__["_dp_saved_params"] = saved
+
+    def _tap_forward_hook(self, module, inputs, output):
+        saved = module.__dict__.pop("_dp_saved_params", None)
+        if saved is None:
+            return None
+        for sub, name, p in saved:
+            sub._parameters[name] = p
+        if output is None:
+            return None
+        self.capture_activations_hook(module, inputs, output)
+        first = output[0] if isinstance(output, (tuple, list)) else output
+        if self._anchor is None or self._anchor.device != first.device:
+            self._anchor = torch.zeros((), device=first.device, requires_grad=True)
+        tapped = _OutputTap.apply(first, self._anchor, self, module)
+        if isinstance(output, tuple):
+            return (tapped,) + tuple(output[1:])
+        if isinstance(output, list):
+            return [tapped] + list(output[1:])
+        return tapped
+
+    def _on_output_grad(self, module, grad_out):
+        self.capture_backprops_hook(module, None, (grad_out,), **self._hook_args)
 
     def remove_hooks(self) -> None:
         self.disable_hooks()
@@ -292,10 +356,10 @@ class GradSampleModule(GradSampleHooks, AbstractGradSampleModule):
     """``nn.Module`` wrapper flavour: ``GradSampleModule(model)(x)``."""
 
     def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
-                 force_functorch=False):
+                 force_functorch=False, skip_param_grads: bool = False):
         nn.Module.__init__(self)
         GradSampleHooks.__init__(self, m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
-                                 force_functorch=force_functorch)
+                                 force_functorch=force_functorch, skip_param_grads=skip_param_grads)
         self.grad_accumulation_hook = None
 
     def forward(self, *args, **kwargs):

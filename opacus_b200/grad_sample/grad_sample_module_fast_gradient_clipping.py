@@ -43,6 +43,7 @@ from ..layers.dp_rnn import DPGRU, DPLSTM, DPRNN, RNNLinear
 from ..utils.module_utils import requires_grad, trainable_modules, trainable_parameters
 from .functorch import ft_compute_per_sample_gradient
 from .grad_sample_module import (
+    _OutputTap,
     _STACKED_TYPES,
     GradSampleHooks,
     create_or_accumulate_grad_sample,
@@ -62,23 +63,6 @@ def create_norm_sample(*, param: torch.Tensor, grad_sample: torch.Tensor, max_ba
         param._norm_sample = torch.tensor([], device=grad_sample.device, dtype=grad_sample.dtype)
     else:
         param._norm_sample = ops.grad_sample_norm_sq(grad_sample).sqrt().to(grad_sample.dtype)
-
-
-class _OutputTap(torch.autograd.Function):
-    """Identity on a layer's output whose backward hands the output gradient to
-    the controller.  ``anchor`` is a dummy that requires grad so that the tap is
-    part of the graph even when nothing upstream requires grad (first layer)."""
-
-    @staticmethod
-    def forward(ctx, out, anchor, controller, module):
-        ctx.controller = controller
-        ctx.module = module
-        return out.view_as(out)
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        ctx.controller._on_output_grad(ctx.module, grad_out)
-        return grad_out, None, None, None
 
 
 class _Site:

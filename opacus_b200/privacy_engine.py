@@ -117,7 +117,8 @@ class PrivacyEngine:
     def _prepare_model(self, module: nn.Module, *, batch_first: bool = True,
                        max_grad_norm: Union[float, List[float]] = 1.0, loss_reduction: str = "mean",
                        grad_sample_mode: str = "hooks", wrap_model: bool = True,
-                       single_pass: Optional[bool] = None) -> Union[AbstractGradSampleModule, GradSampleHooks]:
+                       single_pass: Optional[bool] = None,
+                       skip_param_grads: bool = False) -> Union[AbstractGradSampleModule, GradSampleHooks]:
         self.validate(module=module, optimizer=None, data_loader=None)
         if wrap_model and isinstance(module, AbstractGradSampleModule):
             if (module.batch_first != batch_first or module.loss_reduction != loss_reduction
@@ -137,6 +138,8 @@ class PrivacyEngine:
                 extra["single_pass"] = True if single_pass is None else single_pass
             elif single_pass is not None:
                 extra["single_pass"] = single_pass
+        elif grad_sample_mode in ("hooks", "functorch") and skip_param_grads:
+            extra["skip_param_grads"] = True
         return prepare_module(module, grad_sample_mode=grad_sample_mode, batch_first=batch_first,
                               loss_reduction=loss_reduction, wrap_model=wrap_model, **extra)
 
@@ -184,10 +187,14 @@ class PrivacyEngine:
         distributed = isinstance(module, _distributed_kinds())
         single_pass = kwargs.pop("single_pass", None)
         engine = module if type(module).__name__ == "ShardedDataParallel" else None
+        # hooks mode: skip autograd's own (non-private) weight gradients.  Always with the sharded engine, whose
+        # gradients live in its own buffer anyway; elsewhere on request (``p.grad`` then stays None until step()).
+        skip_param_grads = kwargs.pop("skip_param_grads", engine is not None)
 
         module = self._prepare_model(module, batch_first=batch_first, max_grad_norm=max_grad_norm,
                                      loss_reduction=loss_reduction, grad_sample_mode=grad_sample_mode,
-                                     wrap_model=wrap_model, single_pass=single_pass)
+                                     wrap_model=wrap_model, single_pass=single_pass,
+                                     skip_param_grads=skip_param_grads)
         if poisson_sampling:
             module.forbid_grad_accumulation()
 

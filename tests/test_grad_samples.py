@@ -210,3 +210,29 @@ def test_accumulation_list_and_poisson_guard():
 def test_buffers_rejected():
     with pytest.raises(NotImplementedError):
         GradSampleModule(nn.BatchNorm1d(3))
+
+
+def test_hooks_mode_without_autograd_weight_gradients():
+    """skip_param_grads: same per-sample gradients, no batch gradient computed by autograd (first layer included)."""
+    from opacus_b200.grad_sample import GradSampleModule
+
+    torch.manual_seed(0)
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Conv2d(3, 4, 3, padding=1), nn.GroupNorm(2, 4), nn.ReLU(), nn.Flatten(),
+                             nn.Linear(4 * 6 * 6, 5))
+    x = torch.randn(7, 3, 6, 6)
+    y = torch.randint(0, 5, (7,))
+    a, b = GradSampleModule(make()), GradSampleModule(make(), skip_param_grads=True)
+    for m in (a, b):
+        nn.functional.cross_entropy(m(x), y).backward()
+    for (n1, p1), (n2, p2) in zip(a.named_parameters(), b.named_parameters()):
+        assert p2.grad is None and p1.grad is not None, n1
+        torch.testing.assert_close(p1.grad_sample, p2.grad_sample)
+    # a second pass accumulates nothing stale and evaluation mode passes through
+    b.zero_grad()
+    nn.functional.cross_entropy(b(x), y).backward()
+    for (_, p1), (_, p2) in zip(a.named_parameters(), b.named_parameters()):
+        torch.testing.assert_close(p1.grad_sample, p2.grad_sample)
+    b.eval()
+    assert b(x).shape == (7, 5)
