@@ -37,6 +37,8 @@ constexpr int CV_STAGES = 4;
 constexpr int CV_ABYTES = 2 * CV_BOX_BYTES;
 constexpr int CV_STAGE_BYTES = CV_ABYTES + CV_MAXCH * CV_BOX_BYTES;
 constexpr int CV_THREADS = 256;
+constexpr int CV_EPI_BYTES = 32 * 128;     // one staged 32-row x 64-channel bf16 block (128-byte swizzled rows)
+constexpr int CV_EPI_TOTAL = 4 * 2 * CV_EPI_BYTES;   // four epilogue warps, double buffered
 
 struct CvParams {
   int B, C, O, OH, OW;
@@ -89,10 +91,12 @@ __device__ __forceinline__ CvItem cv_decode(const CvParams& p, int item) {
 }
 
 __global__ void __launch_bounds__(CV_THREADS, 1)
-conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_x, CvParams p) {
+conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_x,
+                const __grid_constant__ CUtensorMap map_o, CvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  auto* bars = reinterpret_cast<CvBarriers*>(smem + CV_STAGES * CV_STAGE_BYTES);
+  uint8_t* epi = smem + CV_STAGES * CV_STAGE_BYTES;            // staging rows of the bf16 epilogue
+  auto* bars = reinterpret_cast<CvBarriers*>(epi + CV_EPI_TOTAL);
   volatile uint32_t* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -198,6 +202,7 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
     const int ew = warp - 4;
     const int taps = p.kh * p.kw;
     int local = 0;
+    uint32_t epi_use = 0;
     for (int item = blockIdx.x; item < p.items; item += gridDim.x, ++local) {
       const CvItem w = cv_decode(p, item);
       const int acc = local & 1;
@@ -209,6 +214,57 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
       const uint32_t taddr = tmem_base + acc * 256 + (static_cast<uint32_t>(ew * 32) << 16);
       const int64_t row_base = ((int64_t)w.b * p.O + row) * taps;
       const bool atomic_out = p.reduce_batch && p.splits > 1;
+      if (p.out != nullptr && p.out_bf16) {
+        // bf16 gradients: every 32-row x 64-channel block is staged in shared memory in the 128-byte-swizzle
+        // pattern and written with ONE tensor store, so global memory sees whole 128-byte rows instead of
+        // 16-byte fragments.  The map clips rows >= O and channels >= C.
+        const int o0 = w.m0 + ew * 32;
+#pragma unroll 1
+        for (int j = 0; j < p.nchunk; ++j) {
+          const int chunk = w.nc0 + j;
+          if (chunk >= p.chunks) break;
+          uint8_t* stage = epi + (ew * 2 + (epi_use & 1)) * CV_EPI_BYTES;
+          if (lane == 0) bulk_wait_read<1>();          // the store issued two blocks ago has left this buffer
+          __syncwarp();
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + j * 64 + hlf * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint4 pk;
+              uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float v0 = __uint_as_float(r[q8 * 8 + 2 * q]), v1 = __uint_as_float(r[q8 * 8 + 2 * q + 1]);
+                sq = fmaf(v0, v0, fmaf(v1, v1, sq));
+                __nv_bfloat162 nv = __floats2bfloat162_rn(v0, v1);
+                pw[q] = *reinterpret_cast<uint32_t*>(&nv);
+              }
+              const int c16 = hlf * 4 + q8;              // 16-byte column of the 128-byte row
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = pk;
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && o0 < p.O) {
+            const int tap = chunk / p.cblocks;
+            tma_store_4d(&map_o, stage, (chunk - tap * p.cblocks) * 64, tap, o0, w.b);
+            bulk_commit();
+          }
+          ++epi_use;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+        if (p.norm_sq != nullptr) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          if (lane == 0) atomicAdd(p.norm_sq + w.b, sq);
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < p.nchunk * 64; c0 += 32) {
         const int chunk = w.nc0 + (c0 >> 6);
@@ -276,6 +332,7 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
     }
   }
 
+  if (warp >= 4 && lane == 0) bulk_wait<0>();        // tensor stores of this warp have completed
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -293,6 +350,7 @@ extern "C" int dpk_conv_psg(const void* x, const void* g, int B, int C, int H, i
   if (B <= 0 || C <= 0 || O <= 0 || OH <= 0 || OW <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0) return cudaErrorInvalidValue;
   if ((C % 8) != 0 || (O % 8) != 0 || sh < 1 || sw < 1 || sh > 8 || sw > 8) return cudaErrorInvalidValue;
   if (reduce_batch && (out == nullptr || out_bf16 || (beta != 0.f && beta != 1.f))) return cudaErrorInvalidValue;
+  if (!reduce_batch && out != nullptr && out_bf16 && beta != 0.f) return cudaErrorInvalidValue;
   CvParams p{};
   p.B = B; p.C = C; p.O = O; p.OH = OH; p.OW = OW;
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
@@ -336,7 +394,13 @@ extern "C" int dpk_conv_psg(const void* x, const void* g, int B, int C, int H, i
   if (rc) return rc;
   rc = make_tmap_4d_bf16(&map_x, x, C, W, H, B, p.bw, p.bh, sw, sh);
   if (rc) return rc;
-  const size_t smem = 1024 + CV_STAGES * CV_STAGE_BYTES + sizeof(CvBarriers);
+  CUtensorMap map_o = map_g;     // only read by the bf16 per-sample epilogue
+  if (out != nullptr && out_bf16 && !reduce_batch) {
+    rc = make_tmap_4d_bf16(&map_o, out, C, kh * kw, O, B, 1, 32, 1, 1);
+    if (rc) return rc;
+  }
+  const size_t smem = 1024 + CV_STAGES * CV_STAGE_BYTES + CV_EPI_TOTAL + sizeof(CvBarriers);
+  static_assert(1024 + CV_STAGES * CV_STAGE_BYTES + CV_EPI_TOTAL + sizeof(CvBarriers) <= 227 * 1024, "shared memory");
   cudaError_t e = cudaSuccess;
   {
     static bool attr_done[64] = {false};
@@ -353,6 +417,6 @@ extern "C" int dpk_conv_psg(const void* x, const void* g, int B, int C, int H, i
     if (e != cudaSuccess) return e;
   }
   const int grid = p.items < sms ? p.items : sms;
-  conv_psg_kernel<<<grid, CV_THREADS, smem, stream>>>(map_g, map_x, p);
+  conv_psg_kernel<<<grid, CV_THREADS, smem, stream>>>(map_g, map_x, map_o, p);
   return cudaGetLastError();
 }
