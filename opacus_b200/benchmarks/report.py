@@ -1,0 +1,51 @@
+"""Pivot the JSON files written by ``benchmarks.layers --json`` into one table and gate on a threshold.
+
+    python -m opacus_b200.benchmarks.layers --impl ours --json ours.json
+    python -m opacus_b200.benchmarks.layers --impl reference --json ref.json
+    python -m opacus_b200.benchmarks.report ours.json ref.json [--max-ratio 1.0] [--csv out.csv]
+
+Prints, per (layer, dtype, mode), both times and ``ours / reference``; with ``--max-ratio`` the exit code is 1 if
+any ratio exceeds it (the role of ``benchmarks/generate_report.py`` and ``benchmarks/check_threshold.py:44-48`` in
+the reference, whose gate compares a DP mode against the non-private baseline).
+"""
+import argparse
+import json
+import sys
+
+
+def load(path):
+    with open(path) as f:
+        return {(r["layer"], r["dtype"], r["mode"]): r for r in json.load(f)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("ours")
+    ap.add_argument("reference")
+    ap.add_argument("--max-ratio", type=float, default=None)
+    ap.add_argument("--csv", default=None)
+    args = ap.parse_args(argv)
+    a, b = load(args.ours), load(args.reference)
+    rows, worst = [], 0.0
+    print(f"{'layer':13s} {'dtype':9s} {'mode':6s} {'ours ms':>10s} {'ref ms':>10s} {'ours/ref':>9s}")
+    for key in sorted(set(a) | set(b)):
+        x, y = a.get(key, {}).get("ms"), b.get(key, {}).get("ms")
+        ratio = x / y if x and y else None
+        if ratio is not None:
+            worst = max(worst, ratio)
+        fmt = lambda v: f"{v:10.3f}" if v is not None else f"{'-':>10s}"
+        print(f"{key[0]:13s} {key[1]:9s} {key[2]:6s} {fmt(x)} {fmt(y)} " + (f"{ratio:9.2f}" if ratio else f"{'-':>9s}"))
+        rows.append((*key, x, y, ratio))
+    if args.csv:
+        with open(args.csv, "w") as f:
+            f.write("layer,dtype,mode,ours_ms,reference_ms,ratio\n")
+            for r in rows:
+                f.write(",".join("" if v is None else str(v) for v in r) + "\n")
+    if args.max_ratio is not None and worst > args.max_ratio:
+        print(f"FAILED: worst ratio {worst:.2f} exceeds {args.max_ratio}")
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
