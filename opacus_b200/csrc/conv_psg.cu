@@ -33,12 +33,12 @@ constexpr int CV_BK = 64;                  // output pixels per stage
 constexpr int CV_BOX_BYTES = CV_BK * 128;  // one 64-column chunk
 constexpr int CV_BM = 128;                 // output channels per tile
 constexpr int CV_MAXCH = 4;                // chunks per tile (N <= 256)
-constexpr int CV_STAGES = 4;
+constexpr int CV_STAGES = 3;
 constexpr int CV_ABYTES = 2 * CV_BOX_BYTES;
 constexpr int CV_STAGE_BYTES = CV_ABYTES + CV_MAXCH * CV_BOX_BYTES;
 constexpr int CV_THREADS = 256;
 constexpr int CV_EPI_BYTES = 32 * 128;     // one staged 32-row x 64-channel bf16 block (128-byte swizzled rows)
-constexpr int CV_EPI_TOTAL = 4 * 2 * CV_EPI_BYTES;   // four epilogue warps, double buffered
+constexpr int CV_EPI_TOTAL = 4 * CV_MAXCH * CV_EPI_BYTES;   // four epilogue warps x one whole tile row-block each
 
 struct CvParams {
   int B, C, O, OH, OW;
@@ -202,7 +202,6 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
     const int ew = warp - 4;
     const int taps = p.kh * p.kw;
     int local = 0;
-    uint32_t epi_use = 0;
     for (int item = blockIdx.x; item < p.items; item += gridDim.x, ++local) {
       const CvItem w = cv_decode(p, item);
       const int acc = local & 1;
@@ -219,25 +218,27 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
         // pattern and written with ONE tensor store, so global memory sees whole 128-byte rows instead of
         // 16-byte fragments.  The map clips rows >= O and channels >= C.
         const int o0 = w.m0 + ew * 32;
+        uint8_t* stage0 = epi + ew * (CV_MAXCH * CV_EPI_BYTES);
+        if (lane == 0) bulk_wait_read<0>();            // the previous tile's stores have left the staging rows
+        __syncwarp();
+        int nstore = 0;
 #pragma unroll 1
         for (int j = 0; j < p.nchunk; ++j) {
-          const int chunk = w.nc0 + j;
-          if (chunk >= p.chunks) break;
-          uint8_t* stage = epi + (ew * 2 + (epi_use & 1)) * CV_EPI_BYTES;
-          if (lane == 0) bulk_wait_read<1>();          // the store issued two blocks ago has left this buffer
-          __syncwarp();
+          if (w.nc0 + j >= p.chunks) break;
+          uint8_t* stage = stage0 + j * CV_EPI_BYTES;
+          uint32_t r[2][32];                           // both halves of the 64-column chunk in flight at once
+          tmem_ld_32x32(taddr + j * 64, r[0]);
+          tmem_ld_32x32(taddr + j * 64 + 32, r[1]);
+          tmem_ld_wait();
 #pragma unroll
           for (int hlf = 0; hlf < 2; ++hlf) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + j * 64 + hlf * 32, r);
-            tmem_ld_wait();
 #pragma unroll
             for (int q8 = 0; q8 < 4; ++q8) {
               uint4 pk;
               uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const float v0 = __uint_as_float(r[q8 * 8 + 2 * q]), v1 = __uint_as_float(r[q8 * 8 + 2 * q + 1]);
+                const float v0 = __uint_as_float(r[hlf][q8 * 8 + 2 * q]), v1 = __uint_as_float(r[hlf][q8 * 8 + 2 * q + 1]);
                 sq = fmaf(v0, v0, fmaf(v1, v1, sq));
                 __nv_bfloat162 nv = __floats2bfloat162_rn(v0, v1);
                 pw[q] = *reinterpret_cast<uint32_t*>(&nv);
@@ -246,18 +247,21 @@ conv_psg_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant
               *reinterpret_cast<uint4*>(stage + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = pk;
             }
           }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && o0 < p.O) {
-            const int tap = chunk / p.cblocks;
-            tma_store_4d(&map_o, stage, (chunk - tap * p.cblocks) * 64, tap, o0, w.b);
-            bulk_commit();
-          }
-          ++epi_use;
+          ++nstore;
         }
-        tc_fence_before();
+        tc_fence_before();                             // the accumulator can be reused while the stores go out
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+        fence_proxy_async();                           // ONE proxy fence per tile
+        __syncwarp();
+        if (lane == 0 && o0 < p.O) {
+          for (int j = 0; j < nstore; ++j) {
+            const int chunk = w.nc0 + j;
+            const int tap = chunk / p.cblocks;
+            tma_store_4d(&map_o, stage0 + j * CV_EPI_BYTES, (chunk - tap * p.cblocks) * 64, tap, o0, w.b);
+          }
+          bulk_commit();
+        }
         if (p.norm_sq != nullptr) {
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);

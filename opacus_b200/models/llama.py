@@ -129,10 +129,13 @@ class Attention(nn.Module):
     def forward(self, x):
         if self.sp_gather is not None:
             x = self.sp_gather(x)
+        q_lin = self.q_proj(x)
+        if isinstance(q_lin, tuple):        # sequence parallel: the projection gathered its input, siblings reuse it
+            q_lin, x = q_lin
         B, T, _ = x.shape
         # everything stays token-major in memory; attention gets [B, H, T, hd] *views*, so neither the
         # inputs nor the output of attention are ever transposed by a copy
-        q = rope(self.q_proj(x).view(B, T, self.n_heads, self.hd), self.theta).transpose(1, 2)
+        q = rope(q_lin.view(B, T, self.n_heads, self.hd), self.theta).transpose(1, 2)
         k = rope(self.k_proj(x).view(B, T, self.n_kv, self.hd), self.theta).transpose(1, 2)
         v = self.v_proj(x).view(B, T, self.n_kv, self.hd).transpose(1, 2)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv != self.n_heads)
@@ -150,7 +153,10 @@ class MLP(nn.Module):
     def forward(self, x):
         if self.sp_gather is not None:
             x = self.sp_gather(x)
-        return self.down_proj(swiglu(self.gate_proj(x), self.up_proj(x)))
+        gate = self.gate_proj(x)
+        if isinstance(gate, tuple):         # sequence parallel: see Attention.forward
+            gate, x = gate
+        return self.down_proj(swiglu(gate, self.up_proj(x)))
 
 
 class Block(nn.Module):

@@ -187,18 +187,24 @@ class _GatherLinear(torch.autograd.Function):
             full = _all_gather0(x2, group)
             y = full @ weight.t()
         full_shape = (lead[0] * world,) + tuple(lead[1:])
-        layer.__dict__["_dp_activation"] = full.view(full_shape + (K,))
+        full_view = full.view(full_shape + (K,))
+        layer.__dict__["_dp_activation"] = full_view
         ctx.save_for_backward(full, weight)
         ctx.group, ctx.x_shape = group, x.shape
-        return y.view(full_shape + (weight.shape[0],))
+        # the gathered input is a second output: layers that consume the same activations (k/v next to q,
+        # up next to gate) take it from here and their input gradients join the one reduce-scatter below
+        return y.view(full_shape + (weight.shape[0],)), full_view
 
     @staticmethod
-    def backward(ctx, gy):
+    def backward(ctx, gy, gfull):
         full, weight = ctx.saved_tensors
         g2 = gy.reshape(-1, gy.shape[-1])
         gx = gw = None
         if ctx.needs_input_grad[0]:
-            gx = _reduce_scatter0(g2 @ weight, ctx.group).view(ctx.x_shape)
+            gin = g2 @ weight
+            if gfull is not None:
+                gin = gin + gfull.reshape(gin.shape)
+            gx = _reduce_scatter0(gin, ctx.group).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             gw = g2.t() @ full
         return gx, gw, None
@@ -252,8 +258,8 @@ class ColumnParallelLinear(nn.Linear):
     With ``gather_output`` the shards of ``y`` are concatenated on every rank."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, process_group=None,
-                 gather_output: bool = False, input_mode: str = "replicated", fused: bool = True, device=None,
-                 dtype=None):
+                 gather_output: bool = False, input_mode: str = "replicated", fused: bool = True,
+                 return_gathered: bool = False, device=None, dtype=None):
         world = _group_size(process_group)
         if out_features % world:
             raise ValueError(f"out_features={out_features} is not divisible by the group size {world}")
@@ -269,6 +275,10 @@ class ColumnParallelLinear(nn.Linear):
         #               the GEMM when ``fused`` and the shapes allow
         self.input_mode = input_mode
         self.fused = fused
+        # with input_mode "local": forward returns ``(y, gathered_input)`` so that sibling layers reuse the gather
+        self.return_gathered = return_gathered and input_mode == "local"
+        if self.return_gathered and gather_output:
+            raise ValueError("return_gathered and gather_output cannot be combined")
         self.sp_local_input = input_mode == "local"
         self.weight.tp_sharded = True
         if self.bias is not None:
@@ -276,9 +286,11 @@ class ColumnParallelLinear(nn.Linear):
 
     def forward(self, x):
         if self.input_mode == "local":
-            y = _GatherLinear.apply(x, self.weight, self)
+            y, gathered = _GatherLinear.apply(x, self.weight, self)
             if self.bias is not None:
                 y = y + self.bias
+            if self.return_gathered:
+                return y, gathered
         elif self.input_mode == "gathered":
             y = F.linear(x, self.weight, self.bias)
         else:
@@ -287,12 +299,12 @@ class ColumnParallelLinear(nn.Linear):
 
     @classmethod
     def from_linear(cls, lin: nn.Linear, process_group=None, gather_output: bool = False,
-                    input_mode: str = "replicated", fused: bool = True):
+                    input_mode: str = "replicated", fused: bool = True, return_gathered: bool = False):
         """Shard an existing (replicated) ``nn.Linear``."""
         rank, world = dist.get_rank(process_group), _group_size(process_group)
         out = cls(lin.in_features, lin.out_features, lin.bias is not None, process_group=process_group,
-                  gather_output=gather_output, input_mode=input_mode, fused=fused, device=lin.weight.device,
-                  dtype=lin.weight.dtype)
+                  gather_output=gather_output, input_mode=input_mode, fused=fused, return_gathered=return_gathered,
+                  device=lin.weight.device, dtype=lin.weight.dtype)
         with torch.no_grad():
             out.weight.copy_(lin.weight.chunk(world, dim=0)[rank])
             if lin.bias is not None:
@@ -457,9 +469,10 @@ def parallelize_llama(model, process_group=None, shard_lm_head: bool = True, seq
     (``examples/tensor_parallelism_llama.py:104-152``).
 
     ``sequence_parallel``: between the tensor-parallel blocks (embedding, residual stream, norms) every rank
-    keeps only its ``B / world`` samples.  Attention and MLP gather their input (``SampleGather``), their output
-    projections reduce-scatter instead of all-reduce -- fused into the GEMM (``GemmReduceScatter``) -- and the
-    output layer gathers inside its GEMM (``AllGatherGemm``) when ``fused`` and the shapes allow.  Embedding and
+    keeps only its ``B / world`` samples.  ``q_proj`` / ``gate_proj`` and the output layer gather their input
+    inside their GEMM (``AllGatherGemm``) and hand the gathered copy to ``k_proj`` / ``v_proj`` / ``up_proj``; the
+    output projections reduce-scatter inside their GEMM (``GemmReduceScatter``) instead of all-reducing -- as fused
+    kernels when ``fused`` and the shapes allow, as NCCL + cuBLAS otherwise.  Embedding and
     norm weights then see only local samples: their per-sample norms are partial (``sp_local``) and their
     clipped sums are completed by an all-reduce in :class:`TensorParallelDPOptimizer`.  Needs
     ``shard_lm_head`` and a batch divisible by the group size."""
@@ -467,22 +480,22 @@ def parallelize_llama(model, process_group=None, shard_lm_head: bool = True, seq
     sp = sequence_parallel
     if sp and not shard_lm_head:
         raise ValueError("sequence_parallel needs the output layer sharded over the vocabulary")
-    col_mode = "gathered" if sp else "replicated"
     for blk in model.layers:
         att, mlp = blk.self_attn, blk.mlp
         if att.n_heads % world or att.n_kv % world:
             raise ValueError(f"{att.n_heads} query / {att.n_kv} key-value heads do not divide over {world} ranks")
-        for name in ("q_proj", "k_proj", "v_proj"):
-            setattr(att, name, ColumnParallelLinear.from_linear(getattr(att, name), process_group, input_mode=col_mode))
+        for name in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"):
+            owner = att if name in ("q_proj", "k_proj", "v_proj") else mlp
+            first = name in ("q_proj", "gate_proj")            # gathers for its siblings (fused into its GEMM)
+            layer = ColumnParallelLinear.from_linear(
+                getattr(owner, name), process_group, input_mode=("local" if first else "gathered") if sp else "replicated",
+                fused=fused, return_gathered=sp and first)
+            setattr(owner, name, layer)
         att.o_proj = RowParallelLinear.from_linear(att.o_proj, process_group, scatter_output=sp, fused=fused)
         att.n_heads //= world
         att.n_kv //= world
-        for name in ("gate_proj", "up_proj"):
-            setattr(mlp, name, ColumnParallelLinear.from_linear(getattr(mlp, name), process_group, input_mode=col_mode))
         mlp.down_proj = RowParallelLinear.from_linear(mlp.down_proj, process_group, scatter_output=sp, fused=fused)
         if sp:
-            att.sp_gather = SampleGather(process_group)
-            mlp.sp_gather = SampleGather(process_group)
             for norm in (blk.input_layernorm, blk.post_attention_layernorm):
                 _mark_sample_local(norm)
     if shard_lm_head:

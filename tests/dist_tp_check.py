@@ -123,6 +123,8 @@ def check_sequence_parallel_llama(rank, world):
         if fused:
             assert "_ag" in model.lm_head.__dict__, "the output layer did not take the fused all-gather GEMM"
             assert "_rs" in model.layers[0].self_attn.o_proj.__dict__, "o_proj did not take the fused reduce-scatter GEMM"
+            assert "_ag" in model.layers[0].self_attn.q_proj.__dict__, "q_proj did not take the fused all-gather GEMM"
+            assert "_ag" in model.layers[1].mlp.gate_proj.__dict__, "gate_proj did not take the fused all-gather GEMM"
     (v0, n0, w0, e0), (v1, n1, w1, e1) = results[False], results[True]
     assert abs(v0 - v1) < 2e-2, (v0, v1)
     torch.testing.assert_close(n0, n1, rtol=3e-2, atol=1e-3)
