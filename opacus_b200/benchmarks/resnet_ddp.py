@@ -47,7 +47,11 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
 
-    from opacus_b200.models import resnet18_gn
+    if args.impl == "reference":           # stock-PyTorch definition, nothing of this package on the reference's path
+        sys.path.insert(0, os.path.join(root, "baseline"))
+        from resnet_plain import resnet18_gn
+    else:
+        from opacus_b200.models import resnet18_gn
 
     torch.manual_seed(0)
     model = resnet18_gn().cuda()
