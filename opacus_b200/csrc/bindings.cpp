@@ -9,6 +9,8 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <mutex>
+#include <sstream>
+#include <stdexcept>
 #include <vector>
 
 #include "api.h"
@@ -38,14 +40,21 @@ StatusBlock& status_for(int device) {
   return s;
 }
 
+// Surfaces in Python as opacus_b200.utils.errors.CommTimeoutError (a RuntimeError).
+struct WaitTimeout : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
 void raise_if_failed(int device) {
   StatusBlock& s = status_for(device);
   const uint32_t code = *reinterpret_cast<volatile uint32_t*>(s.host);
   if (code != 0) {
     const uint32_t blk = s.host[1], d0 = s.host[2], d1 = s.host[3];
     s.host[0] = s.host[1] = s.host[2] = s.host[3] = 0;
-    TORCH_CHECK(false, "opacus_b200: a kernel gave up on a bounded wait (site ", code >> 8, ", code ", code & 0xff,
-                ", block ", blk, ", detail ", d0, "/", d1, "); its results are invalid");
+    std::ostringstream msg;
+    msg << "opacus_b200: a kernel gave up on a bounded wait (site " << (code >> 8) << ", code " << (code & 0xff)
+        << ", block " << blk << ", detail " << d0 << "/" << d1 << "); its results are invalid";
+    throw WaitTimeout(msg.str());
   }
 }
 
@@ -560,6 +569,14 @@ int64_t tensor_entry_size() { return (int64_t)sizeof(DpkTensorEntry); }
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::register_exception_translator([](std::exception_ptr p) {
+    try {
+      if (p) std::rethrow_exception(p);
+    } catch (const WaitTimeout& e) {
+      py::object cls = py::module_::import("opacus_b200.utils.errors").attr("CommTimeoutError");
+      PyErr_SetString(cls.ptr(), e.what());
+    }
+  });
   m.def("gram_pair_norm", &gram_pair_norm);
   m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
   m.def("wgrad_tn", &wgrad_tn);

@@ -41,6 +41,7 @@ import torch.nn as nn
 from .. import ops
 from ..layers.dp_rnn import DPGRU, DPLSTM, DPRNN, RNNLinear
 from ..utils.module_utils import requires_grad, trainable_modules, trainable_parameters
+from ..utils.tracing import phase, record_clipping
 from .functorch import ft_compute_per_sample_gradient
 from .grad_sample_module import (
     _OutputTap,
@@ -203,6 +204,10 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
     def _on_output_grad(self, module, grad_out):
         if not self.hooks_enabled:
             return
+        with phase("dp/norm"):
+            self._capture_site(module, grad_out)
+
+    def _capture_site(self, module, grad_out):
         backprops = grad_out.detach()
         batch_dim = 0 if self.batch_first or type(module) is RNNLinear else 1
         if not hasattr(module, "max_batch_len"):
@@ -345,6 +350,18 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             return coef
         self._add_cross_terms()
         coef = self.get_clipping_coef()
+        norms = getattr(self, "per_sample_gradient_norms", None)
+        if norms is not None and not isinstance(self.max_grad_norm, (list, tuple)):
+            record_clipping(norms, float(self.max_grad_norm))
+        with phase("dp/clipped_sum"):
+            self._write_clipped_sums(coef)
+        for p in self.trainable_parameters:
+            if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
+                p.grad = torch.zeros_like(p)
+        self._reset_single_pass_state()
+        return coef
+
+    def _write_clipped_sums(self, coef):
         for site in self._sites:
             mtype = self._get_module_type(site.module)
             c = self._site_coef(site, coef)
@@ -375,11 +392,6 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                     p.grad = g if g._base is None else g.clone()
                 else:
                     p.grad.add_(g)
-        for p in self.trainable_parameters:
-            if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
-                p.grad = torch.zeros_like(p)
-        self._reset_single_pass_state()
-        return coef
 
     # ------------------------------------------------------- two-pass protocol
     def capture_activations_hook(self, module: nn.Module, forward_input: List[torch.Tensor],

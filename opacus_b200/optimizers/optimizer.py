@@ -26,6 +26,8 @@ import torch
 from torch import nn
 from torch.optim import Optimizer
 
+from ..utils.tracing import phase
+
 from .. import ops
 from .utils import params
 
@@ -267,6 +269,10 @@ class DPOptimizer(Optimizer):
         return plan_for(self)
 
     def step(self, closure: Optional[Callable[[], float]] = None) -> Optional[float]:
+        with phase("dp/optimizer_step"):
+            return self._step(closure)
+
+    def _step(self, closure: Optional[Callable[[], float]] = None) -> Optional[float]:
         if closure is not None:
             with torch.enable_grad():
                 closure()

@@ -138,6 +138,12 @@ class ShardedDataParallel(nn.Module):
     # ------------------------------------------------------------------ the step
     def optimizer_step(self, dpopt, closure=None):
         """Tail of ``FSDPOptimizerFastGradientClipping.step`` when this engine owns the parameters."""
+        from ..utils.tracing import phase
+
+        with phase("dp/optimizer_step"):
+            return self._optimizer_step(dpopt, closure)
+
+    def _optimizer_step(self, dpopt, closure=None):
         from ..ops import _cuda
 
         if closure is not None:

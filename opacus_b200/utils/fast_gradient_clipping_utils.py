@@ -14,6 +14,8 @@ from typing import Union
 
 import torch
 
+from .tracing import phase
+
 
 class DPTensorFastGradientClipping:
     """Per-sample losses with scalar-tensor manners (``item``, ``detach``,
@@ -87,7 +89,8 @@ class DPTensorFastGradientClipping:
         reduced = self._reduced()
         if getattr(self.module, "single_pass", False):
             self.optimizer.zero_grad()
-            reduced.backward()
+            with phase("dp/backward"):
+                reduced.backward()
             self._before_finish()
             self.module.finish_single_pass()
             return

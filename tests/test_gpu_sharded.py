@@ -206,3 +206,30 @@ def test_fused_collective_gemms_single_rank():
         y = rs(x, w)
         assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
     _cuda.check_status()
+
+
+@pytest.mark.gpu
+def test_bounded_wait_runs_out_and_is_reported():
+    """A rank whose peer never raises its flag: the kernel gives up after its time limit, the host gets
+    CommTimeoutError on the next check, and the CUDA context keeps working."""
+    from opacus_b200.ops import _cuda
+    from opacus_b200.utils.errors import CommTimeoutError
+
+    C = _cuda.load()
+    dev = torch.device("cuda", 0)
+    _cuda.check_status()
+    slots = [torch.zeros(2 * 2 * 64, device=dev) for _ in range(2)]          # "rank 1" is a buffer nobody drives
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(2)]
+    part = torch.rand(8, device=dev)
+    C.norm_allreduce_clip([s.data_ptr() for s in slots], [f.data_ptr() for f in flags], part, None, 8, 64, 0, 0, 1,
+                          1.0, dev)
+    torch.cuda.synchronize()                    # returns: the wait is limited to about two seconds
+    with pytest.raises(CommTimeoutError):
+        _cuda.check_status()
+    _cuda.check_status()                        # the report is consumed
+    x = torch.full((1024,), 2.0, device=dev)
+    assert x.sum().item() == 2048.0             # the context is alive
+    red_total, _ = C.norm_allreduce_clip([slots[0].data_ptr()], [flags[0].data_ptr()], part, None, 8, 64, 0, 32, 1, 1.0, dev)
+    torch.cuda.synchronize()
+    assert torch.equal(red_total, part)
+    _cuda.check_status()

@@ -346,3 +346,30 @@ def test_checkpoint_interchange_with_reference(tmp_path, writer, reader):
     assert abs(saved["EPS"] - loaded["EPS"]) < 1e-9
     assert abs(saved["W"] - loaded["W"]) < 1e-6
     assert loaded["EPOCH"] == 7 and loaded["STEPS"] == 4
+
+
+def test_step_recorder_collects_phases_and_clipping():
+    from opacus_b200.utils.tracing import StepRecorder
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 3))
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    ds = TensorDataset(torch.randn(16, 6), torch.randint(0, 3, (16,)))
+    pe = PrivacyEngine()
+    m, o, crit, dl = pe.make_private(module=model, optimizer=opt, criterion=nn.CrossEntropyLoss(),
+                                     data_loader=DataLoader(ds, batch_size=8), noise_multiplier=1.0, max_grad_norm=0.01,
+                                     grad_sample_mode="ghost", poisson_sampling=False)
+    x, y = next(iter(dl))
+    with StepRecorder() as rec:
+        o.zero_grad()
+        crit(m(x), y).backward()
+        o.step()
+    s = rec.summary()
+    assert {"dp/backward", "dp/norm", "dp/clipped_sum", "dp/optimizer_step"} <= set(s["phases_ms"])
+    assert s["calls"]["dp/norm"] == 2 and s["batch"] == 8
+    assert s["clip_fraction"] == 1.0 and s["norm_max"] >= s["norm_mean"] > 0.01
+    # outside the recorder the markers are inert
+    o.zero_grad()
+    crit(m(x), y).backward()
+    o.step()
+    assert rec.summary()["calls"]["dp/norm"] == 2
