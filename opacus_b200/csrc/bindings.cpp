@@ -40,21 +40,15 @@ StatusBlock& status_for(int device) {
   return s;
 }
 
-// Surfaces in Python as opacus_b200.utils.errors.CommTimeoutError (a RuntimeError).
-struct WaitTimeout : std::runtime_error {
-  using std::runtime_error::runtime_error;
-};
-
+// The message below is turned into opacus_b200.utils.errors.CommTimeoutError by the Python wrapper (ops/_cuda.py).
 void raise_if_failed(int device) {
   StatusBlock& s = status_for(device);
   const uint32_t code = *reinterpret_cast<volatile uint32_t*>(s.host);
   if (code != 0) {
     const uint32_t blk = s.host[1], d0 = s.host[2], d1 = s.host[3];
     s.host[0] = s.host[1] = s.host[2] = s.host[3] = 0;
-    std::ostringstream msg;
-    msg << "opacus_b200: a kernel gave up on a bounded wait (site " << (code >> 8) << ", code " << (code & 0xff)
-        << ", block " << blk << ", detail " << d0 << "/" << d1 << "); its results are invalid";
-    throw WaitTimeout(msg.str());
+    TORCH_CHECK(false, "opacus_b200: a kernel gave up on a bounded wait (site ", code >> 8, ", code ", code & 0xff,
+                ", block ", blk, ", detail ", d0, "/", d1, "); its results are invalid");
   }
 }
 
@@ -564,19 +558,14 @@ at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at
 
 void check_status(int64_t device) { raise_if_failed((int)device); }
 
+// Raises what a timed-out kernel makes the next call raise (host only; for tests of the error path).
+void raise_wait_timeout_for_test() { TORCH_CHECK(false, "opacus_b200: a kernel gave up on a bounded wait (test)"); }
+
 int64_t tensor_entry_size() { return (int64_t)sizeof(DpkTensorEntry); }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  py::register_exception_translator([](std::exception_ptr p) {
-    try {
-      if (p) std::rethrow_exception(p);
-    } catch (const WaitTimeout& e) {
-      py::object cls = py::module_::import("opacus_b200.utils.errors").attr("CommTimeoutError");
-      PyErr_SetString(cls.ptr(), e.what());
-    }
-  });
   m.def("gram_pair_norm", &gram_pair_norm);
   m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
   m.def("wgrad_tn", &wgrad_tn);
@@ -602,5 +591,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_backward", &swiglu_backward);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
+  m.def("_raise_wait_timeout_for_test", &raise_wait_timeout_for_test);
   m.def("tensor_entry_size", &tensor_entry_size);
 }

@@ -33,8 +33,35 @@ def load():
             "opacus_b200: the native extension is not built. Run `python -m opacus_b200.build` "
             "(needs nvcc; compiles for sm_100a) before using CUDA tensors."
         ) from e
-    _C = mod
-    return mod
+    _C = _Native(mod)
+    return _C
+
+
+class _Native:
+    """The native module with one translation: the RuntimeError by which a call reports that an earlier kernel
+    gave up on a bounded wait becomes :class:`CommTimeoutError`."""
+
+    def __init__(self, mod):
+        self._mod = mod
+
+    def __getattr__(self, name):
+        fn = getattr(self._mod, name)
+        if not callable(fn):
+            return fn
+
+        def call(*args, **kwargs):
+            try:
+                return fn(*args, **kwargs)
+            except RuntimeError as e:
+                if "gave up on a bounded wait" in str(e):
+                    from ..utils.errors import CommTimeoutError
+
+                    raise CommTimeoutError(str(e).split("\n")[0]) from None
+                raise
+
+        call.__name__ = name
+        self.__dict__[name] = call
+        return call
 
 
 def check_status(device=None):
