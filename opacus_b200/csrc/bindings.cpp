@@ -47,13 +47,23 @@ void raise_if_failed(int device) {
   if (code != 0) {
     const uint32_t blk = s.host[1], d0 = s.host[2], d1 = s.host[3];
     s.host[0] = s.host[1] = s.host[2] = s.host[3] = 0;
-    TORCH_CHECK(false, "opacus_b200: a kernel gave up on a bounded wait (site ", code >> 8, ", code ", code & 0xff,
-                ", block ", blk, ", detail ", d0, "/", d1, "); its results are invalid");
+    // Formatted with snprintf on purpose: number insertion into a std::ostream (which TORCH_CHECK uses for
+    // non-string pieces) crashed in processes that had the CUDA libraries loaded.
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "opacus_b200: a kernel gave up on a bounded wait (site %u, code %u, block %u, detail %u/%u); "
+             "its results are invalid", code >> 8, code & 0xffu, blk, d0, d1);
+    TORCH_CHECK(false, msg);
   }
 }
 
+// Error messages are assembled with snprintf and handed to TORCH_CHECK as ONE string: anything else goes through a
+// std::ostream inside TORCH_CHECK, and stream formatting crashed in processes that had the CUDA libraries loaded.
 void check(int rc, const char* what) {
-  TORCH_CHECK(rc == 0, "opacus_b200: ", what, " failed: ", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+  if (rc == 0) return;
+  char msg[256];
+  snprintf(msg, sizeof(msg), "opacus_b200: %s failed: %s", what, cudaGetErrorString(static_cast<cudaError_t>(rc)));
+  TORCH_CHECK(false, msg);
 }
 
 int elem_kind(const at::Tensor& t) {
@@ -61,12 +71,19 @@ int elem_kind(const at::Tensor& t) {
     case at::kFloat: return 0;
     case at::kBFloat16: return 1;
     case at::kHalf: return 2;
-    default: TORCH_CHECK(false, "opacus_b200: unsupported dtype ", t.scalar_type());
+    default: {
+      char msg[128];
+      snprintf(msg, sizeof(msg), "opacus_b200: unsupported dtype %s", c10::toString(t.scalar_type()));
+      TORCH_CHECK(false, msg);
+    }
   }
 }
 
 void need_cuda_contig(const at::Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "opacus_b200: ", name, " must be a contiguous CUDA tensor");
+  if (t.is_cuda() && t.is_contiguous()) return;
+  char msg[160];
+  snprintf(msg, sizeof(msg), "opacus_b200: %s must be a contiguous CUDA tensor", name);
+  TORCH_CHECK(false, msg);
 }
 
 cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
