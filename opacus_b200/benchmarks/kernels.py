@@ -108,6 +108,25 @@ def run(op, B, T, din, dout, iters=20):
         byts = n * 4.0 * 8        # read+write of param, grad, exp_avg, exp_avg_sq
         ms = _time(one, iters, flush)
         rows.append(("fused_dp_adamw_step", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    if op in ("sharded_step", "all"):
+        # the one-kernel reduce + noise + AdamW + publish step with a one-rank group (no peers: pure streaming)
+        n = 1 << 27
+        grad = torch.zeros(n, device=dev)
+        param = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        flags = torch.zeros(64, device=dev, dtype=torch.int32)
+        master, m1, m2 = (torch.zeros(n, device=dev) for _ in range(3))
+        epoch = [0]
+
+        def sharded():
+            epoch[0] += 1
+            C.sharded_dp_step([grad.data_ptr()], [param.data_ptr()], [flags.data_ptr()], master, m1, m2, 0, n, 0, True,
+                              epoch[0], 2, False, False, 1e-4, 0.0, 0.0, 0.01, 0.9, 0.999, 1e-8, 0.1, 0.0316, 1.0, 0.125,
+                              1234, 4 * epoch[0] * n)
+
+        byts = n * (4.0 * 7 + 2.0)     # read grad/master/m/v, write master/m/v (fp32) + bf16 weights
+        ms = _time(sharded, iters, flush)
+        rows.append(("sharded_step AdamW + noise (1 rank, 134 M)", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+        del grad, param, master, m1, m2
     if op in ("cross_entropy", "all"):
         from ..layers import fused_cross_entropy
 
