@@ -361,8 +361,35 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         self._reset_single_pass_state()
         return coef
 
+    # Clipped sums of different layers are independent GEMMs.  Issued alternately on two CUDA streams, the
+    # tail of one (persistent CTAs that run out of tiles: 256 tiles on 148 SMs is 1.73 waves) is filled by the
+    # head of the next.  Sites that write the same parameter stay on one stream, in order.
+    overlap_clipped_sums = True
+
     def _write_clipped_sums(self, coef):
+        side = main = None
+        if self.overlap_clipped_sums and coef.is_cuda and len(self._sites) > 2:
+            main = torch.cuda.current_stream(coef.device)
+            side = getattr(self, "_side_stream", None)
+            if side is None or side.device != coef.device:
+                side = self._side_stream = torch.cuda.Stream(device=coef.device)
+            side.wait_stream(main)
+        lane_of = {}
         for site in self._sites:
+            if side is not None:
+                ps = [id(p) for _, p in trainable_parameters(site.module)]
+                lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % 2)
+                for i in ps:
+                    lane_of[i] = lane
+                with torch.cuda.stream(side if lane else main):
+                    self._write_site(site, coef)
+            else:
+                self._write_site(site, coef)
+        if side is not None:
+            main.wait_stream(side)
+
+    def _write_site(self, site, coef):
+        if True:
             mtype = self._get_module_type(site.module)
             c = self._site_coef(site, coef)
             if site.kept_grad_samples is not None:
