@@ -236,3 +236,23 @@ def test_hooks_mode_without_autograd_weight_gradients():
         torch.testing.assert_close(p1.grad_sample, p2.grad_sample)
     b.eval()
     assert b(x).shape == (7, 5)
+
+
+def test_dense_axis_order_of_permuted_views():
+    """The clip-weighted sum of a permuted dense view (the channels-last conv gradient) is taken in storage order."""
+    from opacus_b200.ops._cuda import _dense_order
+
+    base = torch.randn(5, 4, 3, 2, 6)                  # [B, O, kh, kw, C]
+    view = base.permute(0, 1, 4, 2, 3)                 # [B, O, C, kh, kw]
+    order = _dense_order(view)
+    assert order == [0, 1, 3, 4, 2] and view.permute(order).is_contiguous()
+    assert _dense_order(base) is None                  # already contiguous
+    assert _dense_order(base[:, :, :, :, ::2]) is None  # strided, not a permutation of a dense buffer
+    # the result mapped back to logical axes equals the plain weighted sum
+    c = torch.rand(5)
+    phys = view.permute(order)
+    out = (phys * c.view(-1, 1, 1, 1, 1)).sum(0)
+    inv = [0] * 4
+    for pos, d in enumerate(order[1:]):
+        inv[d - 1] = pos
+    torch.testing.assert_close(out.permute(inv), (view * c.view(-1, 1, 1, 1, 1)).sum(0))
