@@ -11,6 +11,17 @@ Sharded parameters carry ``tp_sharded = True``; the "ghost_tp" controller sums
 their squared per-sample norms over the group and counts replicated
 parameters once (``opacus/grad_sample/grad_sample_module_fast_gradient_clipping_tp.py:65-115``).
 
+Sequence-parallel form (``parallelize_llama(sequence_parallel=True)``): between
+two tensor-parallel blocks the activations are sharded over *samples*; a
+column-parallel layer with ``input_mode="local"`` gathers its input inside its
+GEMM and a row-parallel layer with ``scatter_output`` reduce-scatters inside its
+GEMM (``parallel/fused_tp.py``), so the two all-reduces become an all-gather
+and a reduce-scatter that overlap the matrix products, and everything outside
+the blocks (norms, residual stream, embedding) runs on ``1 / world`` of the
+batch.  Parameters of those outside modules carry ``sp_local = True``: their
+per-sample norms are partial per rank and their clipped sums are completed by
+an all-reduce in :class:`TensorParallelDPOptimizer`.
+
 The reference obtains the same layout from ``parallelize_module`` with
 ``ColwiseParallel`` / ``RowwiseParallel`` DTensors
 (``examples/tensor_parallelism_llama.py:104-152``) and cannot train replicated
