@@ -60,6 +60,11 @@ class ShardedDataParallel(nn.Module):
         for p in module.parameters():
             if not p.requires_grad or p in self._offsets:
                 continue
+            if getattr(p, "tp_sharded", False):
+                # Ranks of a tensor-parallel group run this engine with the same seed and the same flat layout, so
+                # two shards of one weight would receive the SAME noise values: correlated noise is not the
+                # Gaussian mechanism.  Independent streams per tensor-parallel rank are not implemented.
+                raise NotImplementedError("ShardedDataParallel over tensor-parallel shards (TP x FSDP) is not supported")
             self._offsets[p] = total
             self._params.append(p)
             total += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
