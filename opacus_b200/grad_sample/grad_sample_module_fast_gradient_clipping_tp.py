@@ -71,6 +71,7 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
 
     # ---- single-pass bookkeeping: sharded and replicated parameters are kept apart
     _use_total_fastpath = False
+    overlap_norms = False        # the rules of this controller issue collectives; keep them on the main stream
 
     # ---- activations sharded over samples between the tensor-parallel blocks (sequence parallelism)
     def _world(self) -> int:
