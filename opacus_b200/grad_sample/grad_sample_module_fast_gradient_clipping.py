@@ -388,28 +388,33 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
     # tail of one (persistent CTAs that run out of tiles: 256 tiles on 148 SMs is 1.73 waves) is filled by the
     # head of the next.  Sites that write the same parameter stay on one stream, in order.
     overlap_clipped_sums = True
+    clipped_sum_streams = 2
 
     def _write_clipped_sums(self, coef):
-        side = main = None
+        lanes = None
         if self.overlap_clipped_sums and coef.is_cuda and len(self._sites) > 2:
             main = torch.cuda.current_stream(coef.device)
-            side = getattr(self, "_side_stream", None)
-            if side is None or side.device != coef.device:
-                side = self._side_stream = torch.cuda.Stream(device=coef.device)
-            side.wait_stream(main)
+            sides = getattr(self, "_side_streams", None)
+            if sides is None or sides[0].device != coef.device or len(sides) != self.clipped_sum_streams - 1:
+                sides = self._side_streams = [torch.cuda.Stream(device=coef.device)
+                                              for _ in range(self.clipped_sum_streams - 1)]
+            for st in sides:
+                st.wait_stream(main)
+            lanes = [main] + sides
         lane_of = {}
         for site in self._sites:
-            if side is not None:
+            if lanes is not None:
                 ps = [id(p) for _, p in trainable_parameters(site.module)]
-                lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % 2)
+                lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % len(lanes))
                 for i in ps:
                     lane_of[i] = lane
-                with torch.cuda.stream(side if lane else main):
+                with torch.cuda.stream(lanes[lane]):
                     self._write_site(site, coef)
             else:
                 self._write_site(site, coef)
-        if side is not None:
-            main.wait_stream(side)
+        if lanes is not None:
+            for st in lanes[1:]:
+                lanes[0].wait_stream(st)
 
     def _write_site(self, site, coef):
         if True:
