@@ -128,8 +128,6 @@ def run(op, B, T, din, dout, iters=20):
         rows.append(("sharded_step AdamW + noise (1 rank, 134 M)", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
         del grad, param, master, m1, m2
     if op in ("cross_entropy", "all"):
-        from ..layers import fused_cross_entropy
-
         V = 128256
         logits = torch.randn(B * T, V, device=dev, dtype=torch.bfloat16, requires_grad=True)
         tgt = torch.randint(0, V, (B * T,), device=dev)

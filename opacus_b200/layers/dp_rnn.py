@@ -20,7 +20,7 @@ not supported.
 import math
 import numbers
 import warnings
-from typing import List, Optional, Tuple, Type, Union
+from typing import List, Optional, Type, Union
 
 import torch
 import torch.nn as nn

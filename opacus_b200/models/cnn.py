@@ -1,7 +1,6 @@
 """The small MNIST-style CNN used for CPU runs: two conv layers with max
 pooling of stride 1 (which makes the flattened size 512) and two linear layers
 (same architecture as ``examples/mnist.py:38-55`` of the reference)."""
-import torch
 import torch.nn as nn
 import torch.nn.functional as F
 

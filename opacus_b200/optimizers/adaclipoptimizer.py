@@ -9,13 +9,11 @@ Behavioural parity: ``opacus/optimizers/adaclipoptimizer.py:34-191``.
 from __future__ import annotations
 
 import logging
-import math
 from typing import Callable, Optional
 
 import torch
 from torch.optim import Optimizer
 
-from .. import ops
 from .optimizer import DPOptimizer, _check_processed_flag, _generate_noise, _mark_as_processed
 
 logger = logging.getLogger(__name__)

@@ -8,7 +8,7 @@ Behavioural parity: ``opacus/optimizers/optimizer_fast_gradient_clipping.py:36-2
 from __future__ import annotations
 
 import logging
-from typing import Callable, Optional
+from typing import Optional
 
 import torch
 from torch.optim import Optimizer

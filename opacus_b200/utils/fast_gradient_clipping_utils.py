@@ -10,8 +10,6 @@ With a single-pass module that takes one backward pass followed by
 
 Behavioural parity: ``opacus/utils/fast_gradient_clipping_utils.py:26-276``.
 """
-from typing import Union
-
 import torch
 
 from .tracing import phase

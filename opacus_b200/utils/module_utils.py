@@ -3,7 +3,6 @@
 Behavioural parity: ``opacus/utils/module_utils.py:34-165`` (without the
 import-time ``logging.basicConfig`` side effect of the original).
 """
-import copy
 import io
 import logging
 from typing import Dict, Iterable, Tuple

@@ -4,7 +4,6 @@ with what the gradient engine produced for the whole batch.
 
 Behavioural parity: ``opacus/utils/per_sample_gradients_utils.py:28-439``.
 """
-import copy
 from contextlib import contextmanager
 from typing import Callable, Dict, Iterable, List, Union
 
