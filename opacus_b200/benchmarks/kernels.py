@@ -152,6 +152,17 @@ def run(op, B, T, din, dout, iters=20):
         rows.append(("swiglu forward", ms, 3 * byts / ms / 1e6, "GB/s", 3 * byts / ms / 1e6 / bw_peak))
         ms = _time(lambda: C.swiglu_backward(ga, up, ga), iters, flush)
         rows.append(("swiglu backward", ms, 5 * byts / ms / 1e6, "GB/s", 5 * byts / ms / 1e6 / bw_peak))
+    if op in ("rmsnorm", "all"):
+        xs = torch.randn(B * T, din, device=dev, dtype=torch.bfloat16)
+        dl = torch.randn(B * T, din, device=dev, dtype=torch.bfloat16)
+        wn = torch.ones(din, device=dev, dtype=torch.bfloat16)
+        byts = xs.numel() * 2.0
+        if din % 8 == 0 and din <= 8192:
+            ms = _time(lambda: C.add_rmsnorm_forward(xs, dl, wn, 1e-5), iters, flush)
+            rows.append(("add + rmsnorm forward", ms, 4 * byts / ms / 1e6, "GB/s", 4 * byts / ms / 1e6 / bw_peak))
+            _, hs, rs = C.add_rmsnorm_forward(xs, dl, wn, 1e-5)
+            ms = _time(lambda: C.add_rmsnorm_backward(xs, dl, hs, rs, wn), iters, flush)
+            rows.append(("add + rmsnorm backward", ms, 4 * byts / ms / 1e6, "GB/s", 4 * byts / ms / 1e6 / bw_peak))
     _cuda.check_status()
     print(f"shape B={B} T={T} d_in={din} d_out={dout}; peaks: {tf_peak} TFLOP/s bf16, {bw_peak} GB/s ({src})")
     for name, ms, rate, unit, frac in rows:

@@ -178,6 +178,14 @@ int dpk_swiglu_forward(const void* gate, const void* up, void* h, int kind, int6
 int dpk_swiglu_backward(const void* gate, const void* up, const void* dh, void* dgate, void* dup, int kind, int64_t n,
                         cudaStream_t stream);
 
+// Residual add + RMSNorm over [rows, D] (D a multiple of 8, at most 8192; kind 0 fp32 / 1 bf16 / 2 fp16; w has the same
+// type).  forward: h = x + delta (delta NULL: h = x and h_out is not written), y = h * rstd * w, rstd[rows] kept.
+// backward: dh = (dres or 0) + gradient of the norm with respect to h.
+int dpk_add_rmsnorm_forward(const void* x, const void* delta, const void* w, void* h_out, void* y_out, float* rstd_out,
+                            int kind, int64_t rows, int64_t D, float eps, cudaStream_t stream);
+int dpk_add_rmsnorm_backward(const void* dy, const void* dres, const void* h, const float* rstd, const void* w,
+                             void* dh_out, int kind, int64_t rows, int64_t D, cudaStream_t stream);
+
 // Standard normal samples (testing the generator): out[i] for i < n.
 int dpk_philox_normal(float* out, int64_t n, uint64_t seed, uint64_t offset, float std, cudaStream_t stream);
 

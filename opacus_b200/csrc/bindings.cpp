@@ -565,6 +565,54 @@ std::vector<at::Tensor> swiglu_backward(at::Tensor gate, at::Tensor up, at::Tens
   return {dg, du};
 }
 
+// x, delta (optional) [..., D], w [D], same dtype -> {y, h (== x when delta is absent), rstd fp32 [rows]}
+std::vector<at::Tensor> add_rmsnorm_forward(at::Tensor x, c10::optional<at::Tensor> delta, at::Tensor w, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(w, "w");
+  const int64_t D = w.numel(), rows = x.numel() / D;
+  TORCH_CHECK(x.size(-1) == D && w.scalar_type() == x.scalar_type(), "x [..., D] and w [D] of one dtype expected");
+  at::Tensor h = x;
+  const void* dp = nullptr;
+  void* hp = nullptr;
+  if (delta.has_value()) {
+    need_cuda_contig(*delta, "delta");
+    TORCH_CHECK(delta->sizes() == x.sizes() && delta->scalar_type() == x.scalar_type(), "delta must match x");
+    h = at::empty_like(x);
+    dp = delta->data_ptr();
+    hp = h.data_ptr();
+  }
+  at::Tensor y = at::empty_like(x);
+  at::Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  check(dpk_add_rmsnorm_forward(x.data_ptr(), dp, w.data_ptr(), hp, y.data_ptr(), rstd.data_ptr<float>(), elem_kind(x),
+                                rows, D, (float)eps, stream()),
+        "add_rmsnorm_forward");
+  return {y, h, rstd};
+}
+
+at::Tensor add_rmsnorm_backward(at::Tensor dy, c10::optional<at::Tensor> dres, at::Tensor h, at::Tensor rstd,
+                                at::Tensor w) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  need_cuda_contig(dy, "dy");
+  need_cuda_contig(h, "h");
+  need_cuda_contig(rstd, "rstd");
+  need_cuda_contig(w, "w");
+  const int64_t D = w.numel(), rows = h.numel() / D;
+  TORCH_CHECK(dy.sizes() == h.sizes() && dy.scalar_type() == h.scalar_type() && w.scalar_type() == h.scalar_type() &&
+              rstd.scalar_type() == at::kFloat && rstd.numel() == rows, "dy, h [..., D], w [D], rstd fp32 [rows]");
+  const void* rp = nullptr;
+  if (dres.has_value()) {
+    need_cuda_contig(*dres, "dres");
+    TORCH_CHECK(dres->sizes() == h.sizes() && dres->scalar_type() == h.scalar_type(), "dres must match h");
+    rp = dres->data_ptr();
+  }
+  at::Tensor dh = at::empty_like(h);
+  check(dpk_add_rmsnorm_backward(dy.data_ptr(), rp, h.data_ptr(), rstd.data_ptr<float>(), w.data_ptr(), dh.data_ptr(),
+                                 elem_kind(h), rows, D, stream()),
+        "add_rmsnorm_backward");
+  return dh;
+}
+
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
   at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
@@ -606,6 +654,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope", &rope);
   m.def("swiglu_forward", &swiglu_forward);
   m.def("swiglu_backward", &swiglu_backward);
+  m.def("add_rmsnorm_forward", &add_rmsnorm_forward);
+  m.def("add_rmsnorm_backward", &add_rmsnorm_backward);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
   m.def("_raise_wait_timeout_for_test", &raise_wait_timeout_for_test);

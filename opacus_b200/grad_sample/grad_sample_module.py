@@ -102,6 +102,17 @@ class _OutputTap(torch.autograd.Function):
         return grad_out, None, None, None
 
 
+def captured_inputs(module, inputs, output):
+    """What a forward hook keeps for the per-sample rules: the detached inputs.  A module whose parameters
+    act on a tensor it computes itself and also returns (a fused residual add) names that output by
+    ``dp_activation_output``; it then stands in for the first input."""
+    kept = [t.detach() if isinstance(t, torch.Tensor) else t for t in inputs]
+    index = getattr(module, "dp_activation_output", None)
+    if index is not None and isinstance(output, (tuple, list)):
+        kept[0] = output[index].detach()
+    return kept
+
+
 class GradSampleHooks(AbstractGradSampleHooks):
     GRAD_SAMPLERS = {}
 
@@ -233,7 +244,7 @@ class GradSampleHooks(AbstractGradSampleHooks):
             return
         if not hasattr(module, "activations"):
             module.activations = []
-        module.activations.append([t.detach() if isinstance(t, torch.Tensor) else t for t in forward_input])
+        module.activations.append(captured_inputs(module, forward_input, _forward_output))
         for _, p in trainable_parameters(module):
             p._forward_counter += 1
 
@@ -244,6 +255,9 @@ class GradSampleHooks(AbstractGradSampleHooks):
         backprops = forward_output[0].detach()
         activations, backprops = self.rearrange_grad_samples(
             module=module, backprops=backprops, loss_reduction=loss_reduction, batch_first=batch_first)
+        own = module.__dict__.pop("_dp_activation", None)       # see _prepare_site of the ghost controller
+        if own is not None:
+            activations = [own.detach()] + list(activations[1:])
 
         if isinstance(module, _STACKED_TYPES) and self._has_rule(module):
             ready = self._queue_stacked_call(module, activations, backprops)
@@ -371,5 +385,6 @@ def _get_batch_size(*, module: nn.Module, batch_dim: int) -> int:
     (they differ across time steps of a packed sequence)."""
     best = 0
     for acts in module.activations:
-        best = max(best, acts[-1].shape[batch_dim])
+        tensors = [t for t in acts if isinstance(t, torch.Tensor)]       # optional inputs may be None
+        best = max(best, tensors[-1].shape[batch_dim])
     return best

@@ -47,6 +47,7 @@ from .grad_sample_module import (
     _OutputTap,
     _STACKED_TYPES,
     GradSampleHooks,
+    captured_inputs,
     create_or_accumulate_grad_sample,
     promote_current_grad_sample,
 )
@@ -189,7 +190,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             return None
         if not hasattr(module, "activations"):
             module.activations = []
-        module.activations.append([t.detach() if isinstance(t, torch.Tensor) else t for t in inputs])
+        module.activations.append(captured_inputs(module, inputs, output))
         for sub, name, p in saved:
             p._forward_counter += 1
         first = output[0] if isinstance(output, (tuple, list)) else output
@@ -311,7 +312,12 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         return 1
 
     def _prepare_site(self, module, activations, backprops):
-        """Last chance to exchange the captured tensors (e.g. gather a sharded output gradient)."""
+        """Last chance to exchange the captured tensors (e.g. gather a sharded output gradient).  A module that
+        computes the tensor its parameters act on inside its own forward (a fused residual add, a gathered
+        input) leaves it in ``_dp_activation``; it then stands in for the first module input."""
+        own = module.__dict__.pop("_dp_activation", None)
+        if own is not None:
+            activations = [own.detach()] + list(activations[1:])
         return activations, backprops
 
     def _align_norm(self, p, v):
@@ -455,7 +461,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             return
         if not hasattr(module, "activations"):
             module.activations = []
-        module.activations.append([t.detach() if isinstance(t, torch.Tensor) else t for t in forward_input])
+        module.activations.append(captured_inputs(module, forward_input, _forward_output))
         ghost_layer = self.use_ghost_clipping and type(module) in self.NORM_SAMPLERS
         for _, p in trainable_parameters(module):
             p._forward_counter += 1

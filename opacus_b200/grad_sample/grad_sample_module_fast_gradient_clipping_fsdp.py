@@ -28,6 +28,7 @@ import torch.nn as nn
 from .. import ops
 from ..utils.module_utils import requires_grad, trainable_parameters
 from .functorch import ft_compute_per_sample_gradient
+from .grad_sample_module import captured_inputs
 from .grad_sample_module_fast_gradient_clipping import GradSampleHooksFastGradientClipping
 from .gsm_base import AbstractGradSampleModule
 
@@ -79,7 +80,7 @@ class GradSampleHooksFastGradientClippingFSDP(GradSampleHooksFastGradientClippin
             return
         if not hasattr(module, "activations"):
             module.activations = []
-        module.activations.append([t.detach() if isinstance(t, torch.Tensor) else t for t in forward_input])
+        module.activations.append(captured_inputs(module, forward_input, _forward_output))
         module._forward_counter = getattr(module, "_forward_counter", 0) + 1
         if self.use_ghost_clipping and module._forward_counter > 1:
             raise NotImplementedError("Parameter tying is not supported with FSDP")

@@ -81,9 +81,7 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
         return self._world() if getattr(module, "sp_local_input", False) else 1
 
     def _prepare_site(self, module, activations, backprops):
-        full_in = module.__dict__.pop("_dp_activation", None)
-        if full_in is not None:                       # the layer gathered its input itself
-            activations = [full_in.detach()] + list(activations[1:])
+        activations, backprops = super()._prepare_site(module, activations, backprops)   # a layer's own gathered input
         if getattr(module, "scatter_output", False):  # the output gradient arrives for this rank's samples only
             from ..parallel.tensor_parallel import _all_gather0
 

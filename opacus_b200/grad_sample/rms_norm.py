@@ -5,10 +5,11 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..layers.add_rms_norm import AddRMSNorm
 from .utils import register_grad_sampler
 
 
-@register_grad_sampler(nn.RMSNorm)
+@register_grad_sampler([nn.RMSNorm, AddRMSNorm])
 def compute_rms_norm_grad_sample(layer: nn.RMSNorm, activations: List[torch.Tensor],
                                  backprops: torch.Tensor) -> Dict[nn.Parameter, torch.Tensor]:
     if layer.weight is None or not layer.weight.requires_grad:

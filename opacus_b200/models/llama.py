@@ -1,19 +1,21 @@
 """Llama-3 style decoder (RMSNorm, rotary embeddings, grouped-query attention,
 SwiGLU) written so that DP training applies directly: every parameter lives in
-an ``nn.Linear``, ``nn.Embedding`` or ``nn.RMSNorm``, and there are no buffers
-(the rotary angles are evaluated on the fly).  On CUDA the rotary embedding
-(with the head transpose) and the SwiGLU gate run as fused kernels of this
-package (``csrc/rope.cu``, ``csrc/swiglu.cu``); on CPU as plain PyTorch.
-
-The same definition is used for this package and for the reference library in
-the benchmarks; only ``tie_embeddings`` differs (ghost clipping in the
-reference rejects shared parameters).
+an ``nn.Linear``, ``nn.Embedding`` or an RMSNorm, and there are no buffers
+(the rotary angles are evaluated on the fly).  On CUDA the rotary embedding,
+the SwiGLU gate and every residual addition together with the RMSNorm that
+follows it run as fused kernels of this package (``csrc/rope.cu``,
+``csrc/swiglu.cu``, ``csrc/rmsnorm.cu``); on CPU as plain PyTorch.  Parameter
+names and shapes are those of a decoder built from ``nn.RMSNorm``, so state
+dicts interchange with the plain definition the benchmarks give the reference
+library (``baseline/llama_plain.py``).
 """
 from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from ..layers.add_rms_norm import AddRMSNorm
 
 
 @dataclass
@@ -162,14 +164,17 @@ class MLP(nn.Module):
 class Block(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        self.input_layernorm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.input_layernorm = AddRMSNorm(cfg.d_model, eps=cfg.norm_eps)
         self.self_attn = Attention(cfg)
-        self.post_attention_layernorm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.post_attention_layernorm = AddRMSNorm(cfg.d_model, eps=cfg.norm_eps)
         self.mlp = MLP(cfg)
 
-    def forward(self, x):
-        x = x + self.self_attn(self.input_layernorm(x))
-        return x + self.mlp(self.post_attention_layernorm(x))
+    def forward(self, h, delta=None):
+        """``h`` is the residual stream without the previous block's MLP output ``delta``; every residual
+        addition happens inside the norm that follows it.  Returns the pair for the next block."""
+        x, h = self.input_layernorm(h, delta)
+        x, h = self.post_attention_layernorm(h, self.self_attn(x))
+        return h, self.mlp(x)
 
 
 class Llama(nn.Module):
@@ -178,7 +183,7 @@ class Llama(nn.Module):
         self.cfg = cfg
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.d_model)
         self.layers = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
-        self.norm = nn.RMSNorm(cfg.d_model, eps=cfg.norm_eps)
+        self.norm = AddRMSNorm(cfg.d_model, eps=cfg.norm_eps)
         self.lm_head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
         self.sp_slice = None      # set by parallelize_llama(sequence_parallel=True): this rank's samples
         self.apply(self._init)
@@ -193,10 +198,10 @@ class Llama(nn.Module):
     def forward(self, ids):
         if self.sp_slice is not None:
             ids = self.sp_slice(ids)
-        x = self.embed_tokens(ids)
+        h, delta = self.embed_tokens(ids), None
         for blk in self.layers:
-            x = blk(x)
-        return self.lm_head(self.norm(x))
+            h, delta = blk(h, delta)
+        return self.lm_head(self.norm(h, delta)[0])
 
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -416,3 +416,36 @@ def test_tied_cross_norm_kernel(B, T, D, V):
     _cuda.load().tied_cross_norm(ids, g_e, a_h, g_h, 1.5, total)
     torch.testing.assert_close(total, want + 1.0, rtol=2e-2, atol=2e-2 * want.abs().max().item())
     _cuda.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("D", [64, 2048, 4096, 1000])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_add_rms_norm_matches_torch(dtype, D, with_delta):
+    """Residual add + RMSNorm in one kernel each way against the two statements in fp32."""
+    from opacus_b200.layers.add_rms_norm import AddRMSNorm
+
+    torch.manual_seed(0)
+    rows = (3, 37)
+    m = AddRMSNorm(D, eps=1e-5).to(_dev(), dtype)
+    m.weight.data.uniform_(0.5, 1.5)
+    x = torch.randn(*rows, D, device=_dev()).to(dtype).requires_grad_()
+    d = torch.randn(*rows, D, device=_dev()).to(dtype).requires_grad_() if with_delta else None
+    gy = torch.randn(*rows, D, device=_dev()).to(dtype)
+    gh = torch.randn(*rows, D, device=_dev()).to(dtype)
+    y, h = m(x, d)
+    (y.float() * gy.float() + h.float() * gh.float()).sum().backward()
+
+    xf = x.detach().float().requires_grad_()
+    df = d.detach().float().requires_grad_() if with_delta else None
+    wf = m.weight.detach().float().requires_grad_()
+    hf = xf + df if with_delta else xf
+    hf_seen = hf.to(dtype).float() if with_delta else hf          # the kernel normalises the rounded sum it returns
+    yf = torch.nn.functional.rms_norm(hf_seen, (D,), wf, 1e-5)
+    (yf * gy.float() + hf * gh.float()).sum().backward()
+    tol = 1e-5 if dtype == torch.float32 else (2e-3 if dtype == torch.float16 else 1e-2)
+    assert _rel(h, hf) < tol and _rel(y, yf) < tol
+    assert _rel(x.grad, xf.grad) < tol
+    if with_delta:
+        assert _rel(d.grad, df.grad) < tol
+    assert _rel(m.weight.grad, wf.grad) < 2 * tol

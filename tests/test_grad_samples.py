@@ -256,3 +256,81 @@ def test_dense_axis_order_of_permuted_views():
     for pos, d in enumerate(order[1:]):
         inv[d - 1] = pos
     torch.testing.assert_close(out.permute(inv), (view * c.view(-1, 1, 1, 1, 1)).sum(0))
+
+
+class _AddNormNet(torch.nn.Module):
+    """Two residual additions, each inside the RMSNorm that follows it (or as separate statements)."""
+
+    def __init__(self, fused):
+        super().__init__()
+        from opacus_b200.layers.add_rms_norm import AddRMSNorm
+
+        cls = AddRMSNorm if fused else torch.nn.RMSNorm
+        self.fused = fused
+        self.a, self.n1, self.b, self.n2 = torch.nn.Linear(12, 12), cls(12, eps=1e-5), torch.nn.Linear(12, 12), cls(12, eps=1e-5)
+        self.head = torch.nn.Linear(12, 3)
+
+    def forward(self, x):
+        if self.fused:
+            y, h = self.n1(x)
+            y, h = self.n2(h, self.a(y))
+            return self.head(h + self.b(y)).mean(1)
+        h = x
+        h = h + self.a(self.n1(h))
+        return self.head(h + self.b(self.n2(h))).mean(1)
+
+
+@pytest.mark.parametrize("mode", ["hooks", "ghost", "ghost_single_pass"])
+def test_add_rms_norm_matches_separate_statements(mode):
+    from opacus_b200 import GradSampleModule
+    from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
+
+    torch.manual_seed(3)
+    plain, fused = _AddNormNet(False), _AddNormNet(True)
+    for p in plain.parameters():
+        p.data.uniform_(-0.7, 0.7)
+    fused.load_state_dict(plain.state_dict())
+    x, y = torch.randn(5, 7, 12), torch.randint(0, 3, (5,))
+    if mode == "hooks":
+        got, want = GradSampleModule(fused), GradSampleModule(plain)
+        for m in (got, want):
+            torch.nn.functional.cross_entropy(m(x), y).backward()
+        for (n, p), q in zip(got.named_parameters(), want.parameters()):
+            assert torch.allclose(p.grad_sample, q.grad_sample, atol=1e-6), n
+    else:
+        norms = []
+        for net in (fused, plain):
+            m = GradSampleModuleFastGradientClipping(net, max_grad_norm=0.1, use_ghost_clipping=True,
+                                                     single_pass=mode == "ghost_single_pass")
+            loss = torch.nn.functional.cross_entropy(m(x), y, reduction="none").mean()
+            loss.backward()
+            norms.append(m.get_norm_sample().clone())
+        assert torch.allclose(norms[0], norms[1], atol=1e-6)
+
+
+def test_llama_matches_plain_definition():
+    """The decoder with fused add+norm modules computes what the plain definition computes from the same state dict."""
+    import dataclasses
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+    from llama_plain import Llama as PlainLlama, LlamaConfig as PlainConfig
+
+    from opacus_b200.models.llama import Llama, LlamaConfig
+
+    cfg = LlamaConfig(vocab_size=97, d_model=64, n_layers=3, n_heads=4, n_kv_heads=2, ffn_dim=128)
+    torch.manual_seed(0)
+    ours = Llama(cfg)
+    for n, p in ours.named_parameters():
+        if "norm" in n:
+            p.data.uniform_(0.5, 1.5)
+    plain = PlainLlama(PlainConfig(**{f.name: getattr(cfg, f.name) for f in dataclasses.fields(PlainConfig)}))
+    plain.load_state_dict(ours.state_dict())
+    ids = torch.randint(0, 97, (2, 11))
+    a, b = ours(ids), plain(ids)
+    assert torch.allclose(a, b, atol=1e-6)
+    a.square().sum().backward()
+    b.square().sum().backward()
+    for (n, p), q in zip(ours.named_parameters(), plain.parameters()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-5), n
