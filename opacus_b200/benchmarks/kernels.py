@@ -121,7 +121,7 @@ def run(op, B, T, din, dout, iters=20):
             epoch[0] += 1
             C.sharded_dp_step([grad.data_ptr()], [param.data_ptr()], [flags.data_ptr()], master, m1, m2, 0, n, 0, True,
                               epoch[0], 2, False, False, 1e-4, 0.0, 0.0, 0.01, 0.9, 0.999, 1e-8, 0.1, 0.0316, 1.0, 0.125,
-                              1234, 4 * epoch[0] * n)
+                              1234, 4 * epoch[0] * n, 0, 0)
 
         byts = n * (4.0 * 7 + 2.0)     # read grad/master/m/v, write master/m/v (fp32) + bf16 weights
         ms = _time(sharded, iters, flush)

@@ -111,6 +111,9 @@ struct DpkShardedStep {
   float* state0;
   float* state1;
   int64_t slice_begin, slice_len;
+  // Elements of the flat space at or beyond noise_split draw their noise at counter index + noise_shift
+  // (a multiple of 8): tensor-parallel ranks pass distinct shifts for their shards and share the rest.
+  int64_t noise_split, noise_shift;
   int32_t world, rank, param_bf16, pad;
   uint32_t epoch, pad2;
   struct DpkStepHyper h;

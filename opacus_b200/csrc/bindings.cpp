@@ -393,7 +393,8 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
                      int64_t slice_begin, int64_t slice_len, int64_t rank, bool param_bf16, int64_t epoch,
                      int64_t kind, bool nesterov, bool first_step, double lr, double momentum, double dampening,
                      double weight_decay, double beta1, double beta2, double eps, double bias_c1,
-                     double bias_c2_sqrt, double noise_std, double inv_scale, int64_t seed, int64_t offset) {
+                     double bias_c2_sqrt, double noise_std, double inv_scale, int64_t seed, int64_t offset,
+                     int64_t noise_split, int64_t noise_shift) {
   c10::cuda::CUDAGuard guard(master.device());
   raise_if_failed(master.get_device());
   const int world = (int)grad_ptrs.size();
@@ -410,6 +411,9 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
   p.state0 = state0.has_value() ? state0->data_ptr<float>() : nullptr;
   p.state1 = state1.has_value() ? state1->data_ptr<float>() : nullptr;
   p.slice_begin = slice_begin; p.slice_len = slice_len;
+  TORCH_CHECK(noise_split >= 0 && noise_shift >= 0 && noise_split % 8 == 0 && noise_shift % 8 == 0,
+              "noise_split and noise_shift must be non-negative multiples of 8");
+  p.noise_split = noise_split; p.noise_shift = noise_shift;
   p.world = world; p.rank = (int)rank; p.param_bf16 = param_bf16 ? 1 : 0;
   p.epoch = (uint32_t)epoch;
   DpkStepHyper& h = p.h;

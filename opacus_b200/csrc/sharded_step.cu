@@ -73,8 +73,9 @@ __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep
         g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
       }
       if (h.noise_std != 0.f) {
-        const uint4 u0 = rng(static_cast<uint64_t>(gi) >> 2, h.offset);
-        const uint4 u1 = rng((static_cast<uint64_t>(gi) >> 2) + 1, h.offset);
+        const uint64_t ni = static_cast<uint64_t>(gi >= p.noise_split ? gi + p.noise_shift : gi);
+        const uint4 u0 = rng(ni >> 2, h.offset);
+        const uint4 u1 = rng((ni >> 2) + 1, h.offset);
         const float2 z0 = box_muller(u0.x, u0.y), z1 = box_muller(u0.z, u0.w);
         const float2 z2 = box_muller(u1.x, u1.y), z3 = box_muller(u1.z, u1.w);
         g[0] += z0.x * h.noise_std; g[1] += z0.y * h.noise_std; g[2] += z1.x * h.noise_std; g[3] += z1.y * h.noise_std;

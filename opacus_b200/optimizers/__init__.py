@@ -31,8 +31,12 @@ _PLAIN = {
 }
 
 
-def get_optimizer_class(clipping: str, distributed: bool, grad_sample_mode: str = None):
+def get_optimizer_class(clipping: str, distributed: bool, grad_sample_mode: str = None, engine=None):
     key = (clipping, bool(distributed))
+    if grad_sample_mode == "ghost_tp" and engine is not None and clipping == "flat":
+        # tensor parallel x sharded data parallel: the engine's step kernel draws the noise (one Philox range per
+        # tensor-parallel rank for the shards), so the optimizer is the one that hands the step to the engine
+        return FSDPOptimizerFastGradientClipping
     if grad_sample_mode == "ghost":
         if key in _GHOST:
             return _GHOST[key]

@@ -34,8 +34,15 @@ _SLICE_QUANTUM = 1024
 
 
 class ShardedDataParallel(nn.Module):
+    """``process_group`` is the data-parallel group (ranks that hold the same parameters and see different
+    samples).  ``tp_group`` is the tensor-parallel group this rank also belongs to, when the module was sharded
+    by :mod:`opacus_b200.parallel.tensor_parallel` (2-D layout: every tensor-parallel rank runs this engine over
+    its own data-parallel group).  Parameters marked ``tp_sharded`` then draw their noise from a Philox range of
+    their tensor-parallel rank, all others from a range common to the tensor-parallel group under a seed the
+    group agrees on, so that shards get independent noise and replicas stay bit-identical."""
+
     def __init__(self, module: nn.Module, *, param_dtype: torch.dtype = torch.bfloat16, process_group=None,
-                 **unused):
+                 tp_group=None, **unused):
         super().__init__()
         first = next(module.parameters())
         if not first.is_cuda:
@@ -56,18 +63,29 @@ class ShardedDataParallel(nn.Module):
         # ---- flat layout over the distinct trainable parameters
         self._params: List[nn.Parameter] = []
         self._offsets: Dict[nn.Parameter, int] = {}
-        total = 0
+        self.tp_group = tp_group
+        self.tp_rank, self.tp_world = symm.world_info(tp_group) if tp_group is not None else (0, 1)
+        distinct = []
         for p in module.parameters():
-            if not p.requires_grad or p in self._offsets:
-                continue
-            if getattr(p, "tp_sharded", False):
-                # Ranks of a tensor-parallel group run this engine with the same seed and the same flat layout, so
-                # two shards of one weight would receive the SAME noise values: correlated noise is not the
-                # Gaussian mechanism.  Independent streams per tensor-parallel rank are not implemented.
-                raise NotImplementedError("ShardedDataParallel over tensor-parallel shards (TP x FSDP) is not supported")
+            if p.requires_grad and not any(p is q for q in distinct):
+                distinct.append(p)
+        shards = [p for p in distinct if getattr(p, "tp_sharded", False)]
+        if shards and tp_group is None:
+            # Ranks of a tensor-parallel group run this engine with the same flat layout; under one seed two shards
+            # of one weight would receive the SAME noise values, and correlated noise is not the Gaussian mechanism.
+            raise ValueError("the module holds tensor-parallel shards: pass tp_group= so that they draw independent noise")
+        total = 0
+        self.noise_split = None
+        # replicated parameters first, shards behind them: one split point separates the two noise ranges
+        for p in [q for q in distinct if not getattr(q, "tp_sharded", False)] + shards:
+            if shards and p is shards[0]:
+                self.noise_split = total
             self._offsets[p] = total
             self._params.append(p)
             total += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        # sums of parameters that saw only this tensor-parallel rank's samples are completed before the step
+        self._tp_partial = [p for p in distinct if getattr(p, "sp_local", False)] if tp_group is not None else []
+        self._tp_seed = None
         self.slice_len = (math.ceil(total / self.world) + _SLICE_QUANTUM - 1) // _SLICE_QUANTUM * _SLICE_QUANTUM
         self.total = self.slice_len * self.world
         self.slice_begin = self.rank * self.slice_len
@@ -82,7 +100,8 @@ class ShardedDataParallel(nn.Module):
             o = self._offsets[p]
             full[o: o + p.numel()].copy_(p.data.reshape(-1).float())
         if self.world > 1:
-            dist.broadcast(full, 0, group=process_group)
+            dist.broadcast(full, dist.get_global_rank(process_group, 0) if process_group is not None else 0,
+                           group=process_group)
         self.master = full[self.slice_begin: self.slice_begin + self.slice_len].clone()
         self._flat_param.tensor.copy_(full.to(param_dtype))
         del full
@@ -200,13 +219,24 @@ class ShardedDataParallel(nn.Module):
         denom = float(dpopt._grad_denominator()) * (self.world if dpopt.loss_reduction == "mean" else 1)
         if dpopt.step_hook:
             dpopt.step_hook(dpopt)
-        seed, offset = _cuda._rng_state(dpopt.generator, dev, self.total)
+        seed, offset = _cuda._rng_state(dpopt.generator, dev, self.total * self.tp_world)
+        noise_shift = 0
+        if self.tp_group is not None:
+            for p in self._tp_partial:
+                dist.all_reduce(p._dp_grad_out, op=dist.ReduceOp.SUM, group=self.tp_group)
+            if self._tp_seed is None:      # the group adopts its first rank's generator state, once
+                state = torch.tensor([seed, offset], dtype=torch.int64, device=dev)
+                dist.broadcast(state, dist.get_global_rank(self.tp_group, 0), group=self.tp_group)
+                self._tp_seed = (int(state[0]), int(state[1]) - offset)
+            seed, offset = self._tp_seed[0], offset + self._tp_seed[1]
+            noise_shift = self.tp_rank * self.total if self.noise_split is not None else 0
         C = _cuda.load()
         C.sharded_dp_step(self._flat_grad.ptrs, self._flat_param.ptrs, self._flags.ptrs, self.master, self.state0,
                           self.state1, self.slice_begin, self.slice_len, self.rank,
                           self.param_dtype == torch.bfloat16, self._epoch, kcode, nesterov, first_step,
                           h["lr"], h["momentum"], h["dampening"], h["weight_decay"], h["beta1"], h["beta2"], h["eps"],
-                          h["bias_c1"], h["bias_c2_sqrt"], float(dpopt._noise_std()), 1.0 / denom, seed, offset)
+                          h["bias_c1"], h["bias_c2_sqrt"], float(dpopt._noise_std()), 1.0 / denom, seed, offset,
+                          self.noise_split if noise_shift else 0, noise_shift)
         dpopt._is_last_step_skipped = False
         self.mark_grads_fresh()
         return None

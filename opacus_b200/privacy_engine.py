@@ -91,7 +91,9 @@ class PrivacyEngine:
         if isinstance(optimizer, DPOptimizer):
             optimizer = optimizer.original_optimizer
         generator = self.secure_rng if self.secure_mode else noise_generator
-        cls = get_optimizer_class(clipping=clipping, distributed=distributed, grad_sample_mode=grad_sample_mode)
+        cls = get_optimizer_class(clipping=clipping, distributed=distributed, grad_sample_mode=grad_sample_mode,
+                                  **({"engine": kwargs["engine"]} if grad_sample_mode == "ghost_tp" and "engine" in kwargs
+                                     else {}))
         return cls(optimizer=optimizer, noise_multiplier=noise_multiplier, max_grad_norm=max_grad_norm,
                    expected_batch_size=expected_batch_size, loss_reduction=loss_reduction, generator=generator,
                    secure_mode=self.secure_mode, **kwargs)
@@ -138,6 +140,10 @@ class PrivacyEngine:
                 extra["single_pass"] = True if single_pass is None else single_pass
             elif single_pass is not None:
                 extra["single_pass"] = single_pass
+            tp_group = getattr(module, "tp_group", None)
+            if grad_sample_mode == "ghost_tp" and tp_group is not None:     # 2-d: the sharded engine knows the group
+                extra["process_group"] = tp_group
+                extra.setdefault("single_pass", True)
         elif grad_sample_mode in ("hooks", "functorch") and skip_param_grads:
             extra["skip_param_grads"] = True
         return prepare_module(module, grad_sample_mode=grad_sample_mode, batch_first=batch_first,
@@ -204,7 +210,8 @@ class PrivacyEngine:
         sample_rate = 1 / len(data_loader)
         expected_batch_size = int(len(data_loader.dataset) * sample_rate)
         if distributed:
-            expected_batch_size /= torch.distributed.get_world_size()
+            # workers that see different samples: all ranks, or one per tensor-parallel group in a 2-d layout
+            expected_batch_size /= torch.distributed.get_world_size() // getattr(engine, "tp_world", 1)
 
         opt_kwargs = dict(kwargs)
         if engine is not None and clipping == "flat":

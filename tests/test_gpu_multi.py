@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(script, nproc, timeout=420):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _launch(script, nproc, timeout=420, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
            "--nproc-per-node", str(nproc), os.path.join(HERE, script)]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
@@ -29,3 +29,12 @@ def test_sharded_engine_multi_gpu():
 def test_tensor_parallel_peer_collectives_multi_gpu():
     out = _launch("dist_tp_check.py", min(torch.cuda.device_count(), 8))
     assert "tp check ok" in out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_times_sharded_data_parallel_multi_gpu():
+    """2-way tensor parallel x (GPUs / 2)-way sharded data parallel; with 2 GPUs the data-parallel groups are single ranks."""
+    n = torch.cuda.device_count()
+    nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
+    out = _launch("dist_tp_fsdp_check.py", nproc, TP_SIZE="2")
+    assert "tp x fsdp check ok" in out

@@ -233,3 +233,33 @@ def test_bounded_wait_runs_out_and_is_reported():
     torch.cuda.synchronize()
     assert torch.equal(red_total, part)
     _cuda.check_status()
+
+
+def test_step_kernel_noise_ranges_for_tensor_parallel_shards():
+    """Elements at or beyond ``noise_split`` draw from the Philox range shifted by ``noise_shift``: below the split two
+    tensor-parallel ranks see the same noise, beyond it independent noise -- the draw of index ``i + shift``."""
+    from opacus_b200.ops import _cuda
+
+    C = _cuda.load()
+    dev = torch.device("cuda")
+    n, split, shift = 8192, 2048, 4096
+
+    def noise(length, split_at, shift_by):
+        grad = torch.zeros(length, device=dev)
+        param = torch.zeros(length, device=dev, dtype=torch.bfloat16)
+        flags = torch.zeros(64, device=dev, dtype=torch.int32)
+        master = torch.zeros(length, device=dev)
+        # plain SGD, lr 1, no momentum: master = -(0 + noise) * inv_scale
+        C.sharded_dp_step([grad.data_ptr()], [param.data_ptr()], [flags.data_ptr()], master, None, None, 0, length, 0,
+                          True, 1, 0, False, False, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 1.0, 1.0, 1.0, 1234, 0,
+                          split_at, shift_by)
+        torch.cuda.synchronize()
+        return -master
+
+    base = noise(n, 0, 0)
+    moved = noise(n // 2, split, shift)
+    assert torch.equal(moved[:split], base[:split])
+    assert torch.equal(moved[split:], base[split + shift: n // 2 + shift])
+    assert not torch.equal(moved[split:], base[split: n // 2])
+    assert 0.9 < float(base.std()) < 1.1
+    _cuda.check_status()
