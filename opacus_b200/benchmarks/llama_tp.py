@@ -3,7 +3,10 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
         -m opacus_b200.benchmarks.llama_tp [--layers 32] [--seq 2048] [--batch 64] [--micro 8] [--steps 3]
 
-All ranks form one tensor-parallel group and see the same batch.  Linear layers are
+By default all ranks form one tensor-parallel group and see the same batch; ``--tp K`` (K dividing the number of
+ranks) makes groups of K consecutive ranks and runs the ``ranks / K`` groups as sharded data parallelism over
+``ShardedDataParallel`` (2-d layout: each group sees its own share of the logical batch; optimizer state and fp32
+master weights are sharded over the ranks with the same position in their groups).  Linear layers are
 column / row parallel, the output layer is split over the vocabulary and feeds
 ``VocabParallelCrossEntropy``; embedding and norm weights are replicated and
 trained (identical noise on every rank).  ``--sp`` shards the activations between the
@@ -33,6 +36,7 @@ def main():
     ap.add_argument("--sp", action="store_true",
                     help="sequence parallel: activations sharded over samples between the blocks, fused collective GEMMs")
     ap.add_argument("--no-fused", action="store_true", help="with --sp: NCCL + cuBLAS instead of the fused GEMMs")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel group size (default: all ranks)")
     ap.add_argument("--no-peer-norm", action="store_true", help="reduce the norms with NCCL instead of the peer kernel")
     args = ap.parse_args()
     import warnings
@@ -61,16 +65,36 @@ def main():
     with torch.device(dev):
         model = Llama(cfg)                       # same weights on every rank, then sharded in place
     torch.set_default_dtype(torch.float32)
-    parallelize_llama(model, sequence_parallel=args.sp, fused=not args.no_fused)      # explicit: the flag decides
+    tp = args.tp or world
+    assert world % tp == 0, "--tp must divide the number of ranks"
+    dp = world // tp
+    tp_group = dp_group = None
+    if dp > 1:
+        for k in range(dp):
+            grp = dist.new_group(list(range(k * tp, (k + 1) * tp)))
+            tp_group = grp if rank // tp == k else tp_group
+        for j in range(tp):
+            grp = dist.new_group(list(range(j, world, tp)))
+            dp_group = grp if rank % tp == j else dp_group
+    parallelize_llama(model, tp_group, sequence_parallel=args.sp, fused=not args.no_fused)   # explicit: the flag decides
     torch.cuda.empty_cache()
-    gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=1.0, single_pass=True)
+    if dp > 1:
+        from opacus_b200.optimizers import FSDPOptimizerFastGradientClipping
+        from opacus_b200.parallel.sharded import ShardedDataParallel
+
+        engine = ShardedDataParallel(model, process_group=dp_group, tp_group=tp_group)
+        gsm = GradSampleModuleFastGradientClippingTP(engine, max_grad_norm=1.0, single_pass=True, process_group=tp_group)
+        opt = FSDPOptimizerFastGradientClipping(torch.optim.AdamW(model.parameters(), lr=1e-4), noise_multiplier=1.0,
+                                                max_grad_norm=1.0, expected_batch_size=args.batch // dp, engine=engine)
+    else:
+        gsm = GradSampleModuleFastGradientClippingTP(model, max_grad_norm=1.0, single_pass=True)
+        opt = TensorParallelDPOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-4), noise_multiplier=1.0,
+                                        max_grad_norm=1.0, expected_batch_size=args.batch)
     gsm.use_peer_memory = not args.no_peer_norm
-    opt = TensorParallelDPOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-4), noise_multiplier=1.0,
-                                    max_grad_norm=1.0, expected_batch_size=args.batch)
-    crit = DPLossFastGradientClipping(gsm, opt, VocabParallelCrossEntropy(), "mean")
-    n_micro = args.batch // args.micro
+    crit = DPLossFastGradientClipping(gsm, opt, VocabParallelCrossEntropy(tp_group), "mean")
+    n_micro = args.batch // (args.micro * dp)
     T = args.seq
-    g = torch.Generator().manual_seed(1)
+    g = torch.Generator().manual_seed(1 + rank // tp)       # one stream of samples per tensor-parallel group
     host = [torch.randint(0, cfg.vocab_size, (args.micro, T + 1), generator=g).pin_memory() for _ in range(n_micro)]
     losses = torch.zeros(1, device=dev)
 
@@ -102,7 +126,7 @@ def main():
     if rank == 0:
         print(json.dumps({"metric": "dp_llama8b_tp_tokens_per_s", "value": args.batch * T / (ms / 1e3), "n_gpus": world,
                           "ms_per_logical_step": ms, "config": {"layers": args.layers, "seq": T, "global_batch": args.batch,
-                                                                "micro_batch": args.micro, "parallelism": f"tp{world}" + ("+sp" if args.sp else ""),
+                                                                "micro_batch": args.micro, "parallelism": f"tp{tp}" + ("+sp" if args.sp else "") + (f" x sharded dp{dp}" if dp > 1 else ""),
                                                                 "fused_collective_gemms": bool(args.sp and not args.no_fused)},
                           "peer_norm_kernel": not args.no_peer_norm, "loss": last, "dtype": "bf16",
                           "max_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}))

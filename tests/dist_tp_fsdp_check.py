@@ -31,7 +31,7 @@ def make_groups(rank, world, tp):
     return tp_group, dp_group, dp
 
 
-def build(dev, tp_group, dp_group, *, two_d, sigma, clip, lr, batch):
+def build(dev, tp_group, dp_group, *, two_d, sigma, clip, lr, batch, sp=False):
     from opacus_b200.grad_sample import GradSampleModuleFastGradientClippingTP
     from opacus_b200.models import Llama, LlamaConfig
     from opacus_b200.optimizers import FSDPOptimizerFastGradientClipping
@@ -44,7 +44,7 @@ def build(dev, tp_group, dp_group, *, two_d, sigma, clip, lr, batch):
     cfg = LlamaConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=8, n_kv_heads=8, ffn_dim=512,
                       tie_embeddings=False)
     model = Llama(cfg).to(dev).bfloat16()
-    parallelize_llama(model, tp_group)
+    parallelize_llama(model, tp_group, sequence_parallel=sp)
     if two_d:
         wrapped = ShardedDataParallel(model, process_group=dp_group, tp_group=tp_group)
         gsm = GradSampleModuleFastGradientClippingTP(wrapped, max_grad_norm=clip, single_pass=True,
@@ -79,23 +79,25 @@ def probes(model):
             "embedding (replicated)": model.embed_tokens.weight.detach().float().clone()}
 
 
-def check_matches_tensor_parallel_alone(rank, world, tp, tp_group, dp_group, dp):
+def check_matches_tensor_parallel_alone(rank, world, tp, tp_group, dp_group, dp, sp):
     """Noise off: the 2-D job, whose data-parallel ranks each see a share of the batch, ends where one
-    tensor-parallel group that sees the whole batch ends."""
+    tensor-parallel group that sees the whole batch ends.  ``sp``: activations sharded over samples between the
+    blocks, so the sums of the norm and embedding weights are completed over the tensor-parallel group first."""
     dev = torch.device("cuda", torch.cuda.current_device())
     per_rank, T = 4, 64
     g = torch.Generator().manual_seed(3)
     ids = torch.randint(0, 1024, (per_rank * dp, T + 1), generator=g).to(dev)
     model, gsm, opt, crit = build(dev, tp_group, dp_group, two_d=False, sigma=0.0, clip=1.0, lr=0.1,
-                                  batch=per_rank * dp)
+                                  batch=per_rank * dp, sp=sp)
     train(gsm, opt, crit, ids, 2)
     want = probes(model)
     k = rank // tp
-    model, gsm, opt, crit = build(dev, tp_group, dp_group, two_d=True, sigma=0.0, clip=1.0, lr=0.1, batch=per_rank)
+    model, gsm, opt, crit = build(dev, tp_group, dp_group, two_d=True, sigma=0.0, clip=1.0, lr=0.1, batch=per_rank,
+                                  sp=sp)
     train(gsm, opt, crit, ids[k * per_rank:(k + 1) * per_rank], 2)
     for name, got in probes(model).items():
         ref = want[name]
-        assert (got - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3, (rank, name, (got - ref).abs().max().item())
+        assert (got - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3, (rank, sp, name, (got - ref).abs().max().item())
 
 
 def check_noise_layout(rank, world, tp, tp_group, dp_group, dp):
@@ -135,7 +137,8 @@ def main():
     tp = int(os.environ.get("TP_SIZE", "2"))
     assert world % tp == 0 and tp >= 2
     tp_group, dp_group, dp = make_groups(rank, world, tp)
-    check_matches_tensor_parallel_alone(rank, world, tp, tp_group, dp_group, dp)
+    for sp in (False, True):
+        check_matches_tensor_parallel_alone(rank, world, tp, tp_group, dp_group, dp, sp)
     check_noise_layout(rank, world, tp, tp_group, dp_group, dp)
     dist.barrier()
     if rank == 0:
