@@ -102,12 +102,14 @@ class DPDataLoader(DataLoader):
 
     def __init__(self, dataset: Dataset, *, sample_rate: float, collate_fn=None, drop_last: bool = False,
                  generator=None, distributed: bool = False, batch_first: bool = True,
-                 rand_on_empty: bool = False, **kwargs):
+                 rand_on_empty: bool = False, num_replicas: Optional[int] = None, rank: Optional[int] = None,
+                 **kwargs):
         self.sample_rate = sample_rate
         self.distributed = distributed
         if distributed:
             sampler = DistributedUniformWithReplacementSampler(
-                total_size=len(dataset), sample_rate=sample_rate, generator=generator)
+                total_size=len(dataset), sample_rate=sample_rate, generator=generator, num_replicas=num_replicas,
+                rank=rank)
         else:
             sampler = UniformWithReplacementSampler(
                 num_samples=len(dataset), sample_rate=sample_rate, generator=generator)
@@ -130,9 +132,11 @@ class DPDataLoader(DataLoader):
 
     @classmethod
     def from_data_loader(cls, data_loader: DataLoader, *, distributed: bool = False, generator=None,
-                         batch_first: bool = True, rand_on_empty: bool = False):
+                         batch_first: bool = True, rand_on_empty: bool = False,
+                         num_replicas: Optional[int] = None, rank: Optional[int] = None):
         """Same dataset and worker settings; the batch size only enters through
-        ``sample_rate = 1 / len(data_loader)``."""
+        ``sample_rate = 1 / len(data_loader)``.  ``num_replicas`` / ``rank``: see
+        ``DistributedUniformWithReplacementSampler``."""
         if isinstance(data_loader.dataset, IterableDataset):
             raise ValueError("Uniform sampling is not supported for IterableDataset")
         return cls(
@@ -144,6 +148,8 @@ class DPDataLoader(DataLoader):
             distributed=distributed,
             batch_first=batch_first,
             rand_on_empty=rand_on_empty,
+            num_replicas=num_replicas,
+            rank=rank,
             **_carry(data_loader),
         )
 

@@ -99,7 +99,8 @@ class PrivacyEngine:
                    secure_mode=self.secure_mode, **kwargs)
 
     def _prepare_data_loader(self, data_loader: DataLoader, *, poisson_sampling: bool, distributed: bool,
-                             batch_first: bool = True, rand_on_empty: bool = False) -> DataLoader:
+                             batch_first: bool = True, rand_on_empty: bool = False,
+                             replica: Optional[tuple] = None) -> DataLoader:
         if self.dataset is None:
             self.dataset = data_loader.dataset
         elif self.dataset != data_loader.dataset:
@@ -110,11 +111,33 @@ class PrivacyEngine:
                 "logical dataset"
             )
         if poisson_sampling:
+            if replica is not None:         # 2-d layout: (data-parallel groups, this rank's group, shared generator)
+                return DPDataLoader.from_data_loader(data_loader, generator=replica[2], distributed=True,
+                                                     batch_first=batch_first, rand_on_empty=rand_on_empty,
+                                                     num_replicas=replica[0], rank=replica[1])
             return DPDataLoader.from_data_loader(data_loader, generator=self.secure_rng, distributed=distributed,
                                                  batch_first=batch_first, rand_on_empty=rand_on_empty)
         if self.secure_mode:
             return switch_generator(data_loader=data_loader, generator=self.secure_rng)
         return data_loader
+
+    def _tensor_parallel_replica(self, engine):
+        """Sharded data parallelism over tensor-parallel groups: the ranks of one tensor-parallel group must draw
+        the same Poisson sample, different groups disjoint ones.  Returns ``(groups, this rank's group, generator)``
+        with a generator state common to the tensor-parallel group (rank 0 of the job draws a base seed and
+        broadcasts it; collective), or None for every other layout."""
+        if engine is None or getattr(engine, "tp_world", 1) <= 1:
+            return None
+        if self.secure_mode:
+            raise NotImplementedError("secure_mode with tensor-parallel groups: the sampling generator must be shared")
+        import torch.distributed as dist
+
+        base = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64)
+        dev = next(engine.parameters()).device
+        base = base.to(dev)
+        dist.broadcast(base, 0)
+        groups, mine = engine.world, engine.rank
+        return groups, mine, torch.Generator().manual_seed((int(base.item()) + 7919 * mine) % (2 ** 63 - 1))
 
     def _prepare_model(self, module: nn.Module, *, batch_first: bool = True,
                        max_grad_norm: Union[float, List[float]] = 1.0, loss_reduction: str = "mean",
@@ -206,7 +229,8 @@ class PrivacyEngine:
 
         data_loader = self._prepare_data_loader(data_loader, distributed=distributed,
                                                 poisson_sampling=poisson_sampling, batch_first=batch_first,
-                                                rand_on_empty=rand_on_empty)
+                                                rand_on_empty=rand_on_empty,
+                                                replica=self._tensor_parallel_replica(engine))
         sample_rate = 1 / len(data_loader)
         expected_batch_size = int(len(data_loader.dataset) * sample_rate)
         if distributed:

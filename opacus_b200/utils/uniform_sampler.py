@@ -45,14 +45,20 @@ class DistributedUniformWithReplacementSampler(Sampler):
     """
 
     def __init__(self, *, total_size: int, sample_rate: float, shuffle: bool = True, shuffle_seed: int = 0,
-                 steps: Optional[int] = None, generator=None):
+                 steps: Optional[int] = None, generator=None, num_replicas: Optional[int] = None,
+                 rank: Optional[int] = None):
+        """``num_replicas`` / ``rank`` default to the whole job; a 2-d layout passes the number of data-parallel
+        groups and this rank's group index (with one ``generator`` state per group), so that the ranks of a
+        tensor-parallel group draw the same samples."""
         if total_size <= 0:
             raise ValueError(f"total_size should be a positive integer value, but got total_size={total_size}")
         self.total_size = total_size
         self.sample_rate = sample_rate
         self.generator = generator
-        self.num_replicas = torch.distributed.get_world_size()
-        self.rank = torch.distributed.get_rank()
+        self.num_replicas = torch.distributed.get_world_size() if num_replicas is None else int(num_replicas)
+        self.rank = torch.distributed.get_rank() if rank is None else int(rank)
+        if not 0 <= self.rank < self.num_replicas:
+            raise ValueError(f"rank {self.rank} outside [0, {self.num_replicas})")
         self.epoch = 0
         self.shuffle = shuffle
         self.shuffle_seed = shuffle_seed

@@ -96,3 +96,20 @@ def test_fused_cross_entropy_cpu_fallback():
         got = FusedCrossEntropyLoss(reduction=red)(logits, target)
         want = torch.nn.functional.cross_entropy(logits, target, reduction=red)
         torch.testing.assert_close(got, want)
+
+
+def test_distributed_sampler_with_explicit_replicas():
+    """Tensor-parallel ranks of one group pass the same (replicas, rank, generator state) and draw the same batches;
+    different groups draw from disjoint slices of the data."""
+    import torch
+    from opacus_b200.utils.uniform_sampler import DistributedUniformWithReplacementSampler as Sampler
+
+    def draw(rank, seed):
+        s = Sampler(total_size=200, sample_rate=0.1, num_replicas=2, rank=rank, generator=torch.Generator().manual_seed(seed))
+        return [list(map(int, b)) for b in s]
+
+    assert draw(0, 5) == draw(0, 5)
+    a, b = draw(0, 5), draw(1, 6)
+    assert not ({i for x in a for i in x} & {i for x in b for i in x})
+    with pytest.raises(ValueError):
+        Sampler(total_size=10, sample_rate=0.5, num_replicas=2, rank=2)
