@@ -269,7 +269,7 @@ class ShardedDataParallel(nn.Module):
         return None
 
     # Measured on the Llama-1B step (1 GPU): see the notes on stream overlap in the design document of this package.
-    overlap_step = True
+    overlap_step = False
     step_pieces = 8
 
     def _ready_pieces(self, had_fresh: bool):
