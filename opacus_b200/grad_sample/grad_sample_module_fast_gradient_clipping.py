@@ -431,36 +431,35 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                 lanes[0].wait_stream(st)
 
     def _write_site(self, site, coef):
-        if True:
-            mtype = self._get_module_type(site.module)
-            c = self._site_coef(site, coef)
-            if site.kept_grad_samples is not None:
-                grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]]) for p, gs in site.kept_grad_samples.items()}
-            elif mtype in self.WGRAD_SAMPLERS and not self.force_functorch:
-                grads = self.WGRAD_SAMPLERS[mtype](site.module, site.inputs, site.backprops, c, site.g_scale)
+        mtype = self._get_module_type(site.module)
+        c = self._site_coef(site, coef)
+        if site.kept_grad_samples is not None:
+            grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]]) for p, gs in site.kept_grad_samples.items()}
+        elif mtype in self.WGRAD_SAMPLERS and not self.force_functorch:
+            grads = self.WGRAD_SAMPLERS[mtype](site.module, site.inputs, site.backprops, c, site.g_scale)
+        else:
+            sampler = self.GRAD_SAMPLERS[mtype] if self._has_rule(site.module) else ft_compute_per_sample_gradient
+            scaled = site.backprops * site.g_scale if site.g_scale != 1.0 else site.backprops
+            grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]])
+                     for p, gs in sampler(site.module, site.inputs, scaled).items()}
+        for p, g in grads.items():
+            if not p.requires_grad:
+                continue
+            dst = getattr(p, "_dp_grad_out", None)
+            if dst is not None:
+                # engine-owned gradient storage (fp32, independent of the parameter dtype)
+                if g.data_ptr() != dst.data_ptr():
+                    if getattr(p, "_dp_grad_fresh", True):
+                        dst.copy_(g.reshape(p.shape))
+                        p._dp_grad_fresh = False
+                    else:
+                        dst.add_(g.reshape(p.shape))
+                continue
+            g = g.reshape(p.shape).to(p.dtype)
+            if p.grad is None:
+                p.grad = g if g._base is None else g.clone()
             else:
-                sampler = self.GRAD_SAMPLERS[mtype] if self._has_rule(site.module) else ft_compute_per_sample_gradient
-                scaled = site.backprops * site.g_scale if site.g_scale != 1.0 else site.backprops
-                grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]])
-                         for p, gs in sampler(site.module, site.inputs, scaled).items()}
-            for p, g in grads.items():
-                if not p.requires_grad:
-                    continue
-                dst = getattr(p, "_dp_grad_out", None)
-                if dst is not None:
-                    # engine-owned gradient storage (fp32, independent of the parameter dtype)
-                    if g.data_ptr() != dst.data_ptr():
-                        if getattr(p, "_dp_grad_fresh", True):
-                            dst.copy_(g.reshape(p.shape))
-                            p._dp_grad_fresh = False
-                        else:
-                            dst.add_(g.reshape(p.shape))
-                    continue
-                g = g.reshape(p.shape).to(p.dtype)
-                if p.grad is None:
-                    p.grad = g if g._base is None else g.clone()
-                else:
-                    p.grad.add_(g)
+                p.grad.add_(g)
 
     # ------------------------------------------------------- two-pass protocol
     def capture_activations_hook(self, module: nn.Module, forward_input: List[torch.Tensor],
