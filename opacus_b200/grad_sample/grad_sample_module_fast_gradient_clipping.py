@@ -408,22 +408,14 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                 st.wait_stream(main)
             lanes = [main] + sides
         lane_of = {}
-        for order, site in enumerate(self._sites):
+        for site in self._sites:
             if lanes is not None:
-                owned = [p for _, p in trainable_parameters(site.module)]
-                ps = [id(p) for p in owned]
+                ps = [id(p) for _, p in trainable_parameters(site.module)]
                 lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % len(lanes))
                 for i in ps:
                     lane_of[i] = lane
                 with torch.cuda.stream(lanes[lane]):
                     self._write_site(site, coef)
-                    if any(getattr(p, "_dp_grad_out", None) is not None for p in owned):
-                        # an engine that owns the gradient storage may start its step on the parameters written
-                        # so far while later sums are still running: (stream, position, event) of the last write
-                        done = torch.cuda.Event()
-                        done.record(lanes[lane])
-                        for p in owned:
-                            p._dp_ready = (lane, order, done)
             else:
                 self._write_site(site, coef)
         if lanes is not None:

@@ -120,7 +120,6 @@ class ShardedDataParallel(nn.Module):
         self.state1: Optional[torch.Tensor] = None
         self._epoch = 0
         self._steps = 0
-        self._step_stream = None
         if self.world > 1:
             dist.barrier(group=process_group)
 
@@ -132,7 +131,6 @@ class ShardedDataParallel(nn.Module):
         """The next clipped-gradient write overwrites instead of accumulating."""
         for p in self._params:
             p._dp_grad_fresh = True
-            p.__dict__.pop("_dp_ready", None)
 
     def flat_grad(self) -> torch.Tensor:
         return self._flat_grad.tensor
@@ -175,7 +173,6 @@ class ShardedDataParallel(nn.Module):
         if closure is not None:
             with torch.enable_grad():
                 closure()
-        had_fresh = any(p._dp_grad_fresh for p in self._params)      # such gradients are zero-filled here, on this stream
         self.finish_grads()
         if dpopt._check_skip_next_step():
             dpopt._is_last_step_skipped = True
@@ -234,67 +231,12 @@ class ShardedDataParallel(nn.Module):
             seed, offset = self._tp_seed[0], offset + self._tp_seed[1]
             noise_shift = self.tp_rank * self.total if self.noise_split is not None else 0
         C = _cuda.load()
-
-        def launch(begin, length):
-            """The step over ``[begin, begin + length)`` of this rank's slice (one launch, one flag epoch)."""
-            lo = begin - self.slice_begin
-            cut = lambda t: None if t is None else t[lo: lo + length]
-            C.sharded_dp_step(self._flat_grad.ptrs, self._flat_param.ptrs, self._flags.ptrs, cut(self.master),
-                              cut(self.state0), cut(self.state1), begin, length, self.rank,
-                              self.param_dtype == torch.bfloat16, self._epoch, kcode, nesterov, first_step,
-                              h["lr"], h["momentum"], h["dampening"], h["weight_decay"], h["beta1"], h["beta2"],
-                              h["eps"], h["bias_c1"], h["bias_c2_sqrt"], float(dpopt._noise_std()), 1.0 / denom, seed,
-                              offset, self.noise_split if noise_shift else 0, noise_shift)
-
-        pieces = self._ready_pieces(had_fresh) if self.overlap_step else None
-        if pieces is None:
-            launch(self.slice_begin, self.slice_len)
-        else:
-            # Pieces of the flat space whose clipped sums are complete are stepped on a side stream while the
-            # remaining weight-gradient GEMMs (tensor-core bound) still run: the step is memory bound.
-            main = torch.cuda.current_stream(dev)
-            side = self._step_stream
-            if side is None:
-                side = self._step_stream = torch.cuda.Stream(device=dev)
-            for k, (begin, length, events) in enumerate(pieces):
-                for ev in events:
-                    side.wait_event(ev)
-                with torch.cuda.stream(side):
-                    if k:
-                        self._epoch += 1
-                    launch(begin, length)
-            main.wait_stream(side)
+        C.sharded_dp_step(self._flat_grad.ptrs, self._flat_param.ptrs, self._flags.ptrs, self.master, self.state0,
+                          self.state1, self.slice_begin, self.slice_len, self.rank,
+                          self.param_dtype == torch.bfloat16, self._epoch, kcode, nesterov, first_step,
+                          h["lr"], h["momentum"], h["dampening"], h["weight_decay"], h["beta1"], h["beta2"], h["eps"],
+                          h["bias_c1"], h["bias_c2_sqrt"], float(dpopt._noise_std()), 1.0 / denom, seed, offset,
+                          self.noise_split if noise_shift else 0, noise_shift)
         dpopt._is_last_step_skipped = False
         self.mark_grads_fresh()
         return None
-
-    # Measured on the Llama-1B step (1 GPU): see the notes on stream overlap in the design document of this package.
-    overlap_step = False
-    step_pieces = 8
-
-    def _ready_pieces(self, had_fresh: bool):
-        """``[(begin, length, events)]`` in the order in which the ghost-clipping pass completes them, or None when
-        the step has to be one launch: several ranks (every launch is a meeting of all ranks), a tensor-parallel
-        group (sums are exchanged first), gradients that did not come from the single-pass controller."""
-        if self.world != 1 or self.tp_group is not None or had_fresh or self.step_pieces < 2:
-            return None
-        marks = [getattr(p, "_dp_ready", None) for p in self._params]
-        if any(m is None for m in marks):
-            return None
-        quantum = 1024
-        size = (self.total // self.step_pieces + quantum - 1) // quantum * quantum
-        if size <= 0:
-            return None
-        bounds = [(b, min(size, self.total - b)) for b in range(0, self.total, size)]
-        latest = [dict() for _ in bounds]              # per piece: stream -> (position, event) of its last write
-        for p, (lane, order, event) in zip(self._params, marks):
-            o = self._offsets[p]
-            for k in range(o // size, min((o + p.numel() - 1) // size, len(bounds) - 1) + 1):
-                if lane not in latest[k] or latest[k][lane][0] < order:
-                    latest[k][lane] = (order, event)
-        keyed = []
-        for (begin, length), per_lane in zip(bounds, latest):
-            when = max((v[0] for v in per_lane.values()), default=-1)
-            keyed.append((when, begin, length, [v[1] for v in per_lane.values()]))
-        keyed.sort(key=lambda t: (t[0], t[1]))
-        return [(b, n, ev) for _, b, n, ev in keyed]

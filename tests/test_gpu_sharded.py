@@ -264,25 +264,3 @@ def test_step_kernel_noise_ranges_for_tensor_parallel_shards():
     assert 0.9 < float(base.std()) < 1.1
     _cuda.check_status()
 
-
-def test_step_in_pieces_beside_the_clipped_sums_is_bit_identical(pg):
-    """With one rank the engine steps the pieces of the flat space whose clipped sums are complete on a side
-    stream while later sums still run; noise is indexed by flat position, so the result has the same bits."""
-    from opacus_b200.ops import _cuda
-    from opacus_b200.parallel.sharded import ShardedDataParallel
-
-    ids = torch.randint(0, 512, (4, 65), device="cuda")
-    results = []
-    for overlap in (False, True):
-        torch.cuda.manual_seed(11)
-        eng = ShardedDataParallel(_model())
-        eng.overlap_step = overlap
-        m, opt, crit, _ = _private(eng, "ghost_fsdp", 1.0, torch.optim.AdamW)
-        for _ in range(3):
-            _step(m, opt, crit, ids)
-        torch.cuda.synchronize()
-        _cuda.check_status()
-        assert (eng._step_stream is not None) == overlap
-        results.append((eng.master.clone(), eng._flat_param.tensor.clone(), eng.state0.clone(), eng.state1.clone()))
-    for a, b in zip(*results):
-        assert torch.equal(a, b)
