@@ -44,6 +44,11 @@ def parse():
                     help="ours: sharded data-parallel engine (default) or, on one GPU, the plain ghost path")
     ap.add_argument("--ce", default="fused", choices=["fused", "torch"],
                     help="ours: FusedCrossEntropyLoss on bf16 logits, or nn.CrossEntropyLoss on logits.float()")
+    ap.add_argument("--untied", action="store_true",
+                    help="ours: control run with untied embeddings (the reference arm's parameter set); not the default")
+    ap.add_argument("--plain-model", action="store_true",
+                    help="ours: control run on the stock-PyTorch model definition the reference arm uses (no fused "
+                         "cross entropy / RoPE / SwiGLU / add+RMSNorm kernels in the model); not the default")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a benchmark)")
     ap.add_argument("--vocab", type=int, default=None, help="debug only")
     ap.add_argument("--seq", type=int, default=SEQ, help="debug only")
@@ -145,7 +150,7 @@ def build_ours(args, rank, world):
     from opacus_b200 import PrivacyEngine
     from opacus_b200.distributed import DifferentiallyPrivateDistributedDataParallel as DPDDP
 
-    model, cfg = make_model(args, tie=True)
+    model, cfg = make_model(args, tie=not args.untied, plain=args.plain_model)
     module = model
     mode = "ghost"
     if args.engine == "sharded":
@@ -160,7 +165,7 @@ def build_ours(args, rank, world):
     ds = TensorDataset(torch.zeros(n_data, 1, dtype=torch.long))     # only its length matters (sample rate)
     dl = DataLoader(ds, batch_size=args.batch * world)
     engine = PrivacyEngine(accountant="rdp")
-    fused_ce = args.ce == "fused"
+    fused_ce = args.ce == "fused" and not args.plain_model
     if fused_ce:
         from opacus_b200.layers import FusedCrossEntropyLoss
 
@@ -182,6 +187,7 @@ def build_ours(args, rank, world):
         optimizer.step()
         return loss.detach()
 
+    step.engine = module._module if args.engine == "sharded" else None
     return step, cfg, engine, mode
 
 
@@ -307,15 +313,19 @@ def main():
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    # epsilon of exactly warmup + 2 * steps accounted steps, the same count in both arms
+    eps = None
+    try:
+        eps = float(engine.get_epsilon(1e-5))
+    except Exception:
+        pass
+    sharded = getattr(step, "engine", None)
+    replicas = replicas_identical(sharded, world) if sharded is not None else None
+    nvlink = nvlink_bytes_per_step(sharded) if sharded is not None else None
     # every rank runs the profiled extra step (it contains collectives / peer barriers)
     per_step = count_launches(step, ids_d[0], labels_d[0]) if args.impl == "ours" else None
 
     if rank == 0:
-        eps = None
-        try:
-            eps = float(engine.get_epsilon(1e-5))
-        except Exception:
-            pass
         launches = None if per_step is None else per_step * args.steps
         full = args.layers is None and args.vocab is None and args.seq == SEQ and args.batch == PER_GPU_BATCH
         out = {
@@ -336,6 +346,9 @@ def main():
                 "model": "llama-3.2-1b-shaped" if full else "DEBUG-reduced",
                 "layers": cfg.n_layers, "d_model": cfg.d_model, "vocab": cfg.vocab_size,
                 "tied_embeddings": cfg.tie_embeddings,
+                "model_definition": "stock PyTorch (baseline/llama_plain.py)" if (args.impl == "reference" or
+                                                                                  args.plain_model)
+                else "opacus_b200.models.Llama (fused RoPE / SwiGLU / add+RMSNorm / cross entropy)",
                 "global_batch": args.batch * world, "seq_len": args.seq,
                 "parallelism": ("single" if world == 1 else f"dp{world}") + f" ({mode})",
                 "optimizer": "DP-AdamW lr 1e-4", "noise_multiplier": SIGMA, "max_grad_norm": CLIP,
@@ -348,11 +361,42 @@ def main():
                     "ms_per_step": e2e_ms, "last_loss": last},
             "gpu_launches": launches,
         }
+        if replicas is not None:
+            out["replicas_identical"] = replicas
+        if nvlink is not None:
+            out["nvlink_bytes_per_step"] = nvlink
+            out["step_path"] = {"multicast": bool(sharded.multicast), "pieces": sharded.pieces,
+                                "launches_last_step": sharded.last_step_launches}
         print(json.dumps(out))
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def replicas_identical(engine, world):
+    """After the timed region: do all ranks hold the same compute weights, bit for bit?  (Two 64-bit
+    checksums of the flat parameter buffer, compared across ranks.)"""
+    flat = engine.flat_param()
+    words = flat.view(torch.int16 if flat.element_size() == 2 else torch.int32).to(torch.int64)
+    weights = torch.arange(words.numel(), device=words.device, dtype=torch.int64) % 65521 + 1
+    sums = torch.stack([words.sum(), (words * weights).sum()])
+    if world == 1:
+        return True
+    all_sums = [torch.empty_like(sums) for _ in range(world)]
+    dist.all_gather(all_sums, sums)
+    return all(bool(torch.equal(all_sums[0], t)) for t in all_sums[1:])
+
+
+def nvlink_bytes_per_step(engine):
+    """Bytes that leave one GPU over NVLink in the step kernel: its fp32 gradient sums read by the other owners,
+    and the new weights of its stripes (one copy into the switch with multicast stores, world - 1 copies without)."""
+    w = engine.world
+    if w == 1:
+        return 0
+    reduce_out = engine.total * 4 * (w - 1) // w
+    publish_out = engine.slice_len * engine.flat_param().element_size() * (1 if engine.multicast else w - 1)
+    return int(reduce_out + publish_out)
 
 
 def count_launches(step, ids, labels):

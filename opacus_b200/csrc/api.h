@@ -101,16 +101,33 @@ int dpk_fused_dp_step(const struct DpkTensorEntry* table_dev, int n_tensors, int
 // ---- sharded data-parallel step: reduce-scatter + noise + update + all-gather over peer memory
 // Pointer arrays are indexed by rank and hold addresses that are valid on THIS GPU (peer mappings of
 // symmetric allocations; entry [rank] is local).  grad/param are flat buffers over the whole parameter
-// space; master/state0/state1 cover only the owned slice [slice_begin, slice_begin + slice_len).
+// space; master/state0/state1 cover only the slice_len elements of it that this launch updates: the range
+// [slice_begin, slice_begin + slice_len) when stripe_len == 0, else slice_len / stripe_len stripes of
+// stripe_len elements whose starts are stripe_stride apart, the first at slice_begin (the flat space cut into
+// pieces of stripe_stride elements of which every rank owns one stripe).
 // flags: at least 32 zero-initialised 32-bit words per rank.  epoch: 1, 2, 3, ... on successive calls.
+// grad_mc / param_mc: the same two buffers through the address of an NVLink multicast object that all ranks'
+// copies are bound to (NVLS), or NULL: the reduce then uses plain peer loads, the publish plain peer stores.
+// segs (device memory, nseg entries, ends ascending, last end >= end of the flat space) gives ranges of the flat
+// space their own learning rate and weight decay; nseg <= 1 uses h for everything.
+// max_blocks > 0 caps the grid (a launch that shares the GPU with compute-bound kernels).
+struct DpkStepSegment {
+  int64_t end;
+  float lr, weight_decay;
+};
 struct DpkShardedStep {
   const float* grad[8];
   void* param[8];
   uint32_t* flags[8];
+  const float* grad_mc;
+  void* param_mc;
+  const struct DpkStepSegment* segs;
+  int32_t nseg, max_blocks;
   float* master;
   float* state0;
   float* state1;
   int64_t slice_begin, slice_len;
+  int64_t stripe_len, stripe_stride;
   // Elements of the flat space at or beyond noise_split draw their noise at counter index + noise_shift
   // (a multiple of 8): tensor-parallel ranks pass distinct shifts for their shards and share the rest.
   int64_t noise_split, noise_shift;

@@ -394,7 +394,9 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
                      int64_t kind, bool nesterov, bool first_step, double lr, double momentum, double dampening,
                      double weight_decay, double beta1, double beta2, double eps, double bias_c1,
                      double bias_c2_sqrt, double noise_std, double inv_scale, int64_t seed, int64_t offset,
-                     int64_t noise_split, int64_t noise_shift) {
+                     int64_t noise_split, int64_t noise_shift, int64_t grad_mc, int64_t param_mc,
+                     c10::optional<at::Tensor> segments, int64_t max_blocks, int64_t stripe_len,
+                     int64_t stripe_stride) {
   c10::cuda::CUDAGuard guard(master.device());
   raise_if_failed(master.get_device());
   const int world = (int)grad_ptrs.size();
@@ -411,6 +413,16 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
   p.state0 = state0.has_value() ? state0->data_ptr<float>() : nullptr;
   p.state1 = state1.has_value() ? state1->data_ptr<float>() : nullptr;
   p.slice_begin = slice_begin; p.slice_len = slice_len;
+  p.grad_mc = reinterpret_cast<const float*>(grad_mc);
+  p.param_mc = reinterpret_cast<void*>(param_mc);
+  p.max_blocks = (int)max_blocks;
+  p.stripe_len = stripe_len; p.stripe_stride = stripe_stride;
+  if (segments.has_value()) {
+    TORCH_CHECK(segments->is_cuda() && segments->scalar_type() == at::kByte && segments->is_contiguous() &&
+                segments->numel() % sizeof(DpkStepSegment) == 0, "segments must be a CUDA byte tensor of DpkStepSegment");
+    p.segs = reinterpret_cast<const DpkStepSegment*>(segments->data_ptr());
+    p.nseg = (int)(segments->numel() / sizeof(DpkStepSegment));
+  }
   TORCH_CHECK(noise_split >= 0 && noise_shift >= 0 && noise_split % 8 == 0 && noise_shift % 8 == 0,
               "noise_split and noise_shift must be non-negative multiples of 8");
   p.noise_split = noise_split; p.noise_shift = noise_shift;
@@ -652,6 +664,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_dp_step", &fused_dp_step);
   m.def("sharded_dp_step", &sharded_dp_step);
   m.def("norm_allreduce_clip", &norm_allreduce_clip);
+  m.def("step_segment_size", []() { return (int64_t)sizeof(DpkStepSegment); });
   m.def("tp_gemm", &tp_gemm);
   m.def("cross_entropy_forward", &cross_entropy_forward);
   m.def("cross_entropy_backward", &cross_entropy_backward);

@@ -250,6 +250,14 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t a
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// ----------------------------------------------------------------------------- clip factor
+// min(1, C / (sqrt(max(n2, 0)) + 1e-6)) (opacus/optimizers/optimizer.py:452-455), except that a NaN squared norm
+// gives NaN: fmaxf / fminf return their non-NaN argument, which would turn "norm unknown" into "do not clip".
+__device__ __forceinline__ float clip_factor_of(float n2, float C) {
+  if (n2 != n2) return n2;
+  return fminf(1.f, C / (sqrtf(fmaxf(n2, 0.f)) + 1e-6f));
+}
+
 // ----------------------------------------------------------------------------- flag waits between ranks / blocks
 // Epoch flags: a word holds the number of the last step its writer reached.  The high bit tells waiters to give up.
 constexpr uint32_t kAbortBit = 0x80000000u;

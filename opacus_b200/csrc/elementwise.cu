@@ -86,9 +86,11 @@ __global__ void scale_rows_kernel(const void* x, const float* c, __nv_bfloat16* 
 }
 
 // ---------------------------------------------------------------- clip factor
+// A NaN norm (a producer that marked unfinished work, an overflow upstream) gives a NaN factor, never 1:
+// clipping must not fail open.  fmaxf / fminf would drop the NaN.
 __global__ void clip_factor_kernel(const float* n2, float* c, int64_t B, float C) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i < B) c[i] = fminf(1.f, C / (sqrtf(fmaxf(n2[i], 0.f)) + 1e-6f));
+  if (i < B) c[i] = clip_factor_of(n2[i], C);
 }
 
 // ---------------------------------------------------------------- per-row squared norm

@@ -40,7 +40,16 @@ __global__ void __launch_bounds__(256) norm_allreduce_clip_kernel(DpkNormAllRedu
     if (!spin_until_epoch(p.flags[p.rank] + p.flag_base + threadIdx.x, p.epoch, p.status, 31)) sh_ok = 0;
   }
   __syncthreads();
-  if (!sh_ok) return;
+  if (!sh_ok) {
+    // a peer never arrived: the host learns it from the status word, but kernels already queued behind this
+    // one read the outputs first -- they must see "no gradient passes" (NaN), not uninitialised memory
+    const float nan = __int_as_float(0x7fc00000);
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+      if (p.total_out) p.total_out[i] = nan;
+      if (p.clip_out) p.clip_out[i] = nan;
+    }
+    return;
+  }
   __threadfence_system();
   // 3. sum in rank order, add what is replicated, form the clip factor
   const volatile float* mine = p.slots[p.rank] + (int64_t)(p.epoch & 1u) * half;
@@ -49,7 +58,7 @@ __global__ void __launch_bounds__(256) norm_allreduce_clip_kernel(DpkNormAllRedu
     for (int r = 0; r < p.world; ++r) t += mine[(int64_t)r * p.capacity + i];
     if (p.replicated) t += p.replicated[i];
     if (p.total_out) p.total_out[i] = t;
-    if (p.clip_out) p.clip_out[i] = fminf(1.f, p.max_norm / (sqrtf(fmaxf(t, 0.f)) + 1e-6f));
+    if (p.clip_out) p.clip_out[i] = clip_factor_of(t, p.max_norm);
   }
 }
 

@@ -10,6 +10,19 @@
 //   all-gather     : the new weights are stored, in compute precision, straight
 //                    into every rank's parameter buffer (plain peer stores)
 //
+// When the buffers are bound to an NVLink multicast object (NVLS), the reduce is ONE
+// multimem.ld_reduce per 16 bytes -- the switch adds the eight copies and returns the sum,
+// so a rank receives 1/world of the bytes the peer-load loop pulls and needs 1/world of
+// the loads in flight -- and the publish is ONE multimem.st per 16 bytes, replicated by
+// the switch, instead of world - 1 stores that each cross this GPU's link.
+//
+// A launch covers any 8-aligned range of the rank's share, so the host can step the flat
+// space in pieces, each as soon as its gradients are final on every rank, beside the
+// weight-gradient GEMMs that are still running; every launch is one flag epoch.
+//
+// Parameter groups with their own learning rate / weight decay are ranges of the flat
+// space listed in a small device table (segment ends, ascending), searched per 8 elements.
+//
 // Ranks meet twice through flag words in symmetric memory: before the first peer
 // access (everyone's gradients are final, nobody still reads the old weights) and
 // after the last store (everyone's weights are complete when the kernel ends).
@@ -31,6 +44,22 @@ constexpr int kSlotDone = 8;      // flags[kSlotDone + r]   : rank r finished it
 constexpr int kSlotGo = 16;       // local: block 0 -> other blocks
 constexpr int kSlotCount = 17;    // local: finished-block counter
 constexpr int kShThreads = 512;
+
+// Sum over all ranks' copies of 4 consecutive floats, formed inside the NVSwitch.
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// 16 bytes stored into every rank's copy (the payload is opaque bits; .f32 only names the vector shape).
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
 
 __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep p) {
   __shared__ uint32_t sh_ok;
@@ -58,19 +87,39 @@ __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep
 
   // ---------------------------------------------------------------- reduce, noise, update, publish
   if (go) {
-    const DpkStepHyper h = p.h;
+    __threadfence_system();          // the peers' gradient stores, published by their flags, before any read here
+    DpkStepHyper h = p.h;
     const Philox rng(h.seed);
     const int64_t nvec = p.slice_len >> 3;
     for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t li = v << 3;                 // index inside the owned slice
-      const int64_t gi = p.slice_begin + li;     // index in the flat parameter space
+      const int64_t li = v << 3;                 // index inside the owned share covered by this launch
+      int64_t gi = p.slice_begin + li;           // index in the flat parameter space
+      if (p.stripe_len > 0) {                    // the share is one stripe of every piece: stripes are stripe_stride apart
+        const int64_t k = li / p.stripe_len;
+        gi += k * (p.stripe_stride - p.stripe_len);
+      }
       float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int q = 0; q < p.world; ++q) {
-        int r = p.rank + q;
-        if (r >= p.world) r -= p.world;
-        const float4* src = reinterpret_cast<const float4*>(p.grad[r] + gi);
-        const float4 a = __ldcg(src), b = __ldcg(src + 1);
-        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+      if (p.grad_mc != nullptr) {
+        const float4 a = multimem_ld_reduce_f32x4(p.grad_mc + gi), b = multimem_ld_reduce_f32x4(p.grad_mc + gi + 4);
+        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+      } else {
+        for (int q = 0; q < p.world; ++q) {
+          int r = p.rank + q;
+          if (r >= p.world) r -= p.world;
+          const float4* src = reinterpret_cast<const float4*>(p.grad[r] + gi);
+          const float4 a = __ldcg(src), b = __ldcg(src + 1);
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        }
+      }
+      if (p.nseg > 1) {
+        // first segment whose end lies beyond gi (parameters start on multiples of 64: a vector has one segment)
+        int lo = 0, hi = p.nseg - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (__ldg(&p.segs[mid].end) > gi) hi = mid; else lo = mid + 1;
+        }
+        h.lr = __ldg(&p.segs[lo].lr);
+        h.weight_decay = __ldg(&p.segs[lo].weight_decay);
       }
       if (h.noise_std != 0.f) {
         const uint64_t ni = static_cast<uint64_t>(gi >= p.noise_split ? gi + p.noise_shift : gi);
@@ -136,11 +185,21 @@ __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep
           __nv_bfloat162 hv = __floats2bfloat162_rn(w[2 * q], w[2 * q + 1]);
           pw[q] = *reinterpret_cast<uint32_t*>(&hv);
         }
-        for (int q = 0; q < p.world; ++q) {
-          int r = p.rank + q;
-          if (r >= p.world) r -= p.world;
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.param[r]) + gi) = pk;
+        if (p.param_mc != nullptr) {
+          multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(p.param_mc) + gi, pk);
+        } else {
+          for (int q = 0; q < p.world; ++q) {
+            int r = p.rank + q;
+            if (r >= p.world) r -= p.world;
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.param[r]) + gi) = pk;
+          }
         }
+      } else if (p.param_mc != nullptr) {
+        float* dst = reinterpret_cast<float*>(p.param_mc) + gi;
+        multimem_st_b128(dst, make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
+                                         __float_as_uint(w[3])));
+        multimem_st_b128(dst + 4, make_uint4(__float_as_uint(w[4]), __float_as_uint(w[5]), __float_as_uint(w[6]),
+                                             __float_as_uint(w[7])));
       } else {
         for (int q = 0; q < p.world; ++q) {
           int r = p.rank + q;
@@ -178,6 +237,12 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
   const DpkShardedStep& p = *ph;
   if (p.world < 1 || p.world > 8 || p.rank < 0 || p.rank >= p.world || (p.slice_len & 7) || (p.slice_begin & 7))
     return cudaErrorInvalidValue;
+  if (p.nseg < 0 || (p.nseg > 1 && p.segs == nullptr)) return cudaErrorInvalidValue;
+  if (p.slice_len == 0) return cudaErrorInvalidValue;
+  if (p.stripe_len < 0 || (p.stripe_len & 7) || (p.stripe_stride & 7) || (p.stripe_len > 0 && p.stripe_stride < p.stripe_len))
+    return cudaErrorInvalidValue;     // every launch is a meeting of all ranks: no empty ranges
+  if ((reinterpret_cast<uintptr_t>(p.grad_mc) & 15) || (reinterpret_cast<uintptr_t>(p.param_mc) & 15))
+    return cudaErrorInvalidValue;
   // every block spins on flags, so all of them must be resident at once: as many per SM as fit
   static int per_sm_cached = 0;
   if (per_sm_cached == 0) {
@@ -186,6 +251,7 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
     per_sm_cached = n > 4 ? 4 : n;
   }
   int grid = num_sms() * per_sm_cached;
+  if (p.max_blocks > 0 && p.max_blocks < grid) grid = p.max_blocks;   // a piece beside GEMMs leaves them the SMs
   const int64_t nvec = p.slice_len >> 3;
   const int64_t need = (nvec + kShThreads - 1) / kShThreads;
   if (need < grid) grid = need < 1 ? 1 : (int)need;

@@ -408,19 +408,51 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                 st.wait_stream(main)
             lanes = [main] + sides
         lane_of = {}
-        for site in self._sites:
+        for order, site in enumerate(self._sites_by_parameter()):
             if lanes is not None:
-                ps = [id(p) for _, p in trainable_parameters(site.module)]
+                owned = self._site_params(site)
+                ps = [id(p) for p in owned]
                 lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % len(lanes))
                 for i in ps:
                     lane_of[i] = lane
                 with torch.cuda.stream(lanes[lane]):
                     self._write_site(site, coef)
+                    if any(getattr(p, "_dp_grad_out", None) is not None for p in owned):
+                        # an engine that owns the gradient storage may step the parts of the flat space written so
+                        # far while later sums still run: (stream, position, event) of each parameter's last write
+                        done = torch.cuda.Event()
+                        done.record(lanes[lane])
+                        for p in owned:
+                            p._dp_ready = (lane, order, done)
             else:
                 self._write_site(site, coef)
         if lanes is not None:
             for st in lanes[1:]:
                 lanes[0].wait_stream(st)
+
+    def _site_params(self, site):
+        cached = site.module.__dict__.get("_dp_own_params")
+        if cached is None:
+            cached = site.module.__dict__["_dp_own_params"] = [p for _, p in trainable_parameters(site.module)]
+        return cached
+
+    def _sites_by_parameter(self):
+        """The captured sites in backward order, except that the later uses of a shared parameter follow its first
+        use directly: the parameter's sum is then complete early instead of only when the last site is written."""
+        if all(len(v) < 2 for v in self._uses.values()):
+            return self._sites
+        out, seen = [], set()
+        for site in self._sites:
+            if id(site) in seen:
+                continue
+            seen.add(id(site))
+            out.append(site)
+            for p in self._site_params(site):
+                for other in self._uses.get(p, ()):
+                    if id(other) not in seen:
+                        seen.add(id(other))
+                        out.append(other)
+        return out
 
     def _write_site(self, site, coef):
         mtype = self._get_module_type(site.module)

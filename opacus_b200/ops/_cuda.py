@@ -18,7 +18,7 @@ import torch
 from . import _ref
 
 _C = None
-_scratch: Dict[torch.device, torch.Tensor] = {}
+_scratch: Dict[tuple, torch.Tensor] = {}
 
 
 def load():
@@ -76,10 +76,14 @@ def _bt(x: torch.Tensor) -> torch.Tensor:
 
 
 def _scratch_for(device, floats: int) -> torch.Tensor:
-    buf = _scratch.get(device)
+    """Work space of the ghost-norm kernel, one buffer per (device, stream): calls on different streams never
+    share it, and a buffer is only ever replaced from the stream that uses it (allocated while that stream is
+    current, so the caching allocator orders its reuse after the kernels already queued there)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
     if buf is None or buf.numel() < floats:
         buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
-        _scratch[device] = buf
+        _scratch[key] = buf
     return buf
 
 
@@ -403,8 +407,28 @@ def _rng_state(generator, device, n_elems: int):
 
 
 def fused_dp_step(kind, inner, group, ps, *, noise_std: float, inv_scale: float, generator=None):
-    """One launch: p.summed_grad <- (summed_grad + N(0, std^2)) * inv_scale, then the
-    SGD / Adam / AdamW update of ``p`` and its state, for every tensor in ``ps``."""
+    """p.summed_grad <- (summed_grad + N(0, std^2)) * inv_scale, then the SGD / Adam / AdamW update of ``p``
+    and its state, for every tensor in ``ps``: one launch for all tensors that are at the same point of their
+    history (same Adam step count / same "momentum buffer exists"), which is all of them unless parameters
+    were added to the optimiser later."""
+    state = inner.state
+    if kind == "sgd":
+        has_momentum = float(group.get("momentum", 0.0)) != 0.0
+        key = (lambda p: state[p].get("momentum_buffer") is None if p in state else True) if has_momentum \
+            else (lambda p: False)
+    else:
+        key = lambda p: float(state[p]["step"]) if p in state and len(state[p]) else 0.0
+    parts = {}
+    for p in ps:
+        parts.setdefault(key(p), []).append(p)
+    for where, part in parts.items():
+        _fused_dp_step_uniform(kind, inner, group, part, where, noise_std, inv_scale, generator)
+
+
+_table_cache: Dict[tuple, tuple] = {}
+
+
+def _fused_dp_step_uniform(kind, inner, group, ps, where, noise_std, inv_scale, generator):
     C = load()
     assert C.tensor_entry_size() == _ENTRY.itemsize
     dev = ps[0].device
@@ -418,7 +442,7 @@ def fused_dp_step(kind, inner, group, ps, *, noise_std: float, inv_scale: float,
         hyper["dampening"] = float(group.get("dampening", 0.0))
         nesterov = bool(group.get("nesterov", False))
         if hyper["momentum"] != 0.0:
-            first_step = state[ps[0]].get("momentum_buffer") is None if ps[0] in state else True
+            first_step = bool(where)
             for p in ps:
                 st = state[p]
                 if st.get("momentum_buffer") is None:
@@ -432,40 +456,57 @@ def fused_dp_step(kind, inner, group, ps, *, noise_std: float, inv_scale: float,
                 st["step"] = torch.tensor(0.0, dtype=torch.float32)
                 st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
                 st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
-        t = float(state[ps[0]]["step"]) + 1.0
+        t = float(where) + 1.0
         for p in ps:
             state[p]["step"] += 1
         hyper.update(beta1=float(beta1), beta2=float(beta2), eps=float(group["eps"]),
                      bias_c1=1.0 - float(beta1) ** t, bias_c2_sqrt=math.sqrt(1.0 - float(beta2) ** t))
         kcode = 2 if kind == "adamw" else 1
 
-    table = np.zeros(len(ps), dtype=_ENTRY)
-    prefix = np.zeros(len(ps) + 1, dtype=np.int64)
-    rng_ofs = 0
-    for i, p in enumerate(ps):
+    for p in ps:
         g = p.summed_grad
         if g.dtype != torch.float32 or not g.is_contiguous():
-            g = g.float().contiguous()
-            p.summed_grad = g
-        st = state[p] if p in state else {}
-        e = table[i]
-        e["param"] = p.data_ptr()
-        e["grad"] = g.data_ptr()
-        if kind == "sgd":
-            buf = st.get("momentum_buffer")
-            e["state0"] = buf.data_ptr() if buf is not None else 0
-        else:
-            e["state0"] = st["exp_avg"].data_ptr()
-            e["state1"] = st["exp_avg_sq"].data_ptr()
-        e["numel"] = p.numel()
-        e["rng_offset"] = rng_ofs
-        e["param_bf16"] = 1 if p.dtype == torch.bfloat16 else 0
-        rng_ofs += 4 * ((p.numel() + 3) // 4)
-        prefix[i + 1] = prefix[i] + (p.numel() + _CHUNK - 1) // _CHUNK
+            p.summed_grad = g.float().contiguous()
+    # the table of addresses is rebuilt and uploaded only when an address changed (summed_grad is reallocated
+    # by every backward pass in hooks mode, but lives in fixed storage under the engines)
+    if kind == "sgd":
+        st_ptrs = tuple(0 if state[p].get("momentum_buffer") is None else state[p]["momentum_buffer"].data_ptr()
+                        for p in ps) if hyper["momentum"] != 0.0 else ()
+    else:
+        st_ptrs = tuple((state[p]["exp_avg"].data_ptr(), state[p]["exp_avg_sq"].data_ptr()) for p in ps)
+    sig = tuple((p.data_ptr(), p.summed_grad.data_ptr(), p.numel()) for p in ps) + (st_ptrs, kind, dev)
+    slot = (id(inner), id(group), len(ps), ps[0].data_ptr())
+    cached = _table_cache.get(slot)
+    if cached is not None and cached[0] == sig:
+        _, table_t, prefix_t, n_chunks, rng_ofs = cached
+    else:
+        table = np.zeros(len(ps), dtype=_ENTRY)
+        prefix = np.zeros(len(ps) + 1, dtype=np.int64)
+        rng_ofs = 0
+        for i, p in enumerate(ps):
+            st = state[p] if p in state else {}
+            e = table[i]
+            e["param"] = p.data_ptr()
+            e["grad"] = p.summed_grad.data_ptr()
+            if kind == "sgd":
+                buf = st.get("momentum_buffer")
+                e["state0"] = buf.data_ptr() if buf is not None else 0
+            else:
+                e["state0"] = st["exp_avg"].data_ptr()
+                e["state1"] = st["exp_avg_sq"].data_ptr()
+            e["numel"] = p.numel()
+            e["rng_offset"] = rng_ofs
+            e["param_bf16"] = 1 if p.dtype == torch.bfloat16 else 0
+            rng_ofs += 4 * ((p.numel() + 3) // 4)
+            prefix[i + 1] = prefix[i] + (p.numel() + _CHUNK - 1) // _CHUNK
+        table_t = torch.from_numpy(table.view(np.uint8)).to(dev, non_blocking=True)
+        prefix_t = torch.from_numpy(prefix).to(dev, non_blocking=True)
+        n_chunks = int(prefix[-1])
+        if len(_table_cache) > 64:
+            _table_cache.clear()
+        _table_cache[slot] = (sig, table_t, prefix_t, n_chunks, rng_ofs)
     seed, offset = _rng_state(generator, dev, rng_ofs)
-    table_t = torch.from_numpy(table.view(np.uint8)).to(dev, non_blocking=True)
-    prefix_t = torch.from_numpy(prefix).to(dev, non_blocking=True)
-    C.fused_dp_step(table_t, prefix_t, len(ps), int(prefix[-1]), kcode, nesterov, first_step,
+    C.fused_dp_step(table_t, prefix_t, len(ps), n_chunks, kcode, nesterov, first_step,
                     hyper["lr"], hyper["momentum"], hyper["dampening"], hyper["weight_decay"], hyper["beta1"],
                     hyper["beta2"], hyper["eps"], hyper["bias_c1"], hyper["bias_c2_sqrt"], float(noise_std),
                     float(inv_scale), seed, offset)

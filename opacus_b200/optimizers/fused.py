@@ -39,16 +39,34 @@ class _FusedPlan:
                 p.grad = g if g.dtype == p.dtype else g.to(p.dtype)
 
 
-def plan_for(opt) -> Optional[_FusedPlan]:
-    """A plan if every parameter is a CUDA tensor and the wrapped optimiser is a
-    configuration the kernel implements; else ``None`` (the staged path runs)."""
-    cached = getattr(opt, "_fused_plan_cache", None)
+_GROUP_FLAGS = ("maximize", "differentiable", "amsgrad", "capturable", "decoupled_weight_decay", "foreach", "fused")
+
+
+def _config_key(opt):
+    """What the decision depends on; recomputed every step (cheap) so that ``add_param_group`` or an edited
+    group flag is seen."""
     inner = opt.original_optimizer
-    if cached is not None and cached[0] is type(inner):
+    groups = tuple((len(g["params"]), isinstance(g.get("lr"), torch.Tensor)) + tuple(bool(g.get(k, False))
+                                                                                   for k in _GROUP_FLAGS)
+                   for g in inner.param_groups)
+    gen = opt.generator
+    return (type(inner), groups, None if gen is None else gen.device.type)
+
+
+def plan_for(opt) -> Optional[_FusedPlan]:
+    """A plan if every parameter is a CUDA tensor, the noise generator (if one was given) lives on the GPU and
+    the wrapped optimiser is a configuration the kernel implements; else ``None`` (the staged path runs).
+    Optimiser state is created in fp32 also for bf16 parameters (the update is done in fp32)."""
+    key = _config_key(opt)
+    cached = getattr(opt, "_fused_plan_cache", None)
+    if cached is not None and cached[0] == key:
         return cached[1]
+    inner = opt.original_optimizer
     plan = None
     ps = opt.params
     ok = bool(ps) and all(p.is_cuda and p.dtype in (torch.float32, torch.bfloat16) for p in ps)
+    if ok and opt.generator is not None and opt.generator.device.type != "cuda":
+        ok = False                    # the kernel's Philox stream is keyed by a CUDA generator's (seed, offset)
     if ok:
         t = type(inner)
         if t is torch.optim.SGD:
@@ -63,5 +81,5 @@ def plan_for(opt) -> Optional[_FusedPlan]:
             decoupled = t is torch.optim.AdamW or any(g.get("decoupled_weight_decay", False)
                                                       for g in inner.param_groups)
             plan = _FusedPlan("adamw" if decoupled else "adam") if ok else None
-    opt._fused_plan_cache = (type(inner), plan)
+    opt._fused_plan_cache = (key, plan)
     return plan

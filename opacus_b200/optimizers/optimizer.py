@@ -301,8 +301,15 @@ class DPOptimizer(Optimizer):
         return self.original_optimizer.__repr__()
 
     def state_dict(self):
-        """Exactly the wrapped optimiser's state (checkpoint compatible with it)."""
+        """Exactly the wrapped optimiser's state (checkpoint compatible with it).  Under a sharded engine the
+        state lives on the engine, 1/world per rank; it is gathered into the same layout (a collective call)."""
+        engine = getattr(self, "engine", None)
+        if engine is not None and hasattr(engine, "optimizer_state_dict"):
+            return engine.optimizer_state_dict(self.original_optimizer)
         return self.original_optimizer.state_dict()
 
     def load_state_dict(self, state_dict) -> None:
+        engine = getattr(self, "engine", None)
+        if engine is not None and hasattr(engine, "load_optimizer_state_dict"):
+            return engine.load_optimizer_state_dict(self.original_optimizer, state_dict)
         self.original_optimizer.load_state_dict(state_dict)

@@ -3,26 +3,40 @@
 Layout, sized for GPUs with far more memory than a billion-parameter model
 needs: the *compute* copy of the parameters (bf16 by default) is whole on every
 GPU, in one flat buffer that peers can write; the fp32 master weights and the
-optimiser state exist only for the slice of the flat space a rank owns
+optimiser state exist only for the share of the flat space a rank owns
 (``1/world`` each); clipped gradient sums are written by the ghost-clipping
 engine straight into a flat fp32 buffer that peers can read.
 
-A training step then needs no collective during forward or backward, and one
-kernel at the end (``csrc/sharded_step.cu``): reduce-scatter of the gradient
-sums over NVLink, one Gaussian draw per owned element, scaling, the SGD / Adam /
-AdamW update of the owned slice, and the all-gather of the new weights into
-every GPU's compute buffer -- all inside the same launch.
+The flat space is cut into ``pieces`` equal pieces and every rank owns one
+*stripe* (``1/world``) of every piece.  A training step needs no collective
+during forward or backward.  Its tail is the kernel of ``csrc/sharded_step.cu``:
+reduce-scatter of the gradient sums over NVLink (one ``multimem.ld_reduce`` per
+16 bytes when the buffers are bound to an NVLink multicast object, plain peer
+loads otherwise), one Gaussian draw per owned element, scaling, the SGD / Adam /
+AdamW update of the owned stripes, and the all-gather of the new weights into
+every GPU's compute buffer (``multimem.st`` or peer stores).  With several ranks
+the kernel is launched piece by piece on a side stream, each piece as soon as
+the clipped sums that land in it are complete, so that the NVLink traffic runs
+beside the remaining weight-gradient GEMMs instead of after them.
 
 The reference obtains the same state sharding from ``torch`` FSDP2 at the cost
 of three parameter all-gathers and two gradient reduce-scatters per step
 (``opacus/utils/fsdp_utils.py:39-61``,
 ``opacus/optimizers/fsdpoptimizer_fast_gradient_clipping.py:32-181``).
+
+Checkpoints: :meth:`state_dict` returns the fp32 master weights under the wrapped
+module's own keys, :meth:`optimizer_state_dict` the optimiser state in the
+``torch.optim`` layout (both gather from the owners: collective calls);
+loading either refreshes the sharded fp32 state, so a resumed run continues
+bit for bit (``opacus/privacy_engine.py:618-696`` is the file format).
 """
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -30,7 +44,9 @@ import torch.nn as nn
 from . import symm
 
 _ALIGN = 64           # every parameter starts on a 64-element boundary of the flat space
-_SLICE_QUANTUM = 1024
+_STRIPE_QUANTUM = 1024
+_KINDS = {torch.optim.SGD: "sgd", torch.optim.Adam: "adam", torch.optim.AdamW: "adamw"}
+_SEGMENT = np.dtype([("end", "<i8"), ("lr", "<f4"), ("weight_decay", "<f4")])
 
 
 class ShardedDataParallel(nn.Module):
@@ -39,10 +55,14 @@ class ShardedDataParallel(nn.Module):
     by :mod:`opacus_b200.parallel.tensor_parallel` (2-D layout: every tensor-parallel rank runs this engine over
     its own data-parallel group).  Parameters marked ``tp_sharded`` then draw their noise from a Philox range of
     their tensor-parallel rank, all others from a range common to the tensor-parallel group under a seed the
-    group agrees on, so that shards get independent noise and replicas stay bit-identical."""
+    group agrees on, so that shards get independent noise and replicas stay bit-identical.
+
+    ``step_pieces``: into how many pieces the flat space is cut (default: 16 with several ranks and a model of
+    at least a few million parameters, else 1).  ``multicast``: use the NVLink multicast address of the buffers
+    when there is one (default; ``False`` or ``OPACUS_B200_MULTICAST=0`` keeps plain peer loads and stores)."""
 
     def __init__(self, module: nn.Module, *, param_dtype: torch.dtype = torch.bfloat16, process_group=None,
-                 tp_group=None, **unused):
+                 tp_group=None, step_pieces: Optional[int] = None, multicast: Optional[bool] = None, **unused):
         super().__init__()
         first = next(module.parameters())
         if not first.is_cuda:
@@ -74,25 +94,44 @@ class ShardedDataParallel(nn.Module):
             # Ranks of a tensor-parallel group run this engine with the same flat layout; under one seed two shards
             # of one weight would receive the SAME noise values, and correlated noise is not the Gaussian mechanism.
             raise ValueError("the module holds tensor-parallel shards: pass tp_group= so that they draw independent noise")
-        total = 0
+        used = 0
         self.noise_split = None
         # replicated parameters first, shards behind them: one split point separates the two noise ranges
         for p in [q for q in distinct if not getattr(q, "tp_sharded", False)] + shards:
             if shards and p is shards[0]:
-                self.noise_split = total
-            self._offsets[p] = total
+                self.noise_split = used
+            self._offsets[p] = used
             self._params.append(p)
-            total += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+            used += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.used = used
         # sums of parameters that saw only this tensor-parallel rank's samples are completed before the step
         self._tp_partial = [p for p in distinct if getattr(p, "sp_local", False)] if tp_group is not None else []
         self._tp_seed = None
-        self.slice_len = (math.ceil(total / self.world) + _SLICE_QUANTUM - 1) // _SLICE_QUANTUM * _SLICE_QUANTUM
-        self.total = self.slice_len * self.world
-        self.slice_begin = self.rank * self.slice_len
+
+        # ---- pieces and stripes: piece k is [k * piece_len, (k + 1) * piece_len), rank r owns its r-th stripe
+        if step_pieces is None:
+            step_pieces = 16 if self.world > 1 else 1
+            step_pieces = max(1, min(step_pieces, used // (self.world * (1 << 18))))
+        self.pieces = int(step_pieces)
+        if self.pieces < 1:
+            raise ValueError("step_pieces must be at least 1")
+        cells = self.pieces * self.world
+        self.stripe = (math.ceil(max(used, 1) / cells) + _STRIPE_QUANTUM - 1) // _STRIPE_QUANTUM * _STRIPE_QUANTUM
+        self.piece_len = self.stripe * self.world
+        self.total = self.piece_len * self.pieces
+        self.slice_len = self.stripe * self.pieces            # elements this rank owns
 
         self._flat_param = symm.alloc(self.total, param_dtype, dev, process_group)
         self._flat_grad = symm.alloc(self.total, torch.float32, dev, process_group)
         self._flags = symm.alloc(64, torch.int32, dev, process_group)
+        if multicast is None:
+            multicast = os.environ.get("OPACUS_B200_MULTICAST", "1") != "0"
+        self.multicast = bool(multicast) and self.world > 1 and self._flat_param.mc_ptr != 0 \
+            and self._flat_grad.mc_ptr != 0
+        if self.world > 1:                 # all ranks take the same path or none
+            flag = torch.tensor([1 if self.multicast else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=process_group)
+            self.multicast = bool(flag.item())
 
         # ---- identical start on every rank, then adopt the flat storage
         full = torch.zeros(self.total, dtype=torch.float32, device=dev)
@@ -102,7 +141,7 @@ class ShardedDataParallel(nn.Module):
         if self.world > 1:
             dist.broadcast(full, dist.get_global_rank(process_group, 0) if process_group is not None else 0,
                            group=process_group)
-        self.master = full[self.slice_begin: self.slice_begin + self.slice_len].clone()
+        self.master = self._share_of(full).clone()
         self._flat_param.tensor.copy_(full.to(param_dtype))
         del full
         for p in self._params:
@@ -120,8 +159,34 @@ class ShardedDataParallel(nn.Module):
         self.state1: Optional[torch.Tensor] = None
         self._epoch = 0
         self._steps = 0
+        self._step_stream = None
+        self._segments = None            # (key, device table) of the per-group hyper-parameter ranges
+        self._pending_fp32: Optional[Dict[str, torch.Tensor]] = None
+        self.last_step_launches = 0
+        self.register_load_state_dict_pre_hook(self._before_load)
+        self.register_load_state_dict_post_hook(self._after_load)
+        module.register_load_state_dict_post_hook(self._after_inner_load)
         if self.world > 1:
             dist.barrier(group=process_group)
+
+    # ------------------------------------------------------------------ layout helpers
+    def _share_of(self, full: torch.Tensor) -> torch.Tensor:
+        """This rank's stripes of a ``[total]`` tensor, concatenated in piece order (a view when ``world == 1``)."""
+        return full.view(self.pieces, self.world, self.stripe)[:, self.rank].reshape(-1)
+
+    def _gather(self, share: torch.Tensor) -> torch.Tensor:
+        """``[total]`` tensor in flat order from every rank's share (collective)."""
+        if self.world == 1:
+            return share
+        parts = [torch.empty_like(share) for _ in range(self.world)]
+        dist.all_gather(parts, share.contiguous(), group=self.process_group)
+        return torch.stack(parts).view(self.world, self.pieces, self.stripe).permute(1, 0, 2).reshape(-1)
+
+    def _named_trainable(self):
+        """(name, parameter) for every name under which a parameter of the flat space is reachable."""
+        for name, p in self.module.named_parameters(remove_duplicate=False):
+            if p in self._offsets:
+                yield name, p
 
     # ------------------------------------------------------------------ module API
     def forward(self, *args, **kwargs):
@@ -131,9 +196,13 @@ class ShardedDataParallel(nn.Module):
         """The next clipped-gradient write overwrites instead of accumulating."""
         for p in self._params:
             p._dp_grad_fresh = True
+            p.__dict__.pop("_dp_ready", None)
 
     def flat_grad(self) -> torch.Tensor:
         return self._flat_grad.tensor
+
+    def flat_param(self) -> torch.Tensor:
+        return self._flat_param.tensor
 
     def finish_grads(self):
         """Zero the gradient of parameters that received none in this step."""
@@ -142,14 +211,10 @@ class ShardedDataParallel(nn.Module):
                 p._dp_grad_out.zero_()
                 p._dp_grad_fresh = False
 
+    # ------------------------------------------------------------------ checkpoints
     def full_precision_state_dict(self) -> Dict[str, torch.Tensor]:
         """fp32 master weights of the whole model, gathered from their owners (collective)."""
-        if self.world > 1:
-            pieces = [torch.empty_like(self.master) for _ in range(self.world)]
-            dist.all_gather(pieces, self.master, group=self.process_group)
-            full = torch.cat(pieces)
-        else:
-            full = self.master
+        full = self._gather(self.master)
         out = {}
         for name, p in self.module.named_parameters():
             if p in self._offsets:
@@ -159,6 +224,113 @@ class ShardedDataParallel(nn.Module):
                 out[name] = p.detach().clone()
         return out
 
+    def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
+        """The wrapped module's ``state_dict`` (its own keys, no extra prefix) with every trainable parameter in
+        fp32 master precision.  Collective: all ranks of the group call it."""
+        sd = self.module.state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
+        full = self._gather(self.master)
+        for name, p in self._named_trainable():
+            o = self._offsets[p]
+            sd[prefix + name] = full[o: o + p.numel()].view(p.shape)
+        return sd
+
+    def _before_load(self, module, state_dict, prefix, *unused):
+        """Keys come without the ``module.`` level (as :meth:`state_dict` writes them, and as a checkpoint of
+        the bare model has them); full-precision values are set aside for the master weights."""
+        own = prefix + "module."
+        for key in [k for k in state_dict if k.startswith(prefix) and not k.startswith(own)]:
+            state_dict[own + key[len(prefix):]] = state_dict.pop(key)
+        self._pending_fp32 = {}
+        for name, _ in self._named_trainable():
+            v = state_dict.get(own + name)
+            if isinstance(v, torch.Tensor):
+                self._pending_fp32[name] = v
+
+    def _after_load(self, module, incompatible_keys):
+        pending, self._pending_fp32 = self._pending_fp32, None
+        self.refresh_master(pending)
+
+    def _after_inner_load(self, module, incompatible_keys):
+        if self._pending_fp32 is None:       # loaded through the wrapped module directly: compute precision only
+            self.refresh_master(None)
+
+    @torch.no_grad()
+    def refresh_master(self, values: Optional[Dict[str, torch.Tensor]] = None):
+        """Make the fp32 master weights (and the compute copy) equal to ``values`` (name -> tensor) where given
+        and to the current compute copy elsewhere.  Call it after changing parameter values by hand: the next
+        step otherwise publishes the old master weights again."""
+        full = self._flat_param.tensor.float()
+        if values:
+            for name, p in self._named_trainable():
+                v = values.get(name)
+                if v is not None:
+                    o = self._offsets[p]
+                    full[o: o + p.numel()].copy_(v.detach().reshape(-1).to(device=full.device, dtype=torch.float32))
+        self.master.copy_(self._share_of(full))
+        self._flat_param.tensor.copy_(full.to(self.param_dtype))
+
+    def _state_names(self, inner):
+        kind = _KINDS.get(type(inner))
+        if kind is None:
+            raise NotImplementedError(f"the sharded engine implements SGD, Adam and AdamW, not {type(inner).__name__}")
+        return ("momentum_buffer",) if kind == "sgd" else ("exp_avg", "exp_avg_sq")
+
+    def optimizer_state_dict(self, inner) -> dict:
+        """State of the sharded optimiser in the layout ``inner.state_dict()`` would have had with whole fp32
+        parameters (per-parameter ``step`` / ``exp_avg`` / ``exp_avg_sq`` or ``momentum_buffer``), so the file is
+        interchangeable with ``torch.optim``'s.  Collective."""
+        names = self._state_names(inner)
+        sd = inner.state_dict()
+        if self.state0 is None:
+            return sd
+        fulls = [self._gather(t) for t in (self.state0, self.state1) if t is not None]
+        index = {}
+        for gi, g in enumerate(inner.param_groups):
+            for pi, p in enumerate(g["params"]):
+                index[sd["param_groups"][gi]["params"][pi]] = p
+        state = {}
+        for idx, p in index.items():
+            if p not in self._offsets:
+                continue
+            o = self._offsets[p]
+            entry = {} if len(names) == 1 else {"step": torch.tensor(float(self._steps))}
+            for name, full in zip(names, fulls):
+                entry[name] = full[o: o + p.numel()].view(p.shape)
+            state[idx] = entry
+        sd["state"] = state
+        return sd
+
+    @torch.no_grad()
+    def load_optimizer_state_dict(self, inner, sd: dict) -> None:
+        """Inverse of :meth:`optimizer_state_dict`; also accepts a file written by a plain ``torch.optim``
+        optimiser over the same parameters."""
+        names = self._state_names(inner)
+        inner.load_state_dict({"state": {}, "param_groups": sd["param_groups"]})
+        state = sd.get("state", {})
+        if not state:
+            self.state0 = self.state1 = None
+            self._steps = 0
+            return
+        dev = self.master.device
+        fulls = [torch.zeros(self.total, dtype=torch.float32, device=dev) for _ in names]
+        steps = 0
+        for gi, g in enumerate(inner.param_groups):
+            for pi, p in enumerate(g["params"]):
+                entry = state.get(sd["param_groups"][gi]["params"][pi])
+                if entry is None or p not in self._offsets:
+                    continue
+                o = self._offsets[p]
+                for name, full in zip(names, fulls):
+                    v = entry.get(name)
+                    if v is not None:
+                        full[o: o + p.numel()].copy_(v.reshape(-1).to(device=dev, dtype=torch.float32))
+                if "step" in entry:
+                    steps = max(steps, int(float(entry["step"])))
+        shares = [self._share_of(f).clone() for f in fulls]
+        self.state0 = shares[0]
+        self.state1 = shares[1] if len(shares) > 1 else None
+        self._steps = steps if len(names) > 1 else max(self._steps, 1)
+
     # ------------------------------------------------------------------ the step
     def optimizer_step(self, dpopt, closure=None):
         """Tail of ``FSDPOptimizerFastGradientClipping.step`` when this engine owns the parameters."""
@@ -167,33 +339,75 @@ class ShardedDataParallel(nn.Module):
         with phase("dp/optimizer_step"):
             return self._optimizer_step(dpopt, closure)
 
+    def _hyper(self, inner):
+        """(kind, common hyper-parameters, per-group (lr, weight_decay) or None)."""
+        groups = inner.param_groups
+        g0 = groups[0]
+        kind = _KINDS.get(type(inner))
+        if kind is None:
+            raise NotImplementedError(f"the sharded engine implements SGD, Adam and AdamW, not {type(inner).__name__}")
+        for g in groups:
+            if g.get("amsgrad") or g.get("maximize"):
+                raise NotImplementedError("amsgrad / maximize are not implemented in the sharded engine")
+            if isinstance(g["lr"], torch.Tensor):
+                raise NotImplementedError("a tensor learning rate is not implemented in the sharded engine")
+        for g in groups[1:]:
+            if any(g.get(k) != g0.get(k) for k in ("momentum", "dampening", "nesterov", "betas", "eps",
+                                                    "decoupled_weight_decay")):
+                raise NotImplementedError("parameter groups may differ in lr and weight_decay only "
+                                          "(momentum / betas / eps must be common) in the sharded engine")
+        if kind == "adam" and g0.get("decoupled_weight_decay"):
+            kind = "adamw"
+        per_group = [(float(g["lr"]), float(g.get("weight_decay", 0.0))) for g in groups]
+        return kind, g0, (per_group if len(set(per_group)) > 1 else None)
+
+    def _segment_table(self, inner, per_group):
+        """Device table of the ranges of the flat space that share (lr, weight_decay), rebuilt when a value
+        changes (a scheduler moves lr every step; the table is a few hundred bytes)."""
+        key = tuple(per_group)
+        if self._segments is not None and self._segments[0] == key:
+            return self._segments[1]
+        spans = []
+        for g, hp in zip(inner.param_groups, per_group):
+            for p in g["params"]:
+                if p in self._offsets:
+                    spans.append((self._offsets[p], hp))
+        spans.sort(key=lambda t: t[0])
+        rows = []
+        for i, (begin, hp) in enumerate(spans):
+            end = spans[i + 1][0] if i + 1 < len(spans) else self.total
+            if rows and rows[-1][1] == hp:
+                rows[-1][0] = end
+            else:
+                rows.append([end, hp])
+        table = np.zeros(len(rows), dtype=_SEGMENT)
+        for i, (end, hp) in enumerate(rows):
+            table[i] = (end, hp[0], hp[1])
+        dev_table = torch.from_numpy(table.view(np.uint8).copy()).to(self.master.device)
+        self._segments = (key, dev_table)
+        return dev_table
+
+    # Pieces that run beside the weight-gradient GEMMs leave those the SMs: with the reduction done by the switch a few
+    # blocks keep the link busy, plain peer loads need more of them in flight.
+    overlap_step = True
+    overlap_blocks_multicast = 32
+    overlap_blocks_peer = 64
+
     def _optimizer_step(self, dpopt, closure=None):
         from ..ops import _cuda
 
         if closure is not None:
             with torch.enable_grad():
                 closure()
+        had_fresh = any(p._dp_grad_fresh for p in self._params)   # such gradients are zero-filled here, on this stream
         self.finish_grads()
         if dpopt._check_skip_next_step():
             dpopt._is_last_step_skipped = True
             return None
         inner = dpopt.original_optimizer
-        groups = inner.param_groups
-        g0 = groups[0]
-        kind = {torch.optim.SGD: "sgd", torch.optim.Adam: "adam", torch.optim.AdamW: "adamw"}.get(type(inner))
-        if kind is None:
-            raise NotImplementedError(f"the sharded engine implements SGD, Adam and AdamW, not {type(inner).__name__}")
-        keys = ("lr", "weight_decay", "momentum", "dampening", "nesterov", "betas", "eps")
-        for g in groups[1:]:
-            if any(g.get(k) != g0.get(k) for k in keys):
-                raise NotImplementedError("the sharded engine needs identical hyper-parameters in all param groups")
-        if g0.get("amsgrad") or g0.get("maximize"):
-            raise NotImplementedError("amsgrad / maximize are not implemented in the sharded engine")
-        if kind == "adam" and g0.get("decoupled_weight_decay"):
-            kind = "adamw"
+        kind, g0, per_group = self._hyper(inner)
 
         self._steps += 1
-        self._epoch += 1
         t = self._steps
         dev = self.master.device
         h = dict(lr=float(g0["lr"]), momentum=0.0, dampening=0.0, weight_decay=float(g0.get("weight_decay", 0.0)),
@@ -214,12 +428,26 @@ class ShardedDataParallel(nn.Module):
             h.update(beta1=float(b1), beta2=float(b2), eps=float(g0["eps"]), bias_c1=1.0 - float(b1) ** t,
                      bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
             kcode = 2 if kind == "adamw" else 1
+        segments = self._segment_table(inner, per_group) if per_group is not None else None
 
         # per-worker expected batch (times accumulated batches in hooks mode), summed over the workers
         denom = float(dpopt._grad_denominator()) * (self.world if dpopt.loss_reduction == "mean" else 1)
         if dpopt.step_hook:
             dpopt.step_hook(dpopt)
-        seed, offset = _cuda._rng_state(dpopt.generator, dev, self.total * self.tp_world)
+        noise_std, inv_scale = float(dpopt._noise_std()), 1.0 / denom
+        secure = bool(getattr(dpopt, "secure_mode", False)) and noise_std != 0.0
+        if secure:
+            # The noise comes from the optimizer's cryptographic generator through the five-draw rule
+            # (opacus/optimizers/optimizer.py:143-160), not from the kernel's Philox stream: each rank adds it to
+            # its own copy of the gradient on the stripes it owns, so the sum over ranks holds one draw per element.
+            if self.tp_group is not None:
+                raise NotImplementedError("secure_mode with a tensor-parallel group: replicas need one common draw")
+            from .. import ops
+
+            mine = self._flat_grad.tensor.view(self.pieces, self.world, self.stripe)[:, self.rank]
+            mine.add_(ops.gaussian_like(mine, noise_std, generator=dpopt.generator, secure_mode=True))
+            noise_std = 0.0
+        seed, offset = (0, 0) if secure else _cuda._rng_state(dpopt.generator, dev, self.total * self.tp_world)
         noise_shift = 0
         if self.tp_group is not None:
             for p in self._tp_partial:
@@ -231,12 +459,69 @@ class ShardedDataParallel(nn.Module):
             seed, offset = self._tp_seed[0], offset + self._tp_seed[1]
             noise_shift = self.tp_rank * self.total if self.noise_split is not None else 0
         C = _cuda.load()
-        C.sharded_dp_step(self._flat_grad.ptrs, self._flat_param.ptrs, self._flags.ptrs, self.master, self.state0,
-                          self.state1, self.slice_begin, self.slice_len, self.rank,
-                          self.param_dtype == torch.bfloat16, self._epoch, kcode, nesterov, first_step,
-                          h["lr"], h["momentum"], h["dampening"], h["weight_decay"], h["beta1"], h["beta2"], h["eps"],
-                          h["bias_c1"], h["bias_c2_sqrt"], float(dpopt._noise_std()), 1.0 / denom, seed, offset,
-                          self.noise_split if noise_shift else 0, noise_shift)
+        grad_mc = self._flat_grad.mc_ptr if self.multicast else 0
+        param_mc = self._flat_param.mc_ptr if self.multicast else 0
+
+        def launch(first_piece, n_pieces, max_blocks):
+            """One launch (one flag epoch) over this rank's stripes of ``n_pieces`` consecutive pieces."""
+            self._epoch += 1
+            lo, n = first_piece * self.stripe, n_pieces * self.stripe
+            cut = lambda x: None if x is None else x[lo: lo + n]
+            C.sharded_dp_step(self._flat_grad.ptrs, self._flat_param.ptrs, self._flags.ptrs, cut(self.master),
+                              cut(self.state0), cut(self.state1), first_piece * self.piece_len + self.rank * self.stripe,
+                              n, self.rank, self.param_dtype == torch.bfloat16, self._epoch, kcode, nesterov,
+                              first_step, h["lr"], h["momentum"], h["dampening"], h["weight_decay"], h["beta1"],
+                              h["beta2"], h["eps"], h["bias_c1"], h["bias_c2_sqrt"], noise_std, inv_scale, seed,
+                              offset, self.noise_split if noise_shift else 0, noise_shift, grad_mc, param_mc,
+                              segments, max_blocks, self.stripe if n_pieces > 1 else 0, self.piece_len)
+
+        runs = self._ready_runs(had_fresh) if self.overlap_step and not secure else None
+        if runs is None:
+            launch(0, self.pieces, 0)
+            self.last_step_launches = 1
+        else:
+            main = torch.cuda.current_stream(dev)
+            side = self._step_stream
+            if side is None:
+                side = self._step_stream = torch.cuda.Stream(device=dev)
+            side.wait_stream(main)            # what this method queued on the main stream so far
+            cap = self.overlap_blocks_multicast if self.multicast else self.overlap_blocks_peer
+            for k, (first_piece, n_pieces, events) in enumerate(runs):
+                for ev in events:
+                    side.wait_event(ev)
+                with torch.cuda.stream(side):
+                    launch(first_piece, n_pieces, cap if k + 1 < len(runs) else 0)
+            main.wait_stream(side)
+            self.last_step_launches = len(runs)
         dpopt._is_last_step_skipped = False
         self.mark_grads_fresh()
         return None
+
+    def _ready_runs(self, had_fresh: bool):
+        """``[(first_piece, n_pieces, events)]`` in the order in which the ghost-clipping pass completes the pieces
+        (neighbouring pieces that complete together form one run), or None when the step has to be one launch: a
+        single piece, a tensor-parallel group (sums are exchanged first), gradients that did not come from the
+        single-pass controller.  The order depends only on the model's structure: all ranks compute the same."""
+        if self.pieces < 2 or self.tp_group is not None or had_fresh:
+            return None
+        marks = [getattr(p, "_dp_ready", None) for p in self._params]
+        if any(m is None for m in marks):
+            return None
+        latest = [dict() for _ in range(self.pieces)]   # per piece: stream -> (position, event) of its last write
+        for p, (lane, order, event) in zip(self._params, marks):
+            o = self._offsets[p]
+            for k in range(o // self.piece_len, (o + p.numel() - 1) // self.piece_len + 1):
+                if lane not in latest[k] or latest[k][lane][0] < order:
+                    latest[k][lane] = (order, event)
+        keyed = []
+        for k, per_lane in enumerate(latest):
+            when = max((v[0] for v in per_lane.values()), default=-1)
+            keyed.append((when, k, [v[1] for v in per_lane.values()]))
+        keyed.sort(key=lambda t: (t[0], t[1]))
+        runs = []
+        for when, k, events in keyed:
+            if runs and runs[-1][3] == when and runs[-1][0] + runs[-1][1] == k:
+                runs[-1][1] += 1
+            else:
+                runs.append([k, 1, events, when])
+        return [(a, n, ev) for a, n, ev, _ in runs]

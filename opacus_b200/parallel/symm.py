@@ -5,11 +5,17 @@ then holds, for each buffer, the addresses of all ranks' copies mapped into its
 own address space.  Allocation and handle exchange use
 ``torch.distributed._symmetric_memory`` (CUDA virtual memory management plus a
 rendezvous through the process group's store); nothing else of that module is
-used -- every access to peer memory happens inside this package's own kernels
-through plain loads and stores.
+used -- every access to peer memory happens inside this package's own kernels:
+plain loads and stores through the peers' addresses, or ``multimem`` loads and
+stores through the address of the NVLink multicast object that the rendezvous
+binds all copies to when the fabric supports it (NVLS; ``mc_ptr``, 0 otherwise).
+``OPACUS_B200_MULTICAST=0`` makes every buffer report no multicast address, which
+keeps all kernels on plain peer accesses (jobs that test what happens when a rank
+leaves should run that way).
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -17,12 +23,14 @@ import torch.distributed as dist
 
 
 class SymmetricBuffer:
-    """``tensor`` is this rank's copy; ``ptrs[r]`` is rank ``r``'s copy as seen from this GPU."""
+    """``tensor`` is this rank's copy; ``ptrs[r]`` is rank ``r``'s copy as seen from this GPU; ``mc_ptr`` is the
+    multicast address that reaches all copies at once (0: none)."""
 
-    def __init__(self, tensor: torch.Tensor, ptrs: List[int], handle=None):
+    def __init__(self, tensor: torch.Tensor, ptrs: List[int], handle=None, mc_ptr: int = 0):
         self.tensor = tensor
         self.ptrs = ptrs
         self.handle = handle
+        self.mc_ptr = mc_ptr
 
 
 def world_info(group=None):
@@ -44,7 +52,13 @@ def alloc(numel: int, dtype: torch.dtype, device, group=None, zero: bool = True)
         t.zero_()
     ptrs = [int(p) for p in handle.buffer_ptrs]
     assert ptrs[rank] == t.data_ptr(), "symmetric buffer does not start at its allocation"
-    return SymmetricBuffer(t, ptrs, handle)
+    mc = 0
+    if os.environ.get("OPACUS_B200_MULTICAST", "1") != "0":
+        try:
+            mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            mc = 0
+    return SymmetricBuffer(t, ptrs, handle, mc)
 
 
 def available(group=None) -> Optional[str]:

@@ -386,12 +386,17 @@ _row_parallel_rules()
 class TensorParallelDPOptimizer(DPOptimizerFastGradientClipping):
     """Ghost-clipping optimizer for a tensor-parallel group.
 
-    Every rank sees the same batch.  A sharded parameter's noise is drawn
-    locally (the shards are disjoint pieces of one tensor, so the draws are
-    independent coordinates of one Gaussian); a replicated parameter must
-    receive the *same* noise on every rank, so rank 0 of the group draws it and
-    broadcasts.  No gradient collective is needed: sharded gradients are
-    complete locally and replicated ones are identical by construction.
+    Every rank sees the same batch.  The shards of a sharded parameter are
+    disjoint pieces of one tensor, so their noise must be *independent*: each
+    rank draws it from a generator of its own whose seed folds the rank of the
+    group into the seed of the optimizer's generator (ranks that call
+    ``torch.manual_seed(0)`` alike would otherwise hand every shard the same
+    values, and a full weight with noise ``[Z, Z, ..., Z]`` is not the Gaussian
+    mechanism).  A replicated parameter must receive the *same* noise on every
+    rank, so rank 0 of the group draws it from the optimizer's generator and
+    broadcasts; the other ranks do not draw for it at all.  No gradient
+    collective is needed: sharded gradients are complete locally and replicated
+    ones are identical by construction.
     """
 
     _fused_ok = False
@@ -403,19 +408,52 @@ class TensorParallelDPOptimizer(DPOptimizerFastGradientClipping):
                          expected_batch_size=expected_batch_size, loss_reduction=loss_reduction,
                          generator=generator, secure_mode=secure_mode, **kwargs)
         self.process_group = process_group
+        self._shard_generators = {}
+
+    def _shard_generator(self, device):
+        """This rank's generator for the noise of its shards (one per device, created at first use)."""
+        if self.secure_mode:
+            return self.generator          # a CSPRNG seeded from the OS: already independent between ranks
+        gen = self._shard_generators.get(device)
+        if gen is None:
+            if self.generator is not None:
+                base = int(self.generator.initial_seed())
+            elif device.type == "cuda":
+                base = int(torch.cuda.default_generators[device.index].initial_seed())
+            else:
+                base = int(torch.initial_seed())
+            rank = dist.get_rank(self.process_group) if dist.is_initialized() else 0
+            # splitmix-style fold: distinct ranks land on unrelated 63-bit seeds even for base seeds 0, 1, 2, ...
+            z = (base + (rank + 1) * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+            z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+            z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+            gen = torch.Generator(device=device)
+            gen.manual_seed((z ^ (z >> 31)) & 0x7FFFFFFFFFFFFFFF)
+            self._shard_generators[device] = gen
+        return gen
 
     def add_noise(self):
         std = self._noise_std()
         group = self.process_group
         src = dist.get_global_rank(group, 0) if group is not None else 0
+        first = (dist.get_rank(group) if dist.is_initialized() else 0) == 0
         for p in self.params:
             _check_processed_flag(p.summed_grad)
             if getattr(p, "sp_local", False):
                 # each rank clipped and summed its own samples only: complete the sum over the group
                 dist.all_reduce(p.summed_grad, op=dist.ReduceOp.SUM, group=group)
-            noise = _generate_noise(std=std, reference=p.summed_grad, generator=self.generator,
-                                    secure_mode=self.secure_mode)
-            if not getattr(p, "tp_sharded", False) and std != 0:
+            if getattr(p, "tp_sharded", False):
+                noise = _generate_noise(std=std, reference=p.summed_grad,
+                                        generator=self._shard_generator(p.summed_grad.device),
+                                        secure_mode=self.secure_mode)
+            elif std == 0:
+                noise = torch.zeros_like(p.summed_grad)
+            else:
+                if first:
+                    noise = _generate_noise(std=std, reference=p.summed_grad, generator=self.generator,
+                                            secure_mode=self.secure_mode)
+                else:
+                    noise = torch.empty_like(p.summed_grad)
                 dist.broadcast(noise, src, group=group)
             p.grad = (p.summed_grad + noise).view_as(p).to(p.dtype)
             _mark_as_processed(p.summed_grad)

@@ -4,8 +4,12 @@
 
 Every rank trains on its slice of a global batch for a few noise-free steps;
 rank 0 then repeats the run alone on the whole batch (engine with a one-rank
-group) and compares master weights.  A second phase checks that the noise
-added across ranks has the variance of a single global draw.
+group) and compares master weights -- once with the flat space in one piece and
+plain peer loads / stores, once cut into four pieces that are stepped beside
+the weight-gradient GEMMs, through the NVLink multicast address when the fabric
+offers one.  A second phase checks that the noise added across ranks has the
+variance of a single global draw, a third that a run resumed from the gathered
+state dicts continues exactly like the uninterrupted one.
 """
 import datetime
 import os
@@ -27,10 +31,10 @@ from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientCli
 B, T, C = 4, 64, 0.5
 
 
-def build(group, expected, sigma, opt_cls):
+def build(group, expected, sigma, opt_cls, **engine_kw):
     torch.manual_seed(0)
     model = Llama(LlamaConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=256)).cuda()
-    eng = ShardedDataParallel(model, process_group=group)
+    eng = ShardedDataParallel(model, process_group=group, **engine_kw)
     gsm = GradSampleModuleFastGradientClippingFSDP(eng, max_grad_norm=C)
     inner = opt_cls(model.parameters(), lr=1e-2)
     opt = FSDPOptimizerFastGradientClipping(inner, noise_multiplier=sigma, max_grad_norm=C,
@@ -59,9 +63,15 @@ def main():
     ids_all = torch.randint(0, 512, (B * world, T + 1), generator=g).cuda()
     mine = ids_all[rank * B:(rank + 1) * B]
 
-    for opt_cls in (torch.optim.AdamW, torch.optim.SGD):
-        eng, gsm, opt, crit = build(None, B, 0.0, opt_cls)
+    used_multicast = False
+    for opt_cls, engine_kw in ((torch.optim.AdamW, dict(step_pieces=1, multicast=False)),
+                               (torch.optim.AdamW, dict(step_pieces=4)),
+                               (torch.optim.SGD, dict(step_pieces=4))):
+        eng, gsm, opt, crit = build(None, B, 0.0, opt_cls, **engine_kw)
         run(gsm, opt, crit, mine, 3)
+        used_multicast = used_multicast or eng.multicast
+        if engine_kw.get("step_pieces") == 4:
+            assert eng.last_step_launches > 1, "the step did not run in pieces"
         got = eng.full_precision_state_dict()
         # every rank must also hold identical compute weights
         flat = eng._flat_param.tensor.float()
@@ -89,7 +99,29 @@ def main():
     if rank == 0 and world > 1:
         corr = (pieces[0] * pieces[1]).mean().item() / (std * std)
         assert abs(corr) < 0.02, corr
-        print(f"sharded check ok on {world} GPUs (noise std {std:.2f}, cross-rank corr {corr:.4f})")
+        print(f"sharded check ok on {world} GPUs (noise std {std:.2f}, cross-rank corr {corr:.4f}, "
+              f"multicast {'used' if used_multicast else 'not available'})")
+    dist.barrier()
+
+    # resume: 2 steps, gather the state, load it into a fresh engine, 2 more steps == 4 steps in one go
+    eng, gsm, opt, crit = build(None, B, 0.0, torch.optim.AdamW, step_pieces=4)
+    run(gsm, opt, crit, mine, 2)
+    saved = {"module": {k: v.clone() for k, v in eng.state_dict().items()}, "optimizer": opt.state_dict()}
+    run(gsm, opt, crit, mine, 2)
+    want = eng.full_precision_state_dict()
+    eng2, gsm2, opt2, crit2 = build(None, B, 0.0, torch.optim.AdamW, step_pieces=2)     # another layout on purpose
+    with torch.no_grad():
+        for p in eng2.module.parameters():
+            p.add_(1.0)                      # the start must come from the file, not from the seed
+    eng2.load_state_dict(saved["module"])
+    opt2.load_state_dict(saved["optimizer"])
+    run(gsm2, opt2, crit2, mine, 2)
+    got = eng2.full_precision_state_dict()
+    for k in want:
+        err = ((got[k] - want[k]).norm() / (want[k].norm() + 1e-12)).item()
+        assert err < 1e-4, ("resume", k, err)
+    if rank == 0:
+        print("sharded resume ok")
     dist.barrier()
     dist.destroy_process_group()
 

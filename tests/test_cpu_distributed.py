@@ -153,6 +153,43 @@ def _tp_job(rank, world):
     return results
 
 
+def _tp_noise_job(rank, world):
+    """Both ranks seed alike (what every example does); a wide layer so that correlations are measurable."""
+    from opacus_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, TensorParallelDPOptimizer
+
+    torch.manual_seed(0)
+    full = _TPNet(nn.Linear(12, 256), nn.Linear(256, 12))
+    net = _TPNet(ColumnParallelLinear.from_linear(full.col), RowParallelLinear.from_linear(full.row))
+    torch.manual_seed(0)
+    opt = TensorParallelDPOptimizer(torch.optim.SGD(net.parameters(), lr=1.0), noise_multiplier=2.0,
+                                    max_grad_norm=0.5, expected_batch_size=1, loss_reduction="sum")
+    out = {}
+    for step in range(2):
+        for p in net.parameters():
+            p.summed_grad = torch.zeros_like(p)
+        opt.add_noise()
+        out[step] = {n: p.grad.detach().clone() for n, p in net.named_parameters()}
+    return out
+
+
+def test_tensor_parallel_noise_is_independent_between_shards_and_equal_on_replicas():
+    got = _run(_tp_noise_job)
+    std = 2.0 * 0.5
+    for step in range(2):
+        a, b = got[0][step], got[1][step]
+        for name in ("col.weight", "row.weight"):          # shards: same shape on both ranks, different noise
+            za, zb = a[name].flatten(), b[name].flatten()
+            assert za.numel() >= 1536
+            assert abs(float(za.std()) - std) < 0.1 * std and abs(float(zb.std()) - std) < 0.1 * std
+            corr = float((za * zb).mean() / (za.std() * zb.std()))
+            assert abs(corr) < 5.0 / za.numel() ** 0.5, (name, corr)
+        for name in ("ln.weight", "ln.bias", "row.bias"):  # replicas: the same bits everywhere
+            assert torch.equal(a[name], b[name]), name
+            assert float(a[name].abs().sum()) > 0
+    # a shard's noise also differs from step to step
+    assert not torch.equal(got[0][0]["col.weight"], got[0][1]["col.weight"])
+
+
 def test_tensor_parallel_ghost_matches_unsharded():
     from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
     from opacus_b200.optimizers import DPOptimizerFastGradientClipping

@@ -88,6 +88,22 @@ def test_norm_sq_weighted_sum_clip(dtype):
     assert torch.allclose(ops.weighted_sum(big, c[:4]).float(), _ref.weighted_sum(big.float(), c[:4]), rtol=2e-2, atol=2e-2)
 
 
+def test_clip_factor_does_not_fail_open_on_nan():
+    """A NaN squared norm (unfinished or aborted producer) must not come out as factor 1 = "unclipped"."""
+    n2 = torch.tensor([4.0, float("nan"), 0.0, -1e-9, float("inf")], device=_dev())
+    got = ops.clip_factor(n2, 1.0)
+    want = _ref.clip_factor(n2.cpu(), 1.0)
+    assert torch.isnan(got[1]) and torch.isnan(want[1])
+    keep = torch.tensor([0, 2, 3, 4])
+    assert torch.allclose(got.cpu()[keep], want[keep], rtol=1e-6)
+    assert got[4] == 0 and got[0] < 0.5001
+    from opacus_b200.parallel import symm
+
+    red = symm.PeerNormReducer(torch.device("cuda", 0), capacity=16)
+    _, clip = red(n2, None, 1.0)
+    assert torch.isnan(clip[1]) and torch.allclose(clip.cpu()[keep], want[keep], rtol=1e-6)
+
+
 @pytest.mark.parametrize("kind", ["layer", "rms", "group", "instance"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_norm_layer_grads(kind, dtype):

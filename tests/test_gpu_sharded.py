@@ -115,6 +115,173 @@ def test_sharded_engine_noise_and_virtual_steps(pg):
     assert g1.abs().sum() > 0
 
 
+def test_piecewise_step_equals_single_launch(pg):
+    """The flat space cut into pieces (stepped on a side stream beside the clipped-sum GEMMs) gives the weights of
+    the one-launch step, noise included: the draw of an element depends on its index only."""
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 129), device="cuda")
+    results = []
+    for pieces in (1, 5):
+        eng = ShardedDataParallel(_model(), step_pieces=pieces)
+        gen = torch.Generator(device="cuda").manual_seed(11)
+        from opacus_b200 import PrivacyEngine
+
+        opt = torch.optim.AdamW(eng.module.parameters(), lr=1e-2)
+        dl = DataLoader(TensorDataset(torch.zeros(32, 1)), batch_size=4)
+        m, opt, crit, _ = PrivacyEngine(accountant="rdp").make_private(
+            module=eng, optimizer=opt, criterion=nn.CrossEntropyLoss(), data_loader=dl, noise_multiplier=1.0,
+            max_grad_norm=0.5, grad_sample_mode="ghost_fsdp", poisson_sampling=False, noise_generator=gen)
+        for _ in range(3):
+            _step(m, opt, crit, ids)
+        torch.cuda.synchronize()
+        assert (eng.last_step_launches == 1) == (pieces == 1)
+        results.append(eng.full_precision_state_dict())
+    for k in results[0]:
+        a, b = results[0][k], results[1][k]
+        assert ((a - b).norm() / (a.norm() + 1e-12)).item() < 1e-4, k
+
+
+def test_engine_param_groups_with_own_lr_and_weight_decay(pg):
+    """Two parameter groups (decay / no decay, different learning rates) against torch.optim.AdamW on fp32 copies
+    fed with the engine's own clipped sums."""
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 65), device="cuda")
+    model = _model()
+    eng = ShardedDataParallel(model)
+    decay = [p for n, p in model.named_parameters() if p.dim() >= 2]
+    no_decay = [p for n, p in model.named_parameters() if p.dim() < 2]
+    groups = [{"params": decay, "weight_decay": 0.1, "lr": 1e-2}, {"params": no_decay, "weight_decay": 0.0, "lr": 3e-2}]
+    from opacus_b200 import PrivacyEngine
+
+    opt = torch.optim.AdamW(groups)
+    dl = DataLoader(TensorDataset(torch.zeros(32, 1)), batch_size=4)
+    m, opt, crit, _ = PrivacyEngine(accountant="rdp").make_private(
+        module=eng, optimizer=opt, criterion=nn.CrossEntropyLoss(), data_loader=dl, noise_multiplier=0.0,
+        max_grad_norm=0.5, grad_sample_mode="ghost_fsdp", poisson_sampling=False)
+    start = eng.full_precision_state_dict()
+    names = {id(p): n for n, p in model.named_parameters()}
+    shadow = {n: nn.Parameter(v.clone()) for n, v in start.items()}
+    ref = torch.optim.AdamW([{"params": [shadow[names[id(p)]] for p in decay], "weight_decay": 0.1, "lr": 1e-2},
+                             {"params": [shadow[names[id(p)]] for p in no_decay], "weight_decay": 0.0, "lr": 3e-2}])
+    for _ in range(2):
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = m(ids[:, :-1])
+        crit(logits.float().flatten(0, 1), ids[:, 1:].reshape(-1), shape=(4, 64)).backward()
+        torch.cuda.synchronize()
+        for n, p in model.named_parameters():          # the sums the step is about to consume
+            shadow[n].grad = p._dp_grad_out.detach().clone() / 4
+        opt.step()
+        ref.step()
+    got = eng.full_precision_state_dict()
+    for n in got:
+        assert torch.allclose(got[n], shadow[n].detach(), rtol=1e-4, atol=1e-6), (n, (got[n] - shadow[n]).abs().max())
+
+
+def test_engine_checkpoint_resume(pg, tmp_path):
+    """k steps, save_checkpoint, fresh engine, load_checkpoint, k steps == 2k steps in one go; the optimiser file has
+    torch.optim's layout; loading weights through the engine is not undone by the next step."""
+    from opacus_b200 import PrivacyEngine
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 65), device="cuda")
+
+    def fresh(shift=0.0):
+        model = _model()
+        if shift:
+            with torch.no_grad():
+                for p in model.parameters():
+                    p.add_(shift)
+        eng = ShardedDataParallel(model)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+        dl = DataLoader(TensorDataset(torch.zeros(32, 1)), batch_size=4)
+        pe = PrivacyEngine(accountant="rdp")
+        m, opt, crit, _ = pe.make_private(module=eng, optimizer=opt, criterion=nn.CrossEntropyLoss(), data_loader=dl,
+                                          noise_multiplier=0.0, max_grad_norm=0.5, grad_sample_mode="ghost_fsdp",
+                                          poisson_sampling=False)
+        return pe, eng, m, opt, crit
+
+    def steps(m, opt, crit, n):
+        for _ in range(n):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = m(ids[:, :-1])
+            crit(logits.float().flatten(0, 1), ids[:, 1:].reshape(-1), shape=(4, 64)).backward()
+            opt.step()
+
+    pe, eng, m, opt, crit = fresh()
+    steps(m, opt, crit, 2)
+    path = str(tmp_path / "ckpt.pt")
+    pe.save_checkpoint(path=path, module=m, optimizer=opt)
+    steps(m, opt, crit, 2)
+    want = eng.full_precision_state_dict()
+
+    saved = torch.load(path, weights_only=False)
+    osd = saved["optimizer_state_dict"]
+    assert set(osd) == {"state", "param_groups"} and len(osd["state"]) == len(list(eng.module.parameters()))
+    first = osd["state"][0]
+    assert set(first) == {"step", "exp_avg", "exp_avg_sq"} and float(first["step"]) == 2.0
+    assert first["exp_avg"].dtype == torch.float32 and first["exp_avg"].shape == next(eng.module.parameters()).shape
+    assert all(v.dtype == torch.float32 for k, v in saved["module_state_dict"].items() if v.is_floating_point())
+
+    pe2, eng2, m2, opt2, crit2 = fresh(shift=0.5)
+    pe2.load_checkpoint(path=path, module=m2, optimizer=opt2)
+    steps(m2, opt2, crit2, 2)
+    got = eng2.full_precision_state_dict()
+    for k in want:
+        assert ((got[k] - want[k]).norm() / (want[k].norm() + 1e-12)).item() < 1e-4, k
+
+    # weights loaded into the wrapped module directly survive the next step too
+    pe3, eng3, m3, opt3, crit3 = fresh(shift=0.25)
+    eng3.module.load_state_dict({k[len("_module."):]: v for k, v in saved["module_state_dict"].items()})
+    steps(m3, opt3, crit3, 1)
+    moved = eng3.full_precision_state_dict()
+    k0 = next(iter(moved))
+    assert (moved[k0] - saved["module_state_dict"]["_module." + k0].cuda()).abs().max() < 0.1
+
+
+def test_engine_state_loads_a_torch_optim_file(pg):
+    """An optimiser file written by plain torch.optim over the same parameters loads into the engine."""
+    from opacus_b200.optimizers import FSDPOptimizerFastGradientClipping
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    plain = _model()
+    topt = torch.optim.AdamW(plain.parameters(), lr=1e-2)
+    for p in plain.parameters():
+        p.grad = torch.randn_like(p)
+    topt.step()
+    file = topt.state_dict()
+    model = _model()
+    eng = ShardedDataParallel(model)
+    dpo = FSDPOptimizerFastGradientClipping(torch.optim.AdamW(model.parameters(), lr=5e-3), noise_multiplier=0.0,
+                                            max_grad_norm=1.0, expected_batch_size=4, engine=eng)
+    dpo.load_state_dict(file)
+    assert eng._steps == 1 and dpo.param_groups[0]["lr"] == 1e-2
+    back = dpo.state_dict()
+    for idx, entry in file["state"].items():
+        assert torch.equal(back["state"][idx]["exp_avg"], entry["exp_avg"].float())
+        assert torch.equal(back["state"][idx]["exp_avg_sq"], entry["exp_avg_sq"].float())
+
+
+def test_engine_secure_mode_noise_comes_from_the_optimizer_generator(pg):
+    """With secure_mode the engine adds host-generated noise (five-draw rule) to the stripes it owns and runs the
+    kernel without its own draw: the update then has the std of one draw of sigma * C."""
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 65), device="cuda")
+    eng = ShardedDataParallel(_model(), step_pieces=3)
+    before = eng.master.clone()
+    m, opt, crit, _ = _private(eng, "ghost_fsdp", 100.0, torch.optim.SGD)
+    opt.secure_mode = True
+    opt.generator = torch.Generator(device="cuda").manual_seed(3)
+    _step(m, opt, crit, ids)
+    torch.cuda.synchronize()
+    delta = (eng.master - before) / 1e-2 * 4
+    assert abs(delta.std().item() - 100.0 * 0.5) / 50.0 < 0.05
+
+
 def test_engine_serves_hooks_mode_data_parallel(pg):
     """DistributedDPOptimizer on top of the engine (fp32 compute weights) equals the plain DPOptimizer."""
     import copy

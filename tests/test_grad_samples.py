@@ -207,6 +207,13 @@ def test_accumulation_list_and_poisson_guard():
         m(torch.randn(4, 3)).sum().backward()
 
 
+def test_clip_factor_propagates_nan_on_cpu():
+    from opacus_b200 import ops
+
+    c = ops.clip_factor(torch.tensor([4.0, float("nan"), 0.0]), 1.0)
+    assert torch.isnan(c[1]) and abs(float(c[0]) - 0.5) < 1e-5 and float(c[2]) == 1.0
+
+
 def test_buffers_rejected():
     with pytest.raises(NotImplementedError):
         GradSampleModule(nn.BatchNorm1d(3))
