@@ -150,7 +150,8 @@ def build_ours(args, rank, world):
     from opacus_b200 import PrivacyEngine
     from opacus_b200.distributed import DifferentiallyPrivateDistributedDataParallel as DPDDP
 
-    model, cfg = make_model(args, tie=not args.untied, plain=args.plain_model)
+    plain = getattr(args, "plain_model", False)
+    model, cfg = make_model(args, tie=not getattr(args, "untied", False), plain=plain)
     module = model
     mode = "ghost"
     if args.engine == "sharded":
@@ -165,7 +166,7 @@ def build_ours(args, rank, world):
     ds = TensorDataset(torch.zeros(n_data, 1, dtype=torch.long))     # only its length matters (sample rate)
     dl = DataLoader(ds, batch_size=args.batch * world)
     engine = PrivacyEngine(accountant="rdp")
-    fused_ce = args.ce == "fused" and not args.plain_model
+    fused_ce = args.ce == "fused" and not plain
     if fused_ce:
         from opacus_b200.layers import FusedCrossEntropyLoss
 
@@ -347,7 +348,7 @@ def main():
                 "layers": cfg.n_layers, "d_model": cfg.d_model, "vocab": cfg.vocab_size,
                 "tied_embeddings": cfg.tie_embeddings,
                 "model_definition": "stock PyTorch (baseline/llama_plain.py)" if (args.impl == "reference" or
-                                                                                  args.plain_model)
+                                                                                  getattr(args, "plain_model", False))
                 else "opacus_b200.models.Llama (fused RoPE / SwiGLU / add+RMSNorm / cross entropy)",
                 "global_batch": args.batch * world, "seq_len": args.seq,
                 "parallelism": ("single" if world == 1 else f"dp{world}") + f" ({mode})",

@@ -50,6 +50,11 @@ int dpk_tied_cross_norm(const int64_t* ids, const void* g_e, const void* a_h, co
 // y[r, :] = bf16(x[r, :] * c[r / rows_per_sample] * scale)
 int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, int64_t rows, int64_t cols,
                    int64_t rows_per_sample, float scale, cudaStream_t stream);
+// fp32 x [rows, cols] (rows = samples * T) -> bf16 y [samples, 3, T, cols]: planes (hi, hi, lo) of x * c[sample] * scale,
+// or (hi, lo, hi) when `right`, with hi = bf16(v), lo = bf16(v - hi).  A left and a right operand stacked like this
+// along the contraction axis give the fp32 product on the bf16 tensor cores up to a relative 2^-16.
+int dpk_split3_rows(const float* x, const float* c, void* y_bf16, int64_t rows, int64_t cols, int64_t T, float scale,
+                    int right, cudaStream_t stream);
 // c[n] = min(1, C / (sqrt(max(norm_sq[n], 0)) + 1e-6))
 int dpk_clip_factor(const float* norm_sq, float* c, int64_t B, float max_grad_norm, cudaStream_t stream);
 // out[n] (+)= sum_j x[n, j]^2    (x: fp32 / bf16 / fp16 by elem_kind 0/1/2)
@@ -66,6 +71,12 @@ int dpk_outer_norm_sq(const void* a, const void* g, int elem_kind, int64_t B, in
 // stats_scratch: 2 * B * rows floats of scratch (per-row mean and reciprocal std).
 int dpk_norm_lastdim_grad(int kind, const void* x, const void* g, int elem_kind, int64_t B, int64_t rows, int64_t d,
                           float eps, float* stats_scratch, float* gw, float* gb, cudaStream_t stream);
+// The same gradients plus their squared norms n2w[n] = ||gw[n]||^2, n2b[n] = ||gb[n]||^2 (+= when accumulate) in
+// ONE launch.  gw / gb ([B, d], gb may be NULL) and tickets ([B] words) must be zero on entry.  Covers d % 8 == 0,
+// d <= 4096 (d <= 2048 with gb) and 16-byte aligned x / g; returns cudaErrorNotSupported otherwise.
+int dpk_norm_lastdim_psg_fused(int kind, const void* x, const void* g, int elem_kind, int64_t B, int64_t rows,
+                               int64_t d, float eps, float* gw, float* gb, float* n2w, float* n2b, int accumulate,
+                               unsigned int* tickets, cudaStream_t stream);
 // kind 2 = GroupNorm / InstanceNorm on [B, C, S] with `groups` groups; gw/gb: [B, C] fp32.
 int dpk_norm_channel_grad(const void* x, const void* g, int elem_kind, int64_t B, int64_t C, int64_t S, int groups,
                           float eps, float* gw, float* gb, cudaStream_t stream);

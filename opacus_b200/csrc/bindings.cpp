@@ -267,6 +267,25 @@ at::Tensor scale_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t rows_pe
   return y;
 }
 
+// x fp32 [rows, cols] -> bf16 [rows / T, 3 * T, cols] (see dpk_split3_rows)
+at::Tensor split3_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t T, double scale, bool right) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kFloat, "x must be fp32 [rows, cols]");
+  TORCH_CHECK(T > 0 && x.size(0) % T == 0 && x.size(1) % 8 == 0, "rows must be a multiple of T and cols of 8");
+  at::Tensor y = at::empty({x.size(0) / T, 3 * T, x.size(1)}, x.options().dtype(at::kBFloat16));
+  const float* cp = nullptr;
+  if (c.has_value()) {
+    TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kFloat && c->is_contiguous() && c->numel() == x.size(0) / T,
+                "c must be fp32 CUDA, one value per sample");
+    cp = c->data_ptr<float>();
+  }
+  check(dpk_split3_rows(x.data_ptr<float>(), cp, y.data_ptr(), x.size(0), x.size(1), T, (float)scale, right ? 1 : 0,
+                        stream()),
+        "split3_rows");
+  return y;
+}
+
 at::Tensor clip_factor(at::Tensor n2, double C) {
   c10::cuda::CUDAGuard guard(n2.device());
   need_cuda_contig(n2, "norm_sq");
@@ -286,13 +305,20 @@ at::Tensor row_norm_sq(at::Tensor x) {
   return out;
 }
 
-at::Tensor weighted_sum(at::Tensor x, at::Tensor c) {
+at::Tensor weighted_sum(at::Tensor x, at::Tensor c, c10::optional<at::Tensor> dest) {
   c10::cuda::CUDAGuard guard(x.device());
   need_cuda_contig(x, "x");
   need_cuda_contig(c, "c");
   TORCH_CHECK(c.scalar_type() == at::kFloat && c.numel() == x.size(0), "c must be fp32 [B]");
   const int64_t B = x.size(0), cols = x.numel() / B;
-  at::Tensor out = at::empty({cols}, x.options().dtype(at::kFloat));
+  at::Tensor out;
+  if (dest.has_value()) {             // overwritten in place
+    TORCH_CHECK(dest->is_cuda() && dest->scalar_type() == at::kFloat && dest->is_contiguous() && dest->numel() == cols,
+                "dest must be a contiguous fp32 CUDA tensor with one element per column");
+    out = *dest;
+  } else {
+    out = at::empty({cols}, x.options().dtype(at::kFloat));
+  }
   check(dpk_weighted_sum(x.data_ptr(), elem_kind(x), c.data_ptr<float>(), B, cols, out.data_ptr<float>(), stream()),
         "weighted_sum");
   return out;
@@ -333,6 +359,33 @@ std::vector<at::Tensor> norm_lastdim_grad(int64_t kind, at::Tensor x, at::Tensor
                               want_b ? gb.data_ptr<float>() : nullptr, stream()),
         "norm_lastdim_grad");
   return {gw, gb};
+}
+
+// One launch: {gw [B, d], gb [B, d] or undefined, n2w [B], n2b [B] or undefined}; an empty vector when the shape is
+// outside what the fused kernel covers (the caller then uses norm_lastdim_grad + row_norm_sq).
+std::vector<at::Tensor> norm_lastdim_psg(int64_t kind, at::Tensor x, at::Tensor g, int64_t d, double eps, bool want_b) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_cuda_contig(x, "x");
+  need_cuda_contig(g, "g");
+  TORCH_CHECK(x.scalar_type() == g.scalar_type() && x.numel() == g.numel(), "x and g must match");
+  const int64_t B = x.size(0), rows = x.numel() / B / d;
+  if ((d & 7) || d > 4096 || (want_b && d > 2048) || B > 65535 || B == 0 || rows == 0) return {};
+  const int64_t per = B * d;
+  at::Tensor buf = at::zeros({per * (want_b ? 2 : 1) + B * (want_b ? 3 : 2)}, x.options().dtype(at::kFloat));
+  float* base = buf.data_ptr<float>();
+  at::Tensor gw = buf.narrow(0, 0, per).view({B, d});
+  at::Tensor gb = want_b ? buf.narrow(0, per, per).view({B, d}) : at::Tensor();
+  const int64_t tail = per * (want_b ? 2 : 1);
+  at::Tensor n2w = buf.narrow(0, tail, B);
+  at::Tensor n2b = want_b ? buf.narrow(0, tail + B, B) : at::Tensor();
+  unsigned int* tickets = reinterpret_cast<unsigned int*>(base + tail + B * (want_b ? 2 : 1));
+  const int rc = dpk_norm_lastdim_psg_fused((int)kind, x.data_ptr(), g.data_ptr(), elem_kind(x), B, rows, d, (float)eps,
+                                            gw.data_ptr<float>(), want_b ? gb.data_ptr<float>() : nullptr,
+                                            n2w.data_ptr<float>(), want_b ? n2b.data_ptr<float>() : nullptr, 0, tickets,
+                                            stream());
+  if (rc == cudaErrorNotSupported) return {};
+  check(rc, "norm_lastdim_psg");
+  return {gw, gb, n2w, n2b};
 }
 
 std::vector<at::Tensor> norm_channel_grad(at::Tensor x, at::Tensor g, int64_t groups, double eps, bool want_w,
@@ -655,14 +708,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tied_cross_norm", &tied_cross_norm);
   m.def("scale_rows", &scale_rows);
   m.def("clip_factor", &clip_factor);
+  m.def("split3_rows", &split3_rows);
   m.def("row_norm_sq", &row_norm_sq);
-  m.def("weighted_sum", &weighted_sum);
+  m.def("weighted_sum", &weighted_sum, py::arg("x"), py::arg("c"), py::arg("dest") = py::none());
   m.def("outer_norm_sq", &outer_norm_sq);
   m.def("norm_lastdim_grad", &norm_lastdim_grad);
   m.def("norm_channel_grad", &norm_channel_grad);
+  m.def("norm_lastdim_psg", &norm_lastdim_psg);
   m.def("embedding_scatter", &embedding_scatter);
   m.def("fused_dp_step", &fused_dp_step);
-  m.def("sharded_dp_step", &sharded_dp_step);
+  m.def("sharded_dp_step", &sharded_dp_step, py::arg("grad_ptrs"), py::arg("param_ptrs"), py::arg("flag_ptrs"),
+        py::arg("master"), py::arg("state0"), py::arg("state1"), py::arg("slice_begin"), py::arg("slice_len"),
+        py::arg("rank"), py::arg("param_bf16"), py::arg("epoch"), py::arg("kind"), py::arg("nesterov"),
+        py::arg("first_step"), py::arg("lr"), py::arg("momentum"), py::arg("dampening"), py::arg("weight_decay"),
+        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("bias_c1"), py::arg("bias_c2_sqrt"),
+        py::arg("noise_std"), py::arg("inv_scale"), py::arg("seed"), py::arg("offset"), py::arg("noise_split"),
+        py::arg("noise_shift"), py::arg("grad_mc") = 0, py::arg("param_mc") = 0, py::arg("segments") = py::none(),
+        py::arg("max_blocks") = 0, py::arg("stripe_len") = 0, py::arg("stripe_stride") = 0);
   m.def("norm_allreduce_clip", &norm_allreduce_clip);
   m.def("step_segment_size", []() { return (int64_t)sizeof(DpkStepSegment); });
   m.def("tp_gemm", &tp_gemm);

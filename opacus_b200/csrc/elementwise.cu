@@ -85,6 +85,41 @@ __global__ void scale_rows_kernel(const void* x, const float* c, __nv_bfloat16* 
   }
 }
 
+// ---------------------------------------------------------------- fp32 operand as three bf16 planes
+// v = x * c * scale is written as hi = bf16(v), lo = bf16(v - hi): hi + lo carries 16 mantissa bits.  For a product
+// of two such operands the tensor cores run on the planes (hi, hi, lo) of the left one against (hi, lo, hi) of the
+// right one, stacked along the contraction axis: hi*hi + hi*lo + lo*hi, i.e. the fp32 product up to the
+// lo*lo term (relative 2^-16).  Row r of sample b = r / T lands in rows (3 b + j) * T + r % T, j = 0, 1, 2.
+__global__ void split3_rows_kernel(const float* x, const float* c, __nv_bfloat16* y, int64_t rows, int64_t cols,
+                                   int64_t T, float scale, int right) {
+  const int64_t vec_per_row = cols >> 3;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int64_t col = (i - r * vec_per_row) << 3;
+    const int64_t b = r / T, t = r - b * T;
+    const float f = (c ? c[b] : 1.f) * scale;
+    float v[8];
+    load8<0>(x, i << 3, v);
+    uint4 hi, lo;
+    uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+    uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float v0 = v[2 * q] * f, v1 = v[2 * q + 1] * f;
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+      const __nv_bfloat162 l = __floats2bfloat162_rn(v0 - __bfloat162float(h.x), v1 - __bfloat162float(h.y));
+      hw[q] = *reinterpret_cast<const uint32_t*>(&h);
+      lw[q] = *reinterpret_cast<const uint32_t*>(&l);
+    }
+    __nv_bfloat16* base = y + ((b * 3) * T + t) * cols + col;
+    const int64_t plane = T * cols;
+    *reinterpret_cast<uint4*>(base) = hi;
+    *reinterpret_cast<uint4*>(base + plane) = right ? lo : hi;
+    *reinterpret_cast<uint4*>(base + 2 * plane) = right ? hi : lo;
+  }
+}
+
 // ---------------------------------------------------------------- clip factor
 // A NaN norm (a producer that marked unfinished work, an overflow upstream) gives a NaN factor, never 1:
 // clipping must not fail open.  fmaxf / fminf would drop the NaN.
@@ -210,6 +245,116 @@ __global__ void lastdim_grad_kernel(const void* x, const void* g, const float2* 
   }
   if (gw) atomicAdd(gw + n * d + j, aw);
   if (gb) atomicAdd(gb + n * d + j, ab);
+}
+
+// ---------------------------------------------------------------- LayerNorm / RMSNorm, one launch
+// Per-sample affine gradients AND their squared norms in one kernel (d a multiple of 8, d <= 256 * NV * ... see
+// the launcher).  grid = (chunks, B); a block takes rows [r0, r1) of sample n, one row per warp at a time:
+//   pass 1 over the row gives mean / rstd, pass 2 (the row is in L1 by then) accumulates xhat * g (and g) in
+//   registers, lane l holding columns 8 * (l + 32 * i) .. + 8;
+// the warps of a block are added in shared memory, blocks are added with atomics into gw / gb (zeroed by the
+// launcher), and the last block of a sample to finish (a ticket counter per sample) squares and sums the complete
+// [d] vectors: n2w[n] / n2b[n] (+= when accumulate).  The counter is left at zero again.
+template <int KIND, int NV, bool BIAS>
+__global__ void __launch_bounds__(256)
+lastdim_psg_fused_kernel(int norm_kind, const void* x, const void* g, int64_t rows, int64_t d, int64_t rows_per_block,
+                         float eps, float* gw, float* gb, float* n2w, float* n2b, int accumulate,
+                         unsigned int* tickets) {
+  extern __shared__ float red[];               // [d] (+ [d] with BIAS)
+  __shared__ float sh[32];
+  __shared__ unsigned int sh_last;
+  const int64_t n = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r0 = blockIdx.x * rows_per_block;
+  const int64_t r1 = min(rows, r0 + rows_per_block);
+  float aw[NV][8];
+  float ab[BIAS ? NV : 1][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { aw[i][q] = 0.f; if (BIAS) ab[i][q] = 0.f; }
+  for (int64_t r = r0 + warp; r < r1; r += 8) {
+    const int64_t base = (n * rows + r) * d;
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t col = (int64_t)(lane + 32 * i) * 8;
+      if (col < d) {
+        float v[8];
+        load8<KIND>(x, base + col, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { s += v[q]; ss = fmaf(v[q], v[q], ss); }
+      }
+    }
+    s = warp_sum(s); ss = warp_sum(ss);
+    float mean = 0.f, rstd;
+    if (norm_kind == 0) {
+      mean = s / d;
+      rstd = rsqrtf(fmaxf(ss / d - mean * mean, 0.f) + eps);
+    } else {
+      rstd = rsqrtf(ss / d + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int64_t col = (int64_t)(lane + 32 * i) * 8;
+      if (col < d) {
+        float xv[8], gv[8];
+        load8<KIND>(x, base + col, xv);
+        load8<KIND>(g, base + col, gv);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          aw[i][q] = fmaf((xv[q] - mean) * rstd, gv[q], aw[i][q]);
+          if (BIAS) ab[i][q] += gv[q];
+        }
+      }
+    }
+  }
+  // warps -> block (one warp at a time adds its registers into shared memory), block -> global
+  for (int64_t j = threadIdx.x; j < (BIAS ? 2 * d : d); j += blockDim.x) red[j] = 0.f;
+  __syncthreads();
+  for (int w = 0; w < 8; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int64_t col = (int64_t)(lane + 32 * i) * 8;
+        if (col < d) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            red[col + q] += aw[i][q];
+            if (BIAS) red[d + col + q] += ab[i][q];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int64_t j = threadIdx.x; j < d; j += blockDim.x) {
+    atomicAdd(gw + n * d + j, red[j]);
+    if (BIAS) atomicAdd(gb + n * d + j, red[d + j]);
+  }
+  // the last block of this sample finishes the norms
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(tickets + n, 1u);
+    sh_last = (t == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  float qw = 0.f, qb = 0.f;
+  for (int64_t j = threadIdx.x; j < d; j += blockDim.x) {
+    const float v = __ldcg(gw + n * d + j);
+    qw = fmaf(v, v, qw);
+    if (BIAS) { const float u = __ldcg(gb + n * d + j); qb = fmaf(u, u, qb); }
+  }
+  qw = block_sum(qw, sh);
+  if (BIAS) qb = block_sum(qb, sh);
+  if (threadIdx.x == 0) {
+    if (n2w) n2w[n] = (accumulate ? n2w[n] : 0.f) + qw;
+    if (BIAS && n2b) n2b[n] = (accumulate ? n2b[n] : 0.f) + qb;
+    tickets[n] = 0;
+  }
 }
 
 // ---------------------------------------------------------------- GroupNorm / InstanceNorm
@@ -450,6 +595,14 @@ extern "C" int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void
   return cudaGetLastError();
 }
 
+extern "C" int dpk_split3_rows(const float* x, const float* c, void* y, int64_t rows, int64_t cols, int64_t T,
+                               float scale, int right, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) || T <= 0 || rows % T) return cudaErrorInvalidValue;
+  const int grid = grid_for(rows * (cols >> 3), 256, num_sms() * 16);
+  split3_rows_kernel<<<grid, 256, 0, stream>>>(x, c, (__nv_bfloat16*)y, rows, cols, T, scale, right);
+  return cudaGetLastError();
+}
+
 extern "C" int dpk_clip_factor(const float* n2, float* c, int64_t B, float C, cudaStream_t stream) {
   if (B <= 0) return 0;
   clip_factor_kernel<<<(int)((B + 255) / 256), 256, 0, stream>>>(n2, c, B, C);
@@ -514,6 +667,39 @@ extern "C" int dpk_norm_lastdim_grad(int norm_kind, const void* x, const void* g
   if (B > 65535 || gy > 65535) return cudaErrorInvalidValue;
   dim3 grid(gx, gy, (unsigned)B);
   DISPATCH_KIND(kind, (lastdim_grad_kernel<KIND><<<grid, 128, 0, stream>>>(x, g, stats, rows, d, rpb, gw, gb)));
+  return cudaGetLastError();
+}
+
+// One-launch form: gw (and gb) [B, d] and tickets [B] must be ZERO on entry (one allocation, one memset by the
+// caller).  Returns cudaErrorNotSupported when the shape is outside what the kernel covers
+// (d % 8, d > 4096, or d > 2048 with a bias) so that the caller can take the two-kernel path.
+extern "C" int dpk_norm_lastdim_psg_fused(int norm_kind, const void* x, const void* g, int kind, int64_t B,
+                                          int64_t rows, int64_t d, float eps, float* gw, float* gb, float* n2w,
+                                          float* n2b, int accumulate, unsigned int* tickets, cudaStream_t stream) {
+  if (B <= 0 || rows <= 0 || d <= 0) return 0;
+  const bool bias = gb != nullptr;
+  if ((d & 7) || d > 4096 || (bias && d > 2048) || B > 65535 || gw == nullptr) return cudaErrorNotSupported;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) & 15) != 0) return cudaErrorNotSupported;
+  int64_t chunks = ((int64_t)num_sms() * 3 + B - 1) / B;
+  if (chunks > (rows + 7) / 8) chunks = (rows + 7) / 8;
+  if (chunks < 1) chunks = 1;
+  const int64_t rpb = (rows + chunks - 1) / chunks;
+  chunks = (rows + rpb - 1) / rpb;
+  dim3 grid((unsigned)chunks, (unsigned)B);
+  const size_t smem = sizeof(float) * d * (bias ? 2 : 1);
+  const int nv = (int)((d + 255) / 256);
+#define PSG_LAUNCH(NV_, BIAS_)                                                                                   \
+  DISPATCH_KIND(kind, (lastdim_psg_fused_kernel<KIND, NV_, BIAS_><<<grid, 256, smem, stream>>>(                  \
+                          norm_kind, x, g, rows, d, rpb, eps, gw, gb, n2w, n2b, accumulate, tickets)))
+  if (bias) {
+    if (nv <= 1) { PSG_LAUNCH(1, true); } else if (nv <= 2) { PSG_LAUNCH(2, true); }
+    else if (nv <= 4) { PSG_LAUNCH(4, true); } else { PSG_LAUNCH(8, true); }
+  } else {
+    if (nv <= 1) { PSG_LAUNCH(1, false); } else if (nv <= 2) { PSG_LAUNCH(2, false); }
+    else if (nv <= 4) { PSG_LAUNCH(4, false); } else if (nv <= 8) { PSG_LAUNCH(8, false); }
+    else { PSG_LAUNCH(16, false); }
+  }
+#undef PSG_LAUNCH
   return cudaGetLastError();
 }
 

@@ -61,7 +61,11 @@ __device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
                : "memory");
 }
 
-__global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep p) {
+// WORLD > 0: the number of ranks is a compile-time constant and all peer loads of a vector are issued before the
+// first one is used (one NVLink round trip per vector instead of one per rank); WORLD == 0: any number of ranks,
+// one rank after the other.
+template <int WORLD>
+__global__ void __launch_bounds__(kShThreads, WORLD == 1 ? 2 : 1) sharded_step_kernel(DpkShardedStep p) {
   __shared__ uint32_t sh_ok;
   volatile uint32_t* my_flags = p.flags[p.rank];
 
@@ -102,11 +106,22 @@ __global__ void __launch_bounds__(kShThreads) sharded_step_kernel(DpkShardedStep
       if (p.grad_mc != nullptr) {
         const float4 a = multimem_ld_reduce_f32x4(p.grad_mc + gi), b = multimem_ld_reduce_f32x4(p.grad_mc + gi + 4);
         g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+      } else if constexpr (WORLD > 0) {
+        float4 a[WORLD], b[WORLD];
+#pragma unroll
+        for (int q = 0; q < WORLD; ++q) {         // rank order is fixed (0, 1, ...): the sum has the same bits on
+          const float4* src = reinterpret_cast<const float4*>(p.grad[q] + gi);   // whichever rank owns the element
+          a[q] = __ldcg(src);
+          b[q] = __ldcg(src + 1);
+        }
+#pragma unroll
+        for (int q = 0; q < WORLD; ++q) {
+          g[0] += a[q].x; g[1] += a[q].y; g[2] += a[q].z; g[3] += a[q].w;
+          g[4] += b[q].x; g[5] += b[q].y; g[6] += b[q].z; g[7] += b[q].w;
+        }
       } else {
         for (int q = 0; q < p.world; ++q) {
-          int r = p.rank + q;
-          if (r >= p.world) r -= p.world;
-          const float4* src = reinterpret_cast<const float4*>(p.grad[r] + gi);
+          const float4* src = reinterpret_cast<const float4*>(p.grad[q] + gi);
           const float4 a = __ldcg(src), b = __ldcg(src + 1);
           g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
         }
@@ -244,17 +259,26 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
   if ((reinterpret_cast<uintptr_t>(p.grad_mc) & 15) || (reinterpret_cast<uintptr_t>(p.param_mc) & 15))
     return cudaErrorInvalidValue;
   // every block spins on flags, so all of them must be resident at once: as many per SM as fit
-  static int per_sm_cached = 0;
-  if (per_sm_cached == 0) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sharded_step_kernel, kShThreads, 0) != cudaSuccess || n < 1) n = 1;
-    per_sm_cached = n > 4 ? 4 : n;
+  void (*kernel)(DpkShardedStep) = sharded_step_kernel<0>;
+  int slot = 0;
+  switch (p.world) {
+    case 1: kernel = sharded_step_kernel<1>; slot = 1; break;
+    case 2: kernel = sharded_step_kernel<2>; slot = 2; break;
+    case 4: kernel = sharded_step_kernel<4>; slot = 3; break;
+    case 8: kernel = sharded_step_kernel<8>; slot = 4; break;
+    default: break;
   }
-  int grid = num_sms() * per_sm_cached;
+  static int per_sm_cached[5] = {0, 0, 0, 0, 0};
+  if (per_sm_cached[slot] == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kShThreads, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm_cached[slot] = n > 4 ? 4 : n;
+  }
+  int grid = num_sms() * per_sm_cached[slot];
   if (p.max_blocks > 0 && p.max_blocks < grid) grid = p.max_blocks;   // a piece beside GEMMs leaves them the SMs
   const int64_t nvec = p.slice_len >> 3;
   const int64_t need = (nvec + kShThreads - 1) / kShThreads;
   if (need < grid) grid = need < 1 ? 1 : (int)need;
-  sharded_step_kernel<<<grid, kShThreads, 0, stream>>>(p);
+  kernel<<<grid, kShThreads, 0, stream>>>(p);
   return cudaGetLastError();
 }

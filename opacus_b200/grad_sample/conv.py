@@ -88,7 +88,7 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
 
 def _implicit_geometry(layer, x, backprops):
     """Geometry tuple when the implicit-unfold CUDA kernel covers this call, else None."""
-    if not (x.is_cuda and backprops.dtype == torch.bfloat16) or _base_type(layer) is nn.Conv3d:
+    if not x.is_cuda or backprops.dtype not in (torch.bfloat16, torch.float32) or _base_type(layer) is nn.Conv3d:
         return None
     from ..ops import _cuda
 
@@ -97,8 +97,8 @@ def _implicit_geometry(layer, x, backprops):
 
 @register_norm_sq_sampler(_CONVS)
 def compute_conv_norm_sq(layer, activations, backprops, g_scale: float = 1.0, total=None):
-    """Squared per-sample gradient norms of a conv layer.  On the GPU (bf16, ungrouped,
-    1-d/2-d) the per-sample gradient tiles are formed in tensor memory and squared
+    """Squared per-sample gradient norms of a conv layer.  On the GPU (bf16, 1-d/2-d, up to 8
+    groups) the per-sample gradient tiles are formed in tensor memory and squared
     there, never written; otherwise the gradients are instantiated
     (``opacus/grad_sample/grad_sample_module_fast_gradient_clipping.py:226-250``)."""
     x = activations[0]

@@ -67,13 +67,30 @@ def create_norm_sample(*, param: torch.Tensor, grad_sample: torch.Tensor, max_ba
         param._norm_sample = ops.grad_sample_norm_sq(grad_sample).sqrt().to(grad_sample.dtype)
 
 
+class _OnStream:
+    """``with torch.cuda.stream(s)`` without its device look-ups: the caller knows both streams."""
+
+    __slots__ = ("side", "back")
+
+    def __init__(self, side, back):
+        self.side, self.back = side, back
+
+    def __enter__(self):
+        torch.cuda.set_stream(self.side)
+
+    def __exit__(self, *exc):
+        torch.cuda.set_stream(self.back)
+        return False
+
+
 class _Site:
     """What the single-pass path keeps about one layer call until the clip
     factors are known."""
 
-    __slots__ = ("module", "inputs", "backprops", "g_scale", "kept_grad_samples")
+    __slots__ = ("module", "inputs", "backprops", "g_scale", "kept_grad_samples", "params")
 
     def __init__(self, module, inputs, backprops, g_scale, kept_grad_samples=None):
+        self.params = None
         self.module = module
         self.inputs = inputs
         self.backprops = backprops
@@ -162,6 +179,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         self._norm_sq_total: Optional[torch.Tensor] = None
         self._batch_len: Optional[int] = None
         self._uses: Dict[nn.Parameter, List[_Site]] = {}
+        self._backward_stream = None
 
     # ---- single pass: forward side
     def _active(self, module) -> bool:
@@ -210,12 +228,15 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         with phase("dp/norm"):
             if self.overlap_norms and grad_out.is_cuda:
                 # norm kernels run beside the rest of the backward pass; finish_single_pass() joins the streams
-                main = torch.cuda.current_stream(grad_out.device)
+                main = self._backward_stream
+                if main is None or main.device != grad_out.device:
+                    # the stream autograd runs this device's backward on, looked up once per pass
+                    main = self._backward_stream = torch.cuda.current_stream(grad_out.device)
                 side = getattr(self, "_norm_stream", None)
                 if side is None or side.device != grad_out.device:
                     side = self._norm_stream = torch.cuda.Stream(device=grad_out.device)
                 side.wait_stream(main)
-                with torch.cuda.stream(side):
+                with _OnStream(side, main):
                     self._capture_site(module, grad_out)
                 self._norm_stream_busy = True
             else:
@@ -296,7 +317,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             if not p.requires_grad:
                 continue
             self._add_norm_sq(p, self._align_norm(p, v.float()))
-        for _, p in trainable_parameters(module):
+        for p in self._site_params(site):
             self._uses.setdefault(p, []).append(site)
             p._forward_counter -= uses
         if len(module.activations) == 0 and hasattr(module, "max_batch_len"):
@@ -415,7 +436,7 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                 lane = next((lane_of[i] for i in ps if i in lane_of), len(lane_of) % len(lanes))
                 for i in ps:
                     lane_of[i] = lane
-                with torch.cuda.stream(lanes[lane]):
+                with _OnStream(lanes[lane], main):
                     self._write_site(site, coef)
                     if any(getattr(p, "_dp_grad_out", None) is not None for p in owned):
                         # an engine that owns the gradient storage may step the parts of the flat space written so
@@ -431,10 +452,9 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
                 lanes[0].wait_stream(st)
 
     def _site_params(self, site):
-        cached = site.module.__dict__.get("_dp_own_params")
-        if cached is None:
-            cached = site.module.__dict__["_dp_own_params"] = [p for _, p in trainable_parameters(site.module)]
-        return cached
+        if site.params is None:
+            site.params = [p for _, p in trainable_parameters(site.module)]
+        return site.params
 
     def _sites_by_parameter(self):
         """The captured sites in backward order, except that the later uses of a shared parameter follow its first
@@ -458,7 +478,15 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         mtype = self._get_module_type(site.module)
         c = self._site_coef(site, coef)
         if site.kept_grad_samples is not None:
-            grads = {p: ops.weighted_sum(gs, c[: gs.shape[0]]) for p, gs in site.kept_grad_samples.items()}
+            grads = {}
+            for p, gs in site.kept_grad_samples.items():
+                dst = getattr(p, "_dp_grad_out", None)
+                if dst is not None and getattr(p, "_dp_grad_fresh", True) and gs.shape[1:] == p.shape:
+                    # engine-owned gradient storage that holds nothing yet: the sum is written there directly
+                    grads[p] = ops.weighted_sum(gs, c[: gs.shape[0]], out=dst)
+                    p._dp_grad_fresh = False
+                else:
+                    grads[p] = ops.weighted_sum(gs, c[: gs.shape[0]])
         elif mtype in self.WGRAD_SAMPLERS and not self.force_functorch:
             grads = self.WGRAD_SAMPLERS[mtype](site.module, site.inputs, site.backprops, c, site.g_scale)
         else:

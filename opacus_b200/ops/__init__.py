@@ -151,10 +151,15 @@ def grad_sample_norm_sq(gs):
     return _ref.grad_sample_norm_sq(gs)
 
 
-def weighted_sum(gs, c):
+def weighted_sum(gs, c, out=None):
+    """``sum_n c[n] gs[n]``; ``out`` (optional, shape of one sample's gradient) is overwritten with it."""
     if _on_gpu(gs) and _kernel_dtype(gs) and gs.shape[0] > 0:
-        return _k().weighted_sum(gs, c)
-    return _ref.weighted_sum(gs, c)
+        return _k().weighted_sum(gs, c, out=out)
+    res = _ref.weighted_sum(gs, c)
+    if out is not None:
+        out.copy_(res.view(out.shape))
+        return out
+    return res
 
 
 gaussian_like = _ref.gaussian_like

@@ -1,11 +1,13 @@
 """CUDA side of :mod:`opacus_b200.ops`: shape/dtype preparation around the
 kernels bound in ``opacus_b200._C`` (sources in ``opacus_b200/csrc``).
 
-The tensor-core kernels take bf16 operands and accumulate in fp32.  fp32 inputs
-are routed to them only where a bf16 rounding of the operands is acceptable by
-construction (never for fp32 models: those use the fp32 statements in
-:mod:`._ref` for the GEMM-shaped ops, while the bandwidth-bound kernels are
-dtype generic).
+The tensor-core kernels take bf16 operands and accumulate in fp32.  fp32 models
+use the same kernels through a three-plane split of each operand
+(``split3_rows``: ``v = hi + lo`` with both parts bf16; the planes
+``(hi, hi, lo)`` of one operand are contracted against ``(hi, lo, hi)`` of the
+other, stacked along the contraction axis), which reproduces the fp32 product up
+to a relative 2^-16 -- tighter than a tf32 product (2^-10) at three bf16
+products' cost.  The bandwidth-bound kernels are dtype generic.
 """
 from __future__ import annotations
 
@@ -79,7 +81,8 @@ def _scratch_for(device, floats: int) -> torch.Tensor:
     """Work space of the ghost-norm kernel, one buffer per (device, stream): calls on different streams never
     share it, and a buffer is only ever replaced from the stream that uses it (allocated while that stream is
     current, so the caching allocator orders its reuse after the kernels already queued there)."""
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = (device, torch._C._cuda_getCurrentRawStream(device.index if device.index is not None
+                                                      else torch.cuda.current_device()))
     buf = _scratch.get(key)
     if buf is None or buf.numel() < floats:
         buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
@@ -102,6 +105,16 @@ def _tensor_core_ok(*ts) -> bool:
     return all(t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0 for t in ts)
 
 
+def _split_pair(g3, a3, c=None, g_scale: float = 1.0):
+    """fp32 ``[B, T, d]`` operands of a product contracted over T -> bf16 ``[B, 3T, d]`` planes, left and right
+    form (the clip factors ``c`` and ``g_scale`` go onto the left one)."""
+    C = load()
+    B, T = g3.shape[0], g3.shape[1]
+    gl = C.split3_rows(g3.float().reshape(B * T, g3.shape[-1]).contiguous(), c, T, float(g_scale), False)
+    ar = C.split3_rows(a3.float().reshape(B * T, a3.shape[-1]).contiguous(), None, T, 1.0, True)
+    return gl, ar
+
+
 # ----------------------------------------------------------------------- Linear
 def linear_grad_sample(a, g):
     """``[B, d_out, d_in]`` per-sample gradients (dtype of ``g``) by the batched
@@ -111,12 +124,17 @@ def linear_grad_sample(a, g):
     a3, g3 = _bt(a), _bt(g)
     B, T, d_in = a3.shape
     d_out = g3.shape[-1]
-    if not (g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0):
+    if d_in % 8 or d_out % 8 or g3.dtype not in (torch.bfloat16, torch.float32):
         return _ref.linear_grad_sample(a, g)
     C = load()
-    out = torch.empty(B, d_out, d_in, dtype=torch.bfloat16, device=g.device)
     n2 = torch.zeros(B, dtype=torch.float32, device=g.device)
-    C.wgrad_tn_ex(g3.contiguous(), _bf16(a3), out, 0.0, n2, 0, 0, 0)
+    if g3.dtype == torch.float32:
+        gl, ar = _split_pair(g3, a3)
+        out = torch.empty(B, d_out, d_in, dtype=torch.float32, device=g.device)
+        C.wgrad_tn_ex(gl, ar, out, 0.0, n2, 0, 0, 0)
+    else:
+        out = torch.empty(B, d_out, d_in, dtype=torch.bfloat16, device=g.device)
+        C.wgrad_tn_ex(g3.contiguous(), _bf16(a3), out, 0.0, n2, 0, 0, 0)
     out._dp_norm_sq = n2
     return out
 
@@ -172,6 +190,22 @@ def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0
                 total.add_(b)
             return None, None
         return w, b
+    if g3.dtype == torch.float32 and d_in % 8 == 0 and d_out % 8 == 0:
+        # fp32 model: each sample's gradient is formed tile by tile in TMEM from the split operands, only its norm is kept
+        w = b = None
+        if want_weight:
+            gl, ar = _split_pair(g3, a3)
+            n2 = torch.zeros(B, dtype=torch.float32, device=g.device)
+            C.wgrad_tn_ex(gl, ar, None, 0.0, n2, 0, 0, 0)
+            w = n2 * s2 if s2 != 1.0 else n2
+        if want_bias:
+            b = g3.sum(dim=1).square().sum(dim=1) * s2
+        if acc:
+            for t in (w, b):
+                if t is not None:
+                    total.add_(t)
+            return None, None
+        return w, b
     w, b = _ref.linear_norm_sq(a, g, want_weight, want_bias, g_scale)
     if acc:
         for t in (w, b):
@@ -187,7 +221,7 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
     a3, g3 = _bt(a), _bt(g)
     B, T, d_in = a3.shape
     d_out = g3.shape[-1]
-    if not (g3.dtype == torch.bfloat16 and d_in % 8 == 0 and d_out % 8 == 0):
+    if d_in % 8 or d_out % 8 or g3.dtype not in (torch.bfloat16, torch.float32):
         w, b = _ref.linear_weighted_grad(a, g, c, g_scale, want_bias)
         if out is not None:
             out.add_(w) if accumulate else out.copy_(w)
@@ -197,8 +231,11 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
     c = c.float().contiguous()
     a2 = a3.reshape(B * T, d_in)
     g2 = g3.reshape(B * T, d_out)
+    if g3.dtype == torch.float32:
+        gl, ar = _split_pair(g3, a3, c, g_scale)
+        g_op, a_op = gl.view(3 * B * T, d_out), ar.view(3 * B * T, d_in)
     # the clip factors go onto the narrower operand (fewer bytes to rewrite)
-    if d_in <= d_out and a2.dtype in (torch.float32, torch.bfloat16):
+    elif d_in <= d_out and a2.dtype in (torch.float32, torch.bfloat16):
         a_op = C.scale_rows(a2.contiguous(), c, T, float(g_scale))
         g_op = g2.contiguous()
     else:
@@ -274,6 +311,18 @@ def norm_affine_grad_sample(kind, x, g, eps, normalized_ndim, num_groups, want_w
     x, g = x.contiguous(), g.contiguous()
     if kind in ("layer", "rms"):
         d = x.shape[-1]
+        if want_weight:
+            # one launch: statistics, per-sample gradients and their squared norms (kept on the results as
+            # ``_dp_norm_sq`` so that clipping does not read them again)
+            res = C.norm_lastdim_psg(0 if kind == "layer" else 1, x, g, d, float(eps),
+                                     bool(want_bias) and kind == "layer")
+            if res:
+                gw, gb, n2w, n2b = res
+                gw._dp_norm_sq = n2w
+                if want_bias and kind == "layer":
+                    gb._dp_norm_sq = n2b
+                    return gw, gb
+                return gw, None
         gw, gb = C.norm_lastdim_grad(0 if kind == "layer" else 1, x, g, d, float(eps), bool(want_weight),
                                      bool(want_bias) and kind == "layer")
     else:
@@ -303,7 +352,14 @@ def _dense_order(t):
     return order if t.permute(order).is_contiguous() else None
 
 
-def weighted_sum(gs, c):
+def weighted_sum(gs, c, out=None):
+    """``out``: optional fp32 contiguous destination with the shape of one sample's gradient (overwritten)."""
+    if out is not None and gs.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous():
+        load().weighted_sum(gs, c.float().contiguous(), out.view(-1))
+        return out
+    if out is not None:
+        out.copy_(weighted_sum(gs, c).view(out.shape))
+        return out
     order = _dense_order(gs)
     if order is not None:
         # a permuted view of a dense buffer (e.g. the channels-last conv gradient): sum in storage
@@ -319,26 +375,33 @@ def weighted_sum(gs, c):
 
 
 # ------------------------------------------------------------------- convolution (implicit unfold)
+_MAX_GROUP_CALLS = 8
+
+
 def conv_geometry(layer, x, backprops):
-    """``(kh, kw, sh, sw, ph, pw, dh, dw)`` when the implicit-unfold kernel covers this
-    Conv1d / Conv2d call, else None (grouped, 3-d, string or non-zero-mode padding,
-    channel counts that are not multiples of 8, non-bf16 data)."""
+    """A plan ``(kh, kw, sh, sw, ph, pw, dh, dw, groups, prepad, fp32)`` when the implicit-unfold kernel covers this
+    Conv1d / Conv2d call, else None.  Covered: bf16 and fp32 data (fp32 as three bf16 passes over split operands),
+    any channel counts (padded with zero channels to multiples of 8), up to 8 groups (one call per group; more,
+    e.g. depthwise, stay on the batched-GEMM path), zero padding including ``"same"`` with an odd total (the input is
+    padded explicitly first).  Not covered: 3-d convolutions, non-zero padding modes, strides above 8."""
     nsp = x.dim() - 2
-    if nsp not in (1, 2) or backprops.dtype != torch.bfloat16 or not x.is_cuda:
+    if nsp not in (1, 2) or backprops.dtype not in (torch.bfloat16, torch.float32) or not x.is_cuda:
         return None
-    if layer.groups != 1 or getattr(layer, "padding_mode", "zeros") != "zeros":
-        return None
-    if layer.in_channels % 8 or layer.out_channels % 8:
+    if getattr(layer, "padding_mode", "zeros") != "zeros" or layer.groups > _MAX_GROUP_CALLS:
         return None
     pad = layer.padding
+    prepad = None
     if isinstance(pad, str):
         if pad == "valid":
             pad = (0,) * nsp
         else:
             tot = [d * (k - 1) for k, d in zip(layer.kernel_size, layer.dilation)]
             if any(t % 2 for t in tot):
-                return None
-            pad = tuple(t // 2 for t in tot)
+                # F.pad order: last axis first, (left, right) per axis; the extra element goes to the right
+                prepad = [v for t in reversed(tot) for v in (t // 2, t - t // 2)]
+                pad = (0,) * nsp
+            else:
+                pad = tuple(t // 2 for t in tot)
     k, s, d = tuple(layer.kernel_size), tuple(layer.stride), tuple(layer.dilation)
     if nsp == 1:
         k, s, pad, d = (1,) + k, (1,) + s, (0,) + tuple(pad), (1,) + d
@@ -348,7 +411,8 @@ def conv_geometry(layer, x, backprops):
         bw *= 2
     if max(s) > 8 or bw * s[1] > 256 or (64 // bw) * s[0] > 256:
         return None
-    return (k[0], k[1], s[0], s[1], int(pad[0]), int(pad[1]), d[0], d[1])
+    return (k[0], k[1], s[0], s[1], int(pad[0]), int(pad[1]), d[0], d[1], int(layer.groups), prepad,
+            backprops.dtype == torch.float32)
 
 
 def _nhwc(t):
@@ -358,18 +422,65 @@ def _nhwc(t):
     return t.permute(0, 2, 3, 1).contiguous()
 
 
-def conv_grad_sample(x, backprops, geom, want_out=True, norm_total=None):
-    """Per-sample conv weight gradients ``[B, O, C, kh, kw]`` (a permuted view of the
-    kernel's ``[B, O, kh, kw, C]`` output, ``_dp_norm_sq`` attached) and/or their
-    squared norms added into ``norm_total``."""
-    xh, gh = _nhwc(x.to(torch.bfloat16)), _nhwc(backprops)
-    B, O, C = xh.shape[0], gh.shape[3], xh.shape[3]
+def _pad8(t):
+    """Zero channels up to a multiple of 8 on the last axis (TMA rows are 16-byte multiples)."""
+    extra = -t.shape[-1] % 8
+    return torch.nn.functional.pad(t, (0, extra)) if extra else t
+
+
+def _conv_passes(xh, gh, fp32):
+    """Operand pairs whose products add up to the convolution gradient: one bf16 pair, or for fp32 data the three
+    pairs (hi, hi), (hi, lo), (lo, hi) of the split operands."""
+    if not fp32:
+        return [(xh.to(torch.bfloat16), gh.to(torch.bfloat16))]
+    xf, gf = xh.float(), gh.float()
+    x_hi, g_hi = xf.bfloat16(), gf.bfloat16()
+    x_lo, g_lo = (xf - x_hi.float()).bfloat16(), (gf - g_hi.float()).bfloat16()
+    return [(x_hi, g_hi), (x_lo, g_hi), (x_hi, g_lo)]
+
+
+def _conv_groups(x, backprops, plan):
+    """Channels-last operands of every group, channels padded to multiples of 8: [(xh, gh, C_g, O_g)]."""
+    groups, prepad = plan[8], plan[9]
+    if prepad is not None:
+        x = torch.nn.functional.pad(x, prepad)
+    xh, gh = _nhwc(x), _nhwc(backprops)
+    cg, og = xh.shape[3] // groups, gh.shape[3] // groups
+    out = []
+    for i in range(groups):
+        xs = xh if groups == 1 else xh[..., i * cg:(i + 1) * cg]
+        gs = gh if groups == 1 else gh[..., i * og:(i + 1) * og]
+        out.append((_pad8(xs).contiguous(), _pad8(gs).contiguous(), cg, og))
+    return out
+
+
+def conv_grad_sample(x, backprops, plan, want_out=True, norm_total=None):
+    """Per-sample conv weight gradients ``[B, O, C/groups, kh, kw]`` (a permuted view of the kernel's
+    channels-last output, ``_dp_norm_sq`` attached) and/or their squared norms added into ``norm_total``."""
+    geom, fp32 = list(plan[:8]), plan[10]
     kh, kw = geom[0], geom[1]
-    out = torch.empty((B, O, kh, kw, C), dtype=torch.bfloat16, device=x.device) if want_out else None
+    B = x.shape[0]
+    C = load()
     norm = norm_total if norm_total is not None else torch.zeros(B, dtype=torch.float32, device=x.device)
-    load().conv_psg(xh, gh, list(geom), False, out, 0.0, norm)
-    if out is None:
+    simple = not fp32
+    pieces = []
+    for xh, gh, cg, og in _conv_groups(x, backprops, plan):
+        Op, Cp = gh.shape[3], xh.shape[3]
+        passes = _conv_passes(xh, gh, fp32)
+        if simple:
+            out = torch.empty((B, Op, kh, kw, Cp), dtype=torch.bfloat16, device=x.device) if want_out else None
+            C.conv_psg(passes[0][0], passes[0][1], geom, False, out, 0.0, norm)
+        else:
+            # the norm of a sum of three products needs the sum: the gradients are formed in fp32, then squared
+            out = torch.empty((B, Op, kh, kw, Cp), dtype=torch.float32, device=x.device)
+            for i, (xs, gs) in enumerate(passes):
+                C.conv_psg(xs, gs, geom, False, out, 0.0 if i == 0 else 1.0, None)
+            norm.add_(C.row_norm_sq(out))
+        if out is not None and want_out:
+            pieces.append(out[:, :og, :, :, :cg])
+    if not want_out:
         return norm
+    out = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=1)
     gs = out.permute(0, 1, 4, 2, 3)
     if x.dim() == 3:
         gs = gs.squeeze(3)
@@ -378,14 +489,28 @@ def conv_grad_sample(x, backprops, geom, want_out=True, norm_total=None):
     return gs
 
 
-def conv_weighted_grad(x, backprops, coef, geom, g_scale=1.0):
-    """``sum_b coef_b * grad_b`` of a conv weight as one implicit GEMM over all samples' pixels; fp32 ``[O, C, kh, kw]``."""
-    xh, gh = _nhwc(x.to(torch.bfloat16)), _nhwc(backprops)
-    B, OH, OW, O = gh.shape
-    C = xh.shape[3]
-    gsc = load().scale_rows(gh.view(B * OH * OW, O), coef.float().contiguous(), OH * OW, float(g_scale)).view(gh.shape)
-    out = torch.empty((O, geom[0], geom[1], C), dtype=torch.float32, device=x.device)
-    load().conv_psg(xh, gsc, list(geom), True, out, 0.0, None)
+def conv_weighted_grad(x, backprops, coef, plan, g_scale=1.0):
+    """``sum_b coef_b * grad_b`` of a conv weight as one implicit GEMM over all samples' pixels (per group);
+    fp32 ``[O, C/groups, kh, kw]``."""
+    geom, fp32 = list(plan[:8]), plan[10]
+    C = load()
+    B = x.shape[0]
+    shape = (-1,) + (1,) * (backprops.dim() - 1)
+    scaled = backprops * (coef.to(backprops.dtype) * g_scale).reshape(shape) if fp32 else None
+    pieces = []
+    for xh, gh, cg, og in _conv_groups(x, backprops if scaled is None else scaled, plan):
+        _, OH, OW, Op = gh.shape
+        Cp = xh.shape[3]
+        out = torch.empty((Op, geom[0], geom[1], Cp), dtype=torch.float32, device=x.device)
+        if fp32:
+            for i, (xs, gs) in enumerate(_conv_passes(xh, gh, True)):
+                C.conv_psg(xs, gs, geom, True, out, 0.0 if i == 0 else 1.0, None)
+        else:
+            gsc = C.scale_rows(gh.to(torch.bfloat16).view(B * OH * OW, Op), coef.float().contiguous(), OH * OW,
+                               float(g_scale)).view(gh.shape)
+            C.conv_psg(xh.to(torch.bfloat16), gsc, geom, True, out, 0.0, None)
+        pieces.append(out[:og, :, :, :cg])
+    out = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=0)
     w = out.permute(0, 3, 1, 2).contiguous()
     return w.squeeze(2) if x.dim() == 3 else w
 

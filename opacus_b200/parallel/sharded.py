@@ -110,7 +110,7 @@ class ShardedDataParallel(nn.Module):
 
         # ---- pieces and stripes: piece k is [k * piece_len, (k + 1) * piece_len), rank r owns its r-th stripe
         if step_pieces is None:
-            step_pieces = 16 if self.world > 1 else 1
+            step_pieces = int(os.environ.get("OPACUS_B200_STEP_PIECES", "0")) or (16 if self.world > 1 else 1)
             step_pieces = max(1, min(step_pieces, used // (self.world * (1 << 18))))
         self.pieces = int(step_pieces)
         if self.pieces < 1:
@@ -132,6 +132,10 @@ class ShardedDataParallel(nn.Module):
             flag = torch.tensor([1 if self.multicast else 0], device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=process_group)
             self.multicast = bool(flag.item())
+        # the two uses of the multicast address can be chosen separately: the in-switch reduction of the gradient
+        # (multimem.ld_reduce) and the replicated store of the new weights (multimem.st)
+        self.multicast_reduce = os.environ.get("OPACUS_B200_MC_REDUCE", "1") != "0"
+        self.multicast_publish = os.environ.get("OPACUS_B200_MC_PUBLISH", "1") != "0"
 
         # ---- identical start on every rank, then adopt the flat storage
         full = torch.zeros(self.total, dtype=torch.float32, device=dev)
@@ -387,11 +391,13 @@ class ShardedDataParallel(nn.Module):
         self._segments = (key, dev_table)
         return dev_table
 
-    # Pieces that run beside the weight-gradient GEMMs leave those the SMs: with the reduction done by the switch a few
-    # blocks keep the link busy, plain peer loads need more of them in flight.
+    # Pieces that run beside the weight-gradient GEMMs leave those the SMs.
+    # One block per SM fits beside a GEMM CTA (registers and threads; the step kernel uses no shared memory) and the
+    # step is bound by memory and link latency, not by issue slots.
     overlap_step = True
-    overlap_blocks_multicast = 32
-    overlap_blocks_peer = 64
+    overlap_blocks_multicast = 148
+    overlap_blocks_peer = 148
+    single_launch_blocks = 0         # grid cap of the one-launch step (0: whole grid); benchmarks set it
 
     def _optimizer_step(self, dpopt, closure=None):
         from ..ops import _cuda
@@ -447,7 +453,7 @@ class ShardedDataParallel(nn.Module):
             mine = self._flat_grad.tensor.view(self.pieces, self.world, self.stripe)[:, self.rank]
             mine.add_(ops.gaussian_like(mine, noise_std, generator=dpopt.generator, secure_mode=True))
             noise_std = 0.0
-        seed, offset = (0, 0) if secure else _cuda._rng_state(dpopt.generator, dev, self.total * self.tp_world)
+        seed, offset = (0, 0) if secure else _cuda._rng_state(dpopt.generator, dev, self.used * self.tp_world)
         noise_shift = 0
         if self.tp_group is not None:
             for p in self._tp_partial:
@@ -459,8 +465,8 @@ class ShardedDataParallel(nn.Module):
             seed, offset = self._tp_seed[0], offset + self._tp_seed[1]
             noise_shift = self.tp_rank * self.total if self.noise_split is not None else 0
         C = _cuda.load()
-        grad_mc = self._flat_grad.mc_ptr if self.multicast else 0
-        param_mc = self._flat_param.mc_ptr if self.multicast else 0
+        grad_mc = self._flat_grad.mc_ptr if self.multicast and self.multicast_reduce else 0
+        param_mc = self._flat_param.mc_ptr if self.multicast and self.multicast_publish else 0
 
         def launch(first_piece, n_pieces, max_blocks):
             """One launch (one flag epoch) over this rank's stripes of ``n_pieces`` consecutive pieces."""
@@ -477,7 +483,7 @@ class ShardedDataParallel(nn.Module):
 
         runs = self._ready_runs(had_fresh) if self.overlap_step and not secure else None
         if runs is None:
-            launch(0, self.pieces, 0)
+            launch(0, self.pieces, self.single_launch_blocks)
             self.last_step_launches = 1
         else:
             main = torch.cuda.current_stream(dev)
@@ -485,7 +491,8 @@ class ShardedDataParallel(nn.Module):
             if side is None:
                 side = self._step_stream = torch.cuda.Stream(device=dev)
             side.wait_stream(main)            # what this method queued on the main stream so far
-            cap = self.overlap_blocks_multicast if self.multicast else self.overlap_blocks_peer
+            cap = int(os.environ.get("OPACUS_B200_OVERLAP_BLOCKS", "0")) or (
+                self.overlap_blocks_multicast if self.multicast else self.overlap_blocks_peer)
             for k, (first_piece, n_pieces, events) in enumerate(runs):
                 for ev in events:
                     side.wait_event(ev)

@@ -129,6 +129,41 @@ def test_norm_layer_grads(kind, dtype):
         assert torch.allclose(gb.float(), gf.sum((2, 3)), rtol=1e-3, atol=1e-3)
 
 
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("B,T,d", [(8, 1024, 2048), (3, 50, 4096), (2, 7, 264), (1, 1, 8), (4, 33, 100)])
+def test_norm_layer_one_launch_grads_and_norms(kind, B, T, d):
+    """The one-launch LayerNorm / RMSNorm rule: per-sample gradients and their squared norms (attached to the
+    results) against fp32 torch; d = 100 (not a multiple of 8) and LayerNorm at d = 4096 take the two-kernel path."""
+    import torch.nn.functional as F
+
+    torch.manual_seed(1)
+    x = torch.randn(B, T, d, device=_dev()).bfloat16()
+    g = (torch.randn(B, T, d, device=_dev()) * 0.1).bfloat16()
+    for _ in range(2):                                   # twice: the ticket counters must be left clean
+        gw, gb = ops.norm_affine_grad_sample(kind, x, g, eps=1e-5, normalized_ndim=1, want_bias=kind == "layer")
+        xf, gf = x.float(), g.float()
+        xhat = F.layer_norm(xf, (d,), eps=1e-5) if kind == "layer" else F.rms_norm(xf, (d,), eps=1e-5)
+        want_w = (xhat * gf).sum(1)
+        assert torch.allclose(gw.float(), want_w, rtol=2e-3, atol=2e-3)
+        n2 = ops.grad_sample_norm_sq(gw)
+        assert torch.allclose(n2, want_w.pow(2).sum(1), rtol=2e-3), (n2, want_w.pow(2).sum(1))
+        if kind == "layer":
+            assert torch.allclose(gb.float(), gf.sum(1), rtol=2e-3, atol=2e-3)
+            assert torch.allclose(ops.grad_sample_norm_sq(gb), gf.sum(1).pow(2).sum(1), rtol=2e-3)
+    one_launch = d % 8 == 0 and (d <= 2048 or (kind == "rms" and d <= 4096))
+    assert (getattr(gw, "_dp_norm_sq", None) is not None) == one_launch
+    ops._cuda.check_status()
+
+
+def test_weighted_sum_into_destination():
+    gs = torch.randn(6, 40, 24, device=_dev())
+    c = torch.rand(6, device=_dev())
+    dst = torch.full((40, 24), 7.0, device=_dev())
+    out = ops.weighted_sum(gs, c, out=dst)
+    assert out.data_ptr() == dst.data_ptr()
+    assert torch.allclose(dst, _ref.weighted_sum(gs, c), rtol=1e-5, atol=1e-5)
+
+
 def test_embedding_weighted_grad():
     torch.manual_seed(0)
     ids = torch.randint(0, 40, (6, 33), device=_dev())
@@ -320,6 +355,84 @@ def test_conv_implicit_per_sample_grad(cfg):
     sref = (gs.float() * coef[:, None, None, None, None]).sum(0)
     assert s.shape == sref.shape and (s.float() - sref).abs().max() <= 2e-2 * sref.abs().max()
     _cuda.check_status()
+
+
+def _conv_oracle_general(conv, x, g):
+    """fp32 per-sample weight gradients through the layer's own forward (groups, string padding included)."""
+    import copy
+
+    ref = copy.deepcopy(conv).float()
+    out = []
+    for b in range(x.shape[0]):
+        ref.zero_grad()
+        y = ref(x[b:b + 1].float())
+        (gw,) = torch.autograd.grad(y, ref.weight, g[b:b + 1].float())
+        out.append(gw)
+    return torch.stack(out)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [
+    dict(C=3, O=64, H=32, W=32, k=3, s=1, p=1, groups=1, dtype=torch.bfloat16),       # ResNet stem: 3 channels
+    dict(C=1, O=16, H=28, W=28, k=8, s=2, p=3, groups=1, dtype=torch.bfloat16),       # one channel, wide filter
+    dict(C=32, O=64, H=12, W=12, k=3, s=1, p=1, groups=4, dtype=torch.bfloat16),      # grouped
+    dict(C=12, O=20, H=9, W=11, k=3, s=1, p=1, groups=2, dtype=torch.bfloat16),       # grouped, 6 / 10 channels per group
+    dict(C=16, O=32, H=10, W=10, k=(2, 4), s=1, p="same", groups=1, dtype=torch.bfloat16),   # odd padding totals
+    dict(C=64, O=64, H=16, W=16, k=3, s=1, p=1, groups=1, dtype=torch.float32),       # fp32 as three bf16 passes
+    dict(C=3, O=24, H=14, W=14, k=3, s=2, p=1, groups=1, dtype=torch.float32),
+])
+def test_conv_kernel_coverage_beyond_plain_bf16(cfg):
+    """Channel counts that are not multiples of 8, groups, "same" padding with an odd total and fp32 data all run on
+    the implicit-unfold kernel (no unfolded copy) and agree with per-sample autograd."""
+    from opacus_b200.grad_sample.conv import compute_conv_grad_sample, compute_conv_norm_sq, compute_conv_weighted_grad
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    B, dt = 4, cfg["dtype"]
+    conv = torch.nn.Conv2d(cfg["C"], cfg["O"], cfg["k"], stride=cfg["s"], padding=cfg["p"], groups=cfg["groups"],
+                           bias=True).cuda().to(dt)
+    x = torch.randn(B, cfg["C"], cfg["H"], cfg["W"], device="cuda", dtype=dt)
+    g = torch.randn_like(conv(x))
+    assert _cuda.conv_geometry(conv, x, g) is not None
+    ref = _conv_oracle_general(conv, x, g)
+    tol = 1e-2 if dt == torch.bfloat16 else 2e-4
+    out = compute_conv_grad_sample(conv, [x], g)
+    gw = out[conv.weight]
+    assert gw.shape == ref.shape
+    assert (gw.float() - ref).abs().max() <= tol * ref.abs().max()
+    nref = ref.flatten(1).square().sum(1)
+    torch.testing.assert_close(ops.grad_sample_norm_sq(gw), nref, rtol=2e-3 if dt == torch.bfloat16 else 1e-4, atol=0)
+    nsq = compute_conv_norm_sq(conv, [x], g, 2.0)
+    torch.testing.assert_close(nsq[conv.weight], 4.0 * nref, rtol=2e-3 if dt == torch.bfloat16 else 1e-4, atol=0)
+    coef = torch.rand(B, device="cuda")
+    wg = compute_conv_weighted_grad(conv, [x], g, coef, 1.0)
+    wref = (ref * coef[:, None, None, None, None]).sum(0)
+    assert wg[conv.weight].shape == wref.shape
+    assert (wg[conv.weight].float() - wref).abs().max() <= tol * wref.abs().max()
+    _cuda.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,din,dout", [(4, 128, 512, 512), (3, 50, 72, 40), (2, 1024, 256, 128)])
+def test_fp32_linear_rules_run_on_split_bf16_operands(B, T, din, dout):
+    """fp32 activations and gradients: per-sample gradient, ghost norm and clipped sum through the three-plane
+    bf16 split agree with fp32 torch far inside what one bf16 rounding of the operands would give."""
+    torch.manual_seed(0)
+    a = torch.randn(B, T, din, device=_dev())
+    g = torch.randn(B, T, dout, device=_dev()) * 0.1
+    want = torch.bmm(g.double().transpose(1, 2), a.double())
+    gs = ops.linear_grad_sample(a, g)
+    assert gs.dtype == torch.float32 and gs.shape == (B, dout, din)
+    assert _rel(gs.double(), want) < 5e-5
+    assert _rel(gs._dp_norm_sq.double(), want.pow(2).sum(dim=(1, 2))) < 1e-4
+    w, b = ops.linear_norm_sq(a, g, True, True, g_scale=2.0)
+    assert _rel(w.double(), 4.0 * want.pow(2).sum(dim=(1, 2))) < 1e-4
+    assert _rel(b.double(), 4.0 * g.double().sum(1).pow(2).sum(1)) < 1e-4
+    c = torch.rand(B, device=_dev())
+    ws, _ = ops.linear_weighted_grad(a, g, c, g_scale=1.5)
+    wref = (want * (1.5 * c.double())[:, None, None]).sum(0)
+    assert _rel(ws.double(), wref) < 5e-5
+    ops._cuda.check_status()
 
 
 @pytest.mark.gpu
