@@ -64,6 +64,13 @@ __device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
 // WORLD > 0: the number of ranks is a compile-time constant and all peer loads of a vector are issued before the
 // first one is used (one NVLink round trip per vector instead of one per rank); WORLD == 0: any number of ranks,
 // one rank after the other.
+// 8 bytes stored into every rank's copy.
+__device__ __forceinline__ void multimem_st_b64(void* mc_addr, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y))
+               : "memory");
+}
+
 template <int WORLD>
 __global__ void __launch_bounds__(kShThreads, WORLD == 1 ? 2 : 1) sharded_step_kernel(DpkShardedStep p) {
   __shared__ uint32_t sh_ok;
@@ -90,138 +97,137 @@ __global__ void __launch_bounds__(kShThreads, WORLD == 1 ? 2 : 1) sharded_step_k
   const bool go = sh_ok != 0;
 
   // ---------------------------------------------------------------- reduce, noise, update, publish
+  // A thread owns 8 elements per iteration as two groups of 4.  When the range allows it (lengths multiples of
+  // 256) the groups of a warp interleave -- lane l takes elements [4l, 4l + 4) and [128 + 4l, 128 + 4l + 4) of the
+  // warp's 256 -- so that every load and store instruction of a warp covers one contiguous run of whole 32-byte
+  // sectors: a peer read moves a sector over NVLink, and the 16-bytes-per-lane-at-a-32-byte-stride pattern of
+  // "8 consecutive elements per thread" would fetch every remote sector twice.
   if (go) {
     __threadfence_system();          // the peers' gradient stores, published by their flags, before any read here
     DpkStepHyper h = p.h;
     const Philox rng(h.seed);
     const int64_t nvec = p.slice_len >> 3;
+    const bool wide = ((p.slice_len | p.stripe_len) & 255) == 0;
+    const bool has_m = p.state0 != nullptr && (h.kind != 0 || h.momentum != 0.f);
     for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t li = v << 3;                 // index inside the owned share covered by this launch
-      int64_t gi = p.slice_begin + li;           // index in the flat parameter space
-      if (p.stripe_len > 0) {                    // the share is one stripe of every piece: stripes are stripe_stride apart
-        const int64_t k = li / p.stripe_len;
-        gi += k * (p.stripe_stride - p.stripe_len);
+      int64_t li[2], gi[2];            // index inside the owned share covered by this launch / in the flat space
+      li[0] = wide ? ((v >> 5) << 8) + ((v & 31) << 2) : (v << 3);
+      li[1] = li[0] + (wide ? 128 : 4);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        gi[hf] = p.slice_begin + li[hf];
+        if (p.stripe_len > 0)          // the share is one stripe of every piece: stripes are stripe_stride apart
+          gi[hf] += (li[hf] / p.stripe_len) * (p.stripe_stride - p.stripe_len);
       }
-      float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      float4 g[2];
       if (p.grad_mc != nullptr) {
-        const float4 a = multimem_ld_reduce_f32x4(p.grad_mc + gi), b = multimem_ld_reduce_f32x4(p.grad_mc + gi + 4);
-        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+        g[0] = multimem_ld_reduce_f32x4(p.grad_mc + gi[0]);
+        g[1] = multimem_ld_reduce_f32x4(p.grad_mc + gi[1]);
       } else if constexpr (WORLD > 0) {
         float4 a[WORLD], b[WORLD];
 #pragma unroll
         for (int q = 0; q < WORLD; ++q) {         // rank order is fixed (0, 1, ...): the sum has the same bits on
-          const float4* src = reinterpret_cast<const float4*>(p.grad[q] + gi);   // whichever rank owns the element
-          a[q] = __ldcg(src);
-          b[q] = __ldcg(src + 1);
+          a[q] = __ldcg(reinterpret_cast<const float4*>(p.grad[q] + gi[0]));   // whichever rank owns the element
+          b[q] = __ldcg(reinterpret_cast<const float4*>(p.grad[q] + gi[1]));
         }
+        g[0] = a[0]; g[1] = b[0];
 #pragma unroll
-        for (int q = 0; q < WORLD; ++q) {
-          g[0] += a[q].x; g[1] += a[q].y; g[2] += a[q].z; g[3] += a[q].w;
-          g[4] += b[q].x; g[5] += b[q].y; g[6] += b[q].z; g[7] += b[q].w;
+        for (int q = 1; q < WORLD; ++q) {
+          g[0].x += a[q].x; g[0].y += a[q].y; g[0].z += a[q].z; g[0].w += a[q].w;
+          g[1].x += b[q].x; g[1].y += b[q].y; g[1].z += b[q].z; g[1].w += b[q].w;
         }
       } else {
+        g[0] = g[1] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int q = 0; q < p.world; ++q) {
-          const float4* src = reinterpret_cast<const float4*>(p.grad[q] + gi);
-          const float4 a = __ldcg(src), b = __ldcg(src + 1);
-          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+          const float4 a = __ldcg(reinterpret_cast<const float4*>(p.grad[q] + gi[0]));
+          const float4 b = __ldcg(reinterpret_cast<const float4*>(p.grad[q] + gi[1]));
+          g[0].x += a.x; g[0].y += a.y; g[0].z += a.z; g[0].w += a.w;
+          g[1].x += b.x; g[1].y += b.y; g[1].z += b.z; g[1].w += b.w;
         }
       }
-      if (p.nseg > 1) {
-        // first segment whose end lies beyond gi (parameters start on multiples of 64: a vector has one segment)
-        int lo = 0, hi = p.nseg - 1;
-        while (lo < hi) {
-          const int mid = (lo + hi) >> 1;
-          if (__ldg(&p.segs[mid].end) > gi) hi = mid; else lo = mid + 1;
-        }
-        h.lr = __ldg(&p.segs[lo].lr);
-        h.weight_decay = __ldg(&p.segs[lo].weight_decay);
-      }
-      if (h.noise_std != 0.f) {
-        const uint64_t ni = static_cast<uint64_t>(gi >= p.noise_split ? gi + p.noise_shift : gi);
-        const uint4 u0 = rng(ni >> 2, h.offset);
-        const uint4 u1 = rng((ni >> 2) + 1, h.offset);
-        const float2 z0 = box_muller(u0.x, u0.y), z1 = box_muller(u0.z, u0.w);
-        const float2 z2 = box_muller(u1.x, u1.y), z3 = box_muller(u1.z, u1.w);
-        g[0] += z0.x * h.noise_std; g[1] += z0.y * h.noise_std; g[2] += z1.x * h.noise_std; g[3] += z1.y * h.noise_std;
-        g[4] += z2.x * h.noise_std; g[5] += z2.y * h.noise_std; g[6] += z3.x * h.noise_std; g[7] += z3.y * h.noise_std;
-      }
-      float w[8], m[8], s[8];
-      {
-        const float4 a = *reinterpret_cast<const float4*>(p.master + li), b = *reinterpret_cast<const float4*>(p.master + li + 4);
-        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-      }
-      const bool has_m = p.state0 != nullptr && (h.kind != 0 || h.momentum != 0.f);
-      if (has_m) {
-        const float4 a = *reinterpret_cast<const float4*>(p.state0 + li), b = *reinterpret_cast<const float4*>(p.state0 + li + 4);
-        m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
-      }
-      if (h.kind != 0) {
-        const float4 a = *reinterpret_cast<const float4*>(p.state1 + li), b = *reinterpret_cast<const float4*>(p.state1 + li + 4);
-        s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w; s[4] = b.x; s[5] = b.y; s[6] = b.z; s[7] = b.w;
+      float4 w[2], m[2], s[2];
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        w[hf] = *reinterpret_cast<const float4*>(p.master + li[hf]);
+        if (has_m) m[hf] = *reinterpret_cast<const float4*>(p.state0 + li[hf]);
+        if (h.kind != 0) s[hf] = *reinterpret_cast<const float4*>(p.state1 + li[hf]);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float grad = g[j] * h.inv_scale;
-        float pv = w[j];
-        if (h.kind == 0) {
-          if (h.weight_decay != 0.f) grad = fmaf(h.weight_decay, pv, grad);
-          if (h.momentum != 0.f) {
-            const float buf = h.first_step ? grad : fmaf(h.momentum, m[j], (1.f - h.dampening) * grad);
-            m[j] = buf;
-            grad = h.nesterov ? fmaf(h.momentum, buf, grad) : buf;
+      for (int hf = 0; hf < 2; ++hf) {
+        if (p.nseg > 1) {
+          // first segment whose end lies beyond the group (parameters start on multiples of 64: one segment per group)
+          int lo = 0, hi = p.nseg - 1;
+          while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (__ldg(&p.segs[mid].end) > gi[hf]) hi = mid; else lo = mid + 1;
           }
-          pv = fmaf(-h.lr, grad, pv);
-        } else {
-          if (h.weight_decay != 0.f) {
-            if (h.kind == 2) pv *= (1.f - h.lr * h.weight_decay);
-            else grad = fmaf(h.weight_decay, pv, grad);
-          }
-          m[j] = fmaf(h.beta1, m[j], (1.f - h.beta1) * grad);
-          s[j] = fmaf(h.beta2, s[j], (1.f - h.beta2) * grad * grad);
-          pv -= (h.lr / h.bias_c1) * (m[j] / (sqrtf(s[j]) / h.bias_c2_sqrt + h.eps));
+          h.lr = __ldg(&p.segs[lo].lr);
+          h.weight_decay = __ldg(&p.segs[lo].weight_decay);
         }
-        w[j] = pv;
-      }
-      *reinterpret_cast<float4*>(p.master + li) = make_float4(w[0], w[1], w[2], w[3]);
-      *reinterpret_cast<float4*>(p.master + li + 4) = make_float4(w[4], w[5], w[6], w[7]);
-      if (has_m) {
-        *reinterpret_cast<float4*>(p.state0 + li) = make_float4(m[0], m[1], m[2], m[3]);
-        *reinterpret_cast<float4*>(p.state0 + li + 4) = make_float4(m[4], m[5], m[6], m[7]);
-      }
-      if (h.kind != 0) {
-        *reinterpret_cast<float4*>(p.state1 + li) = make_float4(s[0], s[1], s[2], s[3]);
-        *reinterpret_cast<float4*>(p.state1 + li + 4) = make_float4(s[4], s[5], s[6], s[7]);
-      }
-      if (p.param_bf16) {
-        uint4 pk;
-        uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+        float gv[4] = {g[hf].x, g[hf].y, g[hf].z, g[hf].w};
+        float wv[4] = {w[hf].x, w[hf].y, w[hf].z, w[hf].w};
+        float mv[4] = {0.f, 0.f, 0.f, 0.f}, sv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (has_m) { mv[0] = m[hf].x; mv[1] = m[hf].y; mv[2] = m[hf].z; mv[3] = m[hf].w; }
+        if (h.kind != 0) { sv[0] = s[hf].x; sv[1] = s[hf].y; sv[2] = s[hf].z; sv[3] = s[hf].w; }
+        if (h.noise_std != 0.f) {
+          const uint64_t ni = static_cast<uint64_t>(gi[hf] >= p.noise_split ? gi[hf] + p.noise_shift : gi[hf]);
+          const uint4 u = rng(ni >> 2, h.offset);          // one counter per 4 elements of the flat space
+          const float2 z0 = box_muller(u.x, u.y), z1 = box_muller(u.z, u.w);
+          gv[0] += z0.x * h.noise_std; gv[1] += z0.y * h.noise_std;
+          gv[2] += z1.x * h.noise_std; gv[3] += z1.y * h.noise_std;
+        }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          __nv_bfloat162 hv = __floats2bfloat162_rn(w[2 * q], w[2 * q + 1]);
-          pw[q] = *reinterpret_cast<uint32_t*>(&hv);
-        }
-        if (p.param_mc != nullptr) {
-          multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(p.param_mc) + gi, pk);
-        } else {
-          for (int q = 0; q < p.world; ++q) {
-            int r = p.rank + q;
-            if (r >= p.world) r -= p.world;
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.param[r]) + gi) = pk;
+        for (int j = 0; j < 4; ++j) {
+          float grad = gv[j] * h.inv_scale;
+          float pv = wv[j];
+          if (h.kind == 0) {
+            if (h.weight_decay != 0.f) grad = fmaf(h.weight_decay, pv, grad);
+            if (h.momentum != 0.f) {
+              const float buf = h.first_step ? grad : fmaf(h.momentum, mv[j], (1.f - h.dampening) * grad);
+              mv[j] = buf;
+              grad = h.nesterov ? fmaf(h.momentum, buf, grad) : buf;
+            }
+            pv = fmaf(-h.lr, grad, pv);
+          } else {
+            if (h.weight_decay != 0.f) {
+              if (h.kind == 2) pv *= (1.f - h.lr * h.weight_decay);
+              else grad = fmaf(h.weight_decay, pv, grad);
+            }
+            mv[j] = fmaf(h.beta1, mv[j], (1.f - h.beta1) * grad);
+            sv[j] = fmaf(h.beta2, sv[j], (1.f - h.beta2) * grad * grad);
+            pv -= (h.lr / h.bias_c1) * (mv[j] / (sqrtf(sv[j]) / h.bias_c2_sqrt + h.eps));
           }
+          wv[j] = pv;
         }
-      } else if (p.param_mc != nullptr) {
-        float* dst = reinterpret_cast<float*>(p.param_mc) + gi;
-        multimem_st_b128(dst, make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
-                                         __float_as_uint(w[3])));
-        multimem_st_b128(dst + 4, make_uint4(__float_as_uint(w[4]), __float_as_uint(w[5]), __float_as_uint(w[6]),
-                                             __float_as_uint(w[7])));
-      } else {
-        for (int q = 0; q < p.world; ++q) {
-          int r = p.rank + q;
-          if (r >= p.world) r -= p.world;
-          float* dst = reinterpret_cast<float*>(p.param[r]) + gi;
-          *reinterpret_cast<float4*>(dst) = make_float4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(w[4], w[5], w[6], w[7]);
+        *reinterpret_cast<float4*>(p.master + li[hf]) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+        if (has_m) *reinterpret_cast<float4*>(p.state0 + li[hf]) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+        if (h.kind != 0) *reinterpret_cast<float4*>(p.state1 + li[hf]) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+        if (p.param_bf16) {
+          const __nv_bfloat162 h0 = __floats2bfloat162_rn(wv[0], wv[1]), h1 = __floats2bfloat162_rn(wv[2], wv[3]);
+          const uint2 pk = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+          if (p.param_mc != nullptr) {
+            multimem_st_b64(reinterpret_cast<__nv_bfloat16*>(p.param_mc) + gi[hf], pk);
+          } else {
+#pragma unroll 1
+            for (int q = 0; q < p.world; ++q) {
+              int r = p.rank + q;
+              if (r >= p.world) r -= p.world;
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.param[r]) + gi[hf]) = pk;
+            }
+          }
+        } else {
+          const uint4 pk = make_uint4(__float_as_uint(wv[0]), __float_as_uint(wv[1]), __float_as_uint(wv[2]),
+                                      __float_as_uint(wv[3]));
+          if (p.param_mc != nullptr) {
+            multimem_st_b128(reinterpret_cast<float*>(p.param_mc) + gi[hf], pk);
+          } else {
+#pragma unroll 1
+            for (int q = 0; q < p.world; ++q) {
+              int r = p.rank + q;
+              if (r >= p.world) r -= p.world;
+              *reinterpret_cast<uint4*>(reinterpret_cast<float*>(p.param[r]) + gi[hf]) = pk;
+            }
+          }
         }
       }
     }
@@ -258,6 +264,7 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
     return cudaErrorInvalidValue;     // every launch is a meeting of all ranks: no empty ranges
   if ((reinterpret_cast<uintptr_t>(p.grad_mc) & 15) || (reinterpret_cast<uintptr_t>(p.param_mc) & 15))
     return cudaErrorInvalidValue;
+  if (p.noise_split & 3 || p.noise_shift & 3) return cudaErrorInvalidValue;   // one Philox counter per 4 elements
   // every block spins on flags, so all of them must be resident at once: as many per SM as fit
   void (*kernel)(DpkShardedStep) = sharded_step_kernel<0>;
   int slot = 0;

@@ -1,20 +1,30 @@
 """Data-parallel per-layer clipping.
 
-``SimpleDistributedPerLayerOptimizer`` clips at ``step()`` like the
-single-process version and then synchronises.  ``DistributedPerLayerOptimizer``
-does the work inside backward: because each parameter has its own bound, its
-private gradient is final as soon as its per-sample gradient exists, so a
-tensor hook can emit the clipped, noised, scaled gradient straight into stock
-``DistributedDataParallel``'s bucketed all-reduce, which then overlaps with the
-rest of backward.
+With one clipping bound per parameter, a parameter's private gradient does not
+depend on any other parameter: it is final the moment its per-sample gradient
+exists.  ``DistributedPerLayerOptimizer`` uses that to finish each parameter
+*inside* the backward pass -- a gradient hook replaces the gradient autograd is
+about to hand to stock ``DistributedDataParallel`` by the clipped sum (plus the
+single noise draw on rank 0, divided by the global batch), so DDP's bucketed
+all-reduce carries private gradients and overlaps with the rest of backward.
+What is left for ``step()`` is the accountant hook and the wrapped optimiser.
+
+All bookkeeping lives in one ``_Layer`` record per parameter, owned by the
+optimiser (bound, number of physical batches folded into the running sum, hook
+handle); the three stages are this package's kernels (``ops.clip_factor``,
+``ops.weighted_sum``) -- the same pipeline ``DPPerLayerOptimizer`` runs at
+``step()`` time, applied to one parameter.
+
+``SimpleDistributedPerLayerOptimizer`` is the variant for
+:class:`~opacus_b200.distributed.DifferentiallyPrivateDistributedDataParallel`:
+per-layer clipping at ``step()``, then one bucketed all-reduce.
 
 Behavioural parity: ``opacus/optimizers/ddp_perlayeroptimizer.py:29-175``.
 """
 from __future__ import annotations
 
 import math
-from functools import partial
-from typing import Callable, List, Optional
+from typing import Callable, Dict, List, Optional
 
 import torch
 from torch import nn
@@ -24,15 +34,6 @@ from .. import ops
 from .ddpoptimizer import DistributedDPOptimizer
 from .optimizer import DPOptimizer, _generate_noise
 from .perlayeroptimizer import DPPerLayerOptimizer
-
-
-def _clip_and_accumulate_parameter(p: nn.Parameter, max_grad_norm: float):
-    factor = ops.clip_factor(ops.grad_sample_norm_sq(p.grad_sample), float(max_grad_norm))
-    grad = ops.weighted_sum(p.grad_sample, factor)
-    if p.summed_grad is not None:
-        p.summed_grad += grad
-    else:
-        p.summed_grad = grad
 
 
 class SimpleDistributedPerLayerOptimizer(DPPerLayerOptimizer, DistributedDPOptimizer):
@@ -46,6 +47,17 @@ class SimpleDistributedPerLayerOptimizer(DPPerLayerOptimizer, DistributedDPOptim
                          generator=generator, secure_mode=secure_mode)
 
 
+class _Layer:
+    """Per-parameter state of :class:`DistributedPerLayerOptimizer`."""
+
+    __slots__ = ("bound", "batches", "handle")
+
+    def __init__(self, bound: float):
+        self.bound = float(bound)
+        self.batches = 0          # physical batches in the running sum since the last logical step
+        self.handle = None
+
+
 class DistributedPerLayerOptimizer(DPOptimizer):
     """For models wrapped in stock ``torch.nn.parallel.DistributedDataParallel``."""
 
@@ -56,27 +68,49 @@ class DistributedPerLayerOptimizer(DPOptimizer):
                  secure_mode: bool = False, **kwargs):
         self.rank = torch.distributed.get_rank()
         self.world_size = torch.distributed.get_world_size()
-        self.max_grad_norms = max_grad_norm
-        overall = math.sqrt(sum(float(c) ** 2 for c in max_grad_norm))
-        super().__init__(optimizer, noise_multiplier=noise_multiplier, max_grad_norm=overall,
+        self.max_grad_norms = list(max_grad_norm)
+        sensitivity = math.sqrt(sum(float(c) ** 2 for c in self.max_grad_norms))
+        super().__init__(optimizer, noise_multiplier=noise_multiplier, max_grad_norm=sensitivity,
                          expected_batch_size=expected_batch_size, loss_reduction=loss_reduction,
                          generator=generator, secure_mode=secure_mode)
-        self._register_hooks()
+        self._layers: Dict[nn.Parameter, _Layer] = {}
+        for p, bound in zip(self.params, self.max_grad_norms):
+            if p.requires_grad:
+                layer = self._layers[p] = _Layer(bound)
+                layer.handle = p.register_hook(self._finisher(p, layer))
 
-    def _add_noise_parameter(self, p: nn.Parameter):
-        noise = _generate_noise(std=self.noise_multiplier * self.max_grad_norm, reference=p.summed_grad,
-                                generator=None, secure_mode=self.secure_mode)
-        p.grad = p.summed_grad + noise
+    # ---- what happens to one parameter when its gradient arrives
+    def _finisher(self, p: nn.Parameter, layer: _Layer):
+        def on_grad(_batch_grad: torch.Tensor):
+            gs = self._get_flat_grad_sample(p)
+            factor = ops.clip_factor(ops.grad_sample_norm_sq(gs), layer.bound)
+            clipped = ops.weighted_sum(gs, factor)
+            p.summed_grad = clipped if p.summed_grad is None else p.summed_grad.add_(clipped)
+            layer.batches += 1
+            if self._check_skip_next_step(pop_next=False):
+                return None                       # virtual step: keep accumulating, DDP sees the plain gradient
+            private = p.summed_grad
+            if self.rank == 0:                    # the noise belongs to the global sum: one rank draws it
+                private = private + _generate_noise(std=self._noise_std(), reference=private, generator=None,
+                                                    secure_mode=self.secure_mode)
+            if self.loss_reduction == "mean":
+                private = private / (self.expected_batch_size * layer.batches * self.world_size)
+            p.grad = private
+            return private
+
+        return on_grad
 
     @property
     def accumulated_iterations(self) -> int:
-        return max(p.accumulated_iterations for p in self.params)
+        return max((layer.batches for layer in self._layers.values()), default=0)
 
-    def _scale_grad_parameter(self, p: nn.Parameter):
-        p.accumulated_iterations = getattr(p, "accumulated_iterations", 0) + 1
-        if self.loss_reduction == "mean":
-            p.grad /= self.expected_batch_size * p.accumulated_iterations * self.world_size
+    def remove_hooks(self):
+        for layer in self._layers.values():
+            if layer.handle is not None:
+                layer.handle.remove()
+                layer.handle = None
 
+    # ---- the staged API of the base class does not apply: the stages ran per parameter during backward
     def clip_and_accumulate(self):
         raise NotImplementedError("Clip and accumulate is added per layer in DPDDP Per Layer.")
 
@@ -89,26 +123,7 @@ class DistributedPerLayerOptimizer(DPOptimizer):
             return False
         if self.step_hook:
             self.step_hook(self)
-        for p in self.params:
-            p.accumulated_iterations = 0
+        for layer in self._layers.values():
+            layer.batches = 0
         self._is_last_step_skipped = False
         return True
-
-    def _ddp_per_layer_hook(self, p: nn.Parameter, max_grad_norm: float, _: torch.Tensor):
-        _clip_and_accumulate_parameter(p, max_grad_norm)
-        if self._check_skip_next_step(pop_next=False):
-            return None
-        if self.rank == 0:
-            self._add_noise_parameter(p)
-        else:
-            p.grad = p.summed_grad
-        self._scale_grad_parameter(p)
-        return p.grad
-
-    def _register_hooks(self):
-        for p, bound in zip(self.params, self.max_grad_norms):
-            if not p.requires_grad:
-                continue
-            if not hasattr(p, "ddp_hooks"):
-                p.ddp_hooks = []
-            p.ddp_hooks.append(p.register_hook(partial(self._ddp_per_layer_hook, p, bound)))

@@ -99,6 +99,50 @@ def test_ddp_equals_single_process(mode):
             assert torch.allclose(a, b, atol=1e-6), mode
 
 
+def _ddp_per_layer_job(rank, world):
+    """Stock DistributedDataParallel + DistributedPerLayerOptimizer: every parameter is clipped to its own bound
+    and finished inside backward; DDP's all-reduce carries the private gradients."""
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    from opacus_b200.grad_sample import GradSampleModule
+    from opacus_b200.optimizers import DistributedPerLayerOptimizer
+
+    x, y = _data()
+    base = _mlp()
+    gsm = GradSampleModule(base)
+    ddp = DDP(gsm)
+    bounds = [0.05 * (i + 1) for i, _ in enumerate(base.parameters())]
+    opt = DistributedPerLayerOptimizer(torch.optim.SGD(base.parameters(), lr=0.5), noise_multiplier=0.0,
+                                       max_grad_norm=bounds, expected_batch_size=4)
+    xs, ys = x[rank::world], y[rank::world]
+    for _ in range(2):
+        opt.zero_grad()
+        nn.functional.cross_entropy(ddp(xs), ys).backward()
+        opt.step()
+    assert opt.accumulated_iterations == 0
+    return [p.detach().clone() for p in base.parameters()]
+
+
+def test_ddp_per_layer_hooks_equal_single_process_per_layer_clipping():
+    from opacus_b200.grad_sample import GradSampleModule
+    from opacus_b200.optimizers import DPPerLayerOptimizer
+
+    got = _run(_ddp_per_layer_job)
+    x, y = _data()
+    model = _mlp()
+    gsm = GradSampleModule(model)
+    bounds = [0.05 * (i + 1) for i, _ in enumerate(model.parameters())]
+    opt = DPPerLayerOptimizer(torch.optim.SGD(model.parameters(), lr=0.5), noise_multiplier=0.0, max_grad_norm=bounds,
+                              expected_batch_size=8)
+    for _ in range(2):
+        opt.zero_grad()
+        nn.functional.cross_entropy(gsm(x), y).backward()
+        opt.step()
+    for r in range(2):
+        for a, b in zip(got[r], model.parameters()):
+            assert torch.allclose(a, b, atol=1e-6)
+
+
 class _TPNet(nn.Module):
     def __init__(self, col, row):
         super().__init__()
