@@ -117,7 +117,12 @@ class GradSampleHooks(AbstractGradSampleHooks):
     GRAD_SAMPLERS = {}
 
     def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
-                 force_functorch=False, skip_param_grads: bool = False):
+                 force_functorch=False, skip_param_grads: bool = False, early_capture: bool = False):
+        # early_capture: per-sample gradients are computed when the gradient of a layer's OUTPUT arrives (a tap on
+        # the output) instead of after the layer's own backward; parameters stay attached, so autograd still forms
+        # their batch gradient -- afterwards.  Gradient hooks on parameters (per-layer clipping inside stock
+        # DistributedDataParallel) then always find ``grad_sample`` in place.
+        self.early_capture = early_capture
         # skip_param_grads: layers run with detached parameters, so autograd never computes the (non-private)
         # batch gradient of the weights -- a whole GEMM per layer that DP-SGD throws away.  ``p.grad`` then
         # stays None until the DP optimizer writes the private gradient.  Off by default (reference behaviour).
@@ -169,6 +174,9 @@ class GradSampleHooks(AbstractGradSampleHooks):
                 handles.append(sub.register_forward_pre_hook(self._detach_params_pre_hook))
                 handles.append(sub.register_forward_hook(self._tap_forward_hook, always_call=True))
                 continue
+            if self.early_capture:
+                handles.append(sub.register_forward_hook(self._early_tap_forward_hook))
+                continue
             handles.append(sub.register_forward_hook(self.capture_activations_hook))
             handles.append(sub.register_full_backward_hook(
                 partial(self.capture_backprops_hook, loss_reduction=loss_reduction, batch_first=batch_first)))
@@ -196,6 +204,20 @@ class GradSampleHooks(AbstractGradSampleHooks):
         for sub, name, p in saved:
             sub._parameters[name] = p
         if output is None:
+            return None
+        self.capture_activations_hook(module, inputs, output)
+        first = output[0] if isinstance(output, (tuple, list)) else output
+        if self._anchor is None or self._anchor.device != first.device:
+            self._anchor = torch.zeros((), device=first.device, requires_grad=True)
+        tapped = _OutputTap.apply(first, self._anchor, self, module)
+        if isinstance(output, tuple):
+            return (tapped,) + tuple(output[1:])
+        if isinstance(output, list):
+            return [tapped] + list(output[1:])
+        return tapped
+
+    def _early_tap_forward_hook(self, module, inputs, output):
+        if not self._capturing(module) or output is None:
             return None
         self.capture_activations_hook(module, inputs, output)
         first = output[0] if isinstance(output, (tuple, list)) else output
@@ -370,10 +392,11 @@ class GradSampleModule(GradSampleHooks, AbstractGradSampleModule):
     """``nn.Module`` wrapper flavour: ``GradSampleModule(model)(x)``."""
 
     def __init__(self, m: nn.Module, *, batch_first=True, loss_reduction="mean", strict: bool = True,
-                 force_functorch=False, skip_param_grads: bool = False):
+                 force_functorch=False, skip_param_grads: bool = False, early_capture: bool = False):
         nn.Module.__init__(self)
         GradSampleHooks.__init__(self, m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
-                                 force_functorch=force_functorch, skip_param_grads=skip_param_grads)
+                                 force_functorch=force_functorch, skip_param_grads=skip_param_grads,
+                                 early_capture=early_capture)
         self.grad_accumulation_hook = None
 
     def forward(self, *args, **kwargs):

@@ -72,7 +72,13 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
 
 
 # -------------------------------------------------------------------- Embedding
-def embedding_grad_sample(ids, g, num_embeddings):
+def embedding_grad_sample(ids, g, num_embeddings, lazy: bool = True):
+    """Per-sample gradient ``[B, V, D]``: by default in compact form (see :mod:`.lazy`), which the norm and
+    weighted-sum operations below consume directly and every other use turns into the dense tensor."""
+    if lazy and ids.shape[0] > 0:
+        from .lazy import LazyEmbeddingGradSample
+
+        return LazyEmbeddingGradSample(ids, g, num_embeddings)
     return _ref.embedding_grad_sample(ids, g, num_embeddings)
 
 
@@ -145,7 +151,15 @@ def clip_factor(norm_sq, max_grad_norm: float):
     return _ref.clip_factor(norm_sq, max_grad_norm)
 
 
+def _compact(gs):
+    from .lazy import LazyEmbeddingGradSample
+
+    return isinstance(gs, LazyEmbeddingGradSample) and not gs.is_materialized
+
+
 def grad_sample_norm_sq(gs):
+    if _compact(gs):
+        return embedding_norm_sq(gs._ids, gs._g)
     if _on_gpu(gs) and _kernel_dtype(gs) and gs.shape[0] > 0:
         return _k().grad_sample_norm_sq(gs)
     return _ref.grad_sample_norm_sq(gs)
@@ -153,6 +167,12 @@ def grad_sample_norm_sq(gs):
 
 def weighted_sum(gs, c, out=None):
     """``sum_n c[n] gs[n]``; ``out`` (optional, shape of one sample's gradient) is overwritten with it."""
+    if _compact(gs):
+        res = embedding_weighted_grad(gs._ids, gs._g, c.float(), gs._num_embeddings, out_dtype=gs.dtype)
+        if out is not None:
+            out.copy_(res.view(out.shape))
+            return out
+        return res
     if _on_gpu(gs) and _kernel_dtype(gs) and gs.shape[0] > 0:
         return _k().weighted_sum(gs, c, out=out)
     res = _ref.weighted_sum(gs, c)

@@ -15,6 +15,12 @@ handle); the three stages are this package's kernels (``ops.clip_factor``,
 ``ops.weighted_sum``) -- the same pipeline ``DPPerLayerOptimizer`` runs at
 ``step()`` time, applied to one parameter.
 
+The hook needs the parameter's per-sample gradient to exist when autograd
+delivers the parameter's batch gradient.  Module backward hooks run after the
+layer's own backward, i.e. too late for all but the first layer, so the model is
+wrapped as ``GradSampleModule(model, early_capture=True)``: per-sample gradients
+are then computed when the gradient of the layer's output arrives.
+
 ``SimpleDistributedPerLayerOptimizer`` is the variant for
 :class:`~opacus_b200.distributed.DifferentiallyPrivateDistributedDataParallel`:
 per-layer clipping at ``step()``, then one bucketed all-reduce.
@@ -82,6 +88,9 @@ class DistributedPerLayerOptimizer(DPOptimizer):
     # ---- what happens to one parameter when its gradient arrives
     def _finisher(self, p: nn.Parameter, layer: _Layer):
         def on_grad(_batch_grad: torch.Tensor):
+            if getattr(p, "grad_sample", None) is None:
+                raise ValueError("the per-sample gradient of a parameter is not there when its gradient arrives: "
+                                 "wrap the model as GradSampleModule(model, early_capture=True)")
             gs = self._get_flat_grad_sample(p)
             factor = ops.clip_factor(ops.grad_sample_norm_sq(gs), layer.bound)
             clipped = ops.weighted_sum(gs, factor)

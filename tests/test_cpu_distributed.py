@@ -109,7 +109,7 @@ def _ddp_per_layer_job(rank, world):
 
     x, y = _data()
     base = _mlp()
-    gsm = GradSampleModule(base)
+    gsm = GradSampleModule(base, early_capture=True)
     ddp = DDP(gsm)
     bounds = [0.05 * (i + 1) for i, _ in enumerate(base.parameters())]
     opt = DistributedPerLayerOptimizer(torch.optim.SGD(base.parameters(), lr=0.5), noise_multiplier=0.0,

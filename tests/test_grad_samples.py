@@ -214,6 +214,38 @@ def test_clip_factor_propagates_nan_on_cpu():
     assert torch.isnan(c[1]) and abs(float(c[0]) - 0.5) < 1e-5 and float(c[2]) == 1.0
 
 
+def test_embedding_per_sample_gradient_stays_compact_through_a_dp_step():
+    """Hooks mode on an embedding: ``p.grad_sample`` has the dense shape but holds (ids, G); clipping and the
+    weighted sum run on the compact pair, the step equals the one computed from dense per-sample gradients, and
+    reading the tensor any other way yields the dense values."""
+    from opacus_b200 import ops
+    from opacus_b200.grad_sample import GradSampleModule
+    from opacus_b200.ops import _ref
+    from opacus_b200.ops.lazy import LazyEmbeddingGradSample
+    from opacus_b200.optimizers import DPOptimizer
+
+    torch.manual_seed(0)
+    emb = nn.Embedding(300, 16)
+    model = GradSampleModule(nn.Sequential(emb, nn.Flatten(), nn.Linear(16 * 7, 3)))
+    opt = DPOptimizer(torch.optim.SGD(model.parameters(), lr=1.0), noise_multiplier=0.0, max_grad_norm=0.1,
+                      expected_batch_size=5)
+    ids = torch.randint(0, 300, (5, 7))
+    y = torch.randint(0, 3, (5,))
+    before = emb.weight.detach().clone()
+    nn.functional.cross_entropy(model(ids), y).backward()
+    gs = emb.weight.grad_sample
+    assert isinstance(gs, LazyEmbeddingGradSample) and gs.shape == (5, 300, 16) and not gs.is_materialized
+    dense = _ref.embedding_grad_sample(gs._ids, gs._g, 300)
+    others = [p.grad_sample.reshape(5, -1) for p in model.parameters() if p is not emb.weight]
+    norms = torch.cat([dense.reshape(5, -1)] + others, dim=1).norm(dim=1)
+    want = before - (dense * (0.1 / (norms + 1e-6)).clamp(max=1.0)[:, None, None]).sum(0) / 5
+    opt.step()
+    assert not gs.is_materialized
+    assert torch.allclose(emb.weight, want, atol=1e-6)
+    assert torch.allclose(gs * 1.0, dense) and gs.is_materialized
+    assert torch.allclose(ops.grad_sample_norm_sq(gs), dense.pow(2).sum((1, 2)), rtol=1e-5)
+
+
 def test_buffers_rejected():
     with pytest.raises(NotImplementedError):
         GradSampleModule(nn.BatchNorm1d(3))
