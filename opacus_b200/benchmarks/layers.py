@@ -11,7 +11,13 @@ RNN / GRU / LSTM in=hidden=512 T=128.  ``--impl reference`` runs the same
 harness on the reference library found under ``baseline/_ref`` (its modes and
 layers; protocol modelled on ``benchmarks/benchmark_layer.py:26-89`` there).
 Times are CUDA-event medians in milliseconds; a 256 MB buffer is rewritten
-between iterations so every iteration starts with a cold L2.
+between iterations so every iteration starts with a cold L2.  ``peak_mb`` is the
+peak of CUDA memory allocated during one step above what was allocated before it
+(layer, input and optimiser state excluded), the second metric of the
+reference's layer benchmark (``benchmarks/utils.py:30-53``,
+``benchmarks/layers.py:59-119`` there).  ``--kernels`` adds, per row, the names of
+the GEMM-shaped kernels one step launched (``dpk::`` = this package's tensor-core
+kernels; ``nvjet`` / ``gemm`` / ``cutlass`` / ``bmm`` = library GEMMs).
 """
 import argparse
 import json
@@ -114,7 +120,7 @@ def _median_ms(fn, iters, flush):
     return ts[len(ts) // 2]
 
 
-def time_layer(lib, impl, name, make, make_input, mode, dtype, iters, flush):
+def time_layer(lib, impl, name, make, make_input, mode, dtype, iters, flush, want_kernels=False):
     torch.manual_seed(0)
     layer = make().cuda()
     if dtype == torch.bfloat16:
@@ -143,7 +149,30 @@ def time_layer(lib, impl, name, make, make_input, mode, dtype, iters, flush):
             crit(model(x)).backward()
             opt.step()
 
-    return _median_ms(step, iters, flush)
+    ms = _median_ms(step, iters, flush)
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    step()
+    torch.cuda.synchronize()
+    peak_mb = (torch.cuda.max_memory_allocated() - base) / 2 ** 20
+    return ms, peak_mb, (_gemm_kernels(step) if want_kernels else None)
+
+
+def _gemm_kernels(step):
+    """Names (shortened) of the GEMM-shaped kernels of one step with their launch counts."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    marks = ("wgrad_tn", "gram_pair", "conv_psg", "tp_gemm", "nvjet", "gemm", "cutlass", "bmm", "xmma", "cudnn")
+    out = {}
+    for e in prof.key_averages():
+        low = e.key.lower()
+        if any(m in low for m in marks):
+            out[e.key.split("(")[0][:60]] = int(e.count)
+    return out
 
 
 def main():
@@ -154,6 +183,7 @@ def main():
     ap.add_argument("--modes", default="hooks,ghost")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--kernels", action="store_true", help="list the GEMM-shaped kernels of one step per row")
     args = ap.parse_args()
     import warnings
 
@@ -164,20 +194,23 @@ def main():
     dtypes = {"fp32": [torch.float32], "bf16": [torch.bfloat16], "both": [torch.float32, torch.bfloat16]}[args.dtype]
     flush = torch.zeros(64 << 20, device="cuda")
     rows = []
-    print(f"impl={args.impl}  batch={B}  (ms per DP step: fwd + bwd + clip + noise + SGD)")
+    print(f"impl={args.impl}  batch={B}  (ms per DP step: fwd + bwd + clip + noise + SGD; peak CUDA MB of a step)")
     for name in names:
         make, make_input = specs[name]
         for dt in dtypes:
             for mode in args.modes.split(","):
+                peak, kernels = None, None
                 try:
-                    ms = time_layer(lib, args.impl, name, make, make_input, mode, dt, args.iters, flush)
+                    ms, peak, kernels = time_layer(lib, args.impl, name, make, make_input, mode, dt, args.iters, flush,
+                                                   args.kernels)
                     err = None
                 except Exception as e:  # a layer/mode/dtype the library cannot run is reported, not fatal
                     ms, err = None, f"{type(e).__name__}: {str(e)[:120]}"
                 rows.append({"impl": args.impl, "layer": name, "dtype": str(dt).split(".")[-1], "mode": mode,
-                             "ms": ms, "error": err})
-                shown = f"{ms:9.3f} ms" if ms is not None else f"   failed ({err})"
-                print(f"{name:13s} {str(dt).split('.')[-1]:9s} {mode:6s} {shown}", flush=True)
+                             "ms": ms, "peak_mb": peak, "gemm_kernels": kernels, "error": err})
+                shown = f"{ms:9.3f} ms {peak:10.1f} MB" if ms is not None else f"   failed ({err})"
+                print(f"{name:13s} {str(dt).split('.')[-1]:9s} {mode:6s} {shown}"
+                      + (f"   {kernels}" if kernels else ""), flush=True)
     if args.impl == "ours":
         from opacus_b200.ops import _cuda
 

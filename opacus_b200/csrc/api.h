@@ -160,7 +160,9 @@ struct DpkNormAllReduce {
   const float* replicated;   // [n] added once, unreduced, or NULL
   float* total_out;          // [n] or NULL
   float* clip_out;           // [n] or NULL
-  int32_t n, capacity, world, rank, flag_base, pad;
+  // pull != 0: rank r's partial sums already are in slots[r] at (epoch & 1) * world * capacity + r * capacity
+  // (accumulated there by earlier kernels on the same stream); `sharded` is ignored and nothing is copied.
+  int32_t n, capacity, world, rank, flag_base, pull;
   uint32_t epoch;
   float max_norm;
   uint32_t* status;

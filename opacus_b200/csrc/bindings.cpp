@@ -24,6 +24,22 @@ struct StatusBlock {
 StatusBlock g_status[64];
 std::mutex g_mu;
 
+// Debug mode (OPACUS_B200_DEBUG=1 or set_debug(true)): every buffer a binding allocates for a kernel to fill starts
+// as all-ones bytes, which reads as NaN in fp32 / bf16 / fp16 -- an element a kernel failed to write (a tile missed at
+// an odd size, a predicate that is off by one) then shows in the result instead of being whatever the allocator left.
+bool g_debug = [] {
+  const char* e = getenv("OPACUS_B200_DEBUG");
+  return e != nullptr && e[0] != '\0' && e[0] != '0';
+}();
+
+at::Tensor poison(at::Tensor t) {
+  if (g_debug && t.defined() && t.is_cuda() && t.numel() > 0)
+    cudaMemsetAsync(t.data_ptr(), 0xFF, t.nbytes(), at::cuda::getCurrentCUDAStream());
+  return t;
+}
+at::Tensor new_out(at::IntArrayRef sizes, const at::TensorOptions& opt) { return poison(at::empty(sizes, opt)); }
+at::Tensor new_out_like(const at::Tensor& t) { return poison(at::empty_like(t)); }
+
 StatusBlock& status_for(int device) {
   std::lock_guard<std::mutex> lock(g_mu);
   StatusBlock& s = g_status[device & 63];
@@ -232,7 +248,7 @@ at::Tensor tied_cross_norm(at::Tensor ids, at::Tensor g_e, at::Tensor a_h, at::T
   const int D = g_e.size(2);
   const int64_t V = g_h.size(2);
   const int64_t nT = (T + 127) / 128;
-  at::Tensor scratch = at::empty({2 * (int64_t)B * nT * nT}, g_e.options().dtype(at::kFloat));
+  at::Tensor scratch = new_out({2 * (int64_t)B * nT * nT}, g_e.options().dtype(at::kFloat));
   at::Tensor out;
   int accumulate = 0;
   if (total.has_value()) {
@@ -241,7 +257,7 @@ at::Tensor tied_cross_norm(at::Tensor ids, at::Tensor g_e, at::Tensor a_h, at::T
     out = *total;
     accumulate = 1;
   } else {
-    out = at::empty({B}, g_e.options().dtype(at::kFloat));
+    out = new_out({B}, g_e.options().dtype(at::kFloat));
   }
   check(dpk_tied_cross_norm(ids.data_ptr<int64_t>(), g_e.data_ptr(), a_h.data_ptr(), g_h.data_ptr(),
                             g_h.scalar_type() == at::kFloat, B, T, D, V, (float)scale, scratch.data_ptr<float>(),
@@ -255,7 +271,7 @@ at::Tensor scale_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t rows_pe
   need_cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 2, "x must be [rows, cols]");
   TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "x must be fp32 or bf16");
-  at::Tensor y = at::empty(x.sizes(), x.options().dtype(at::kBFloat16));
+  at::Tensor y = new_out(x.sizes(), x.options().dtype(at::kBFloat16));
   const float* cp = nullptr;
   if (c.has_value()) {
     TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kFloat && c->is_contiguous(), "c must be fp32 CUDA");
@@ -273,7 +289,7 @@ at::Tensor split3_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t T, dou
   need_cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kFloat, "x must be fp32 [rows, cols]");
   TORCH_CHECK(T > 0 && x.size(0) % T == 0 && x.size(1) % 8 == 0, "rows must be a multiple of T and cols of 8");
-  at::Tensor y = at::empty({x.size(0) / T, 3 * T, x.size(1)}, x.options().dtype(at::kBFloat16));
+  at::Tensor y = new_out({x.size(0) / T, 3 * T, x.size(1)}, x.options().dtype(at::kBFloat16));
   const float* cp = nullptr;
   if (c.has_value()) {
     TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kFloat && c->is_contiguous() && c->numel() == x.size(0) / T,
@@ -290,7 +306,7 @@ at::Tensor clip_factor(at::Tensor n2, double C) {
   c10::cuda::CUDAGuard guard(n2.device());
   need_cuda_contig(n2, "norm_sq");
   TORCH_CHECK(n2.scalar_type() == at::kFloat, "norm_sq must be fp32");
-  at::Tensor c = at::empty_like(n2);
+  at::Tensor c = new_out_like(n2);
   check(dpk_clip_factor(n2.data_ptr<float>(), c.data_ptr<float>(), n2.numel(), (float)C, stream()), "clip_factor");
   return c;
 }
@@ -299,7 +315,7 @@ at::Tensor row_norm_sq(at::Tensor x) {
   c10::cuda::CUDAGuard guard(x.device());
   need_cuda_contig(x, "x");
   const int64_t B = x.size(0);
-  at::Tensor out = at::empty({B}, x.options().dtype(at::kFloat));
+  at::Tensor out = new_out({B}, x.options().dtype(at::kFloat));
   check(dpk_row_norm_sq(x.data_ptr(), elem_kind(x), B, B ? x.numel() / B : 0, out.data_ptr<float>(), 0, stream()),
         "row_norm_sq");
   return out;
@@ -317,7 +333,7 @@ at::Tensor weighted_sum(at::Tensor x, at::Tensor c, c10::optional<at::Tensor> de
                 "dest must be a contiguous fp32 CUDA tensor with one element per column");
     out = *dest;
   } else {
-    out = at::empty({cols}, x.options().dtype(at::kFloat));
+    out = new_out({cols}, x.options().dtype(at::kFloat));
   }
   check(dpk_weighted_sum(x.data_ptr(), elem_kind(x), c.data_ptr<float>(), B, cols, out.data_ptr<float>(), stream()),
         "weighted_sum");
@@ -351,9 +367,9 @@ std::vector<at::Tensor> norm_lastdim_grad(int64_t kind, at::Tensor x, at::Tensor
   TORCH_CHECK(x.scalar_type() == g.scalar_type() && x.numel() == g.numel(), "x and g must match");
   const int64_t B = x.size(0), rows = x.numel() / B / d;
   auto opt = x.options().dtype(at::kFloat);
-  at::Tensor gw = want_w ? at::empty({B, d}, opt) : at::Tensor();
-  at::Tensor gb = want_b ? at::empty({B, d}, opt) : at::Tensor();
-  at::Tensor stats = at::empty({B * rows * 2}, opt);
+  at::Tensor gw = want_w ? new_out({B, d}, opt) : at::Tensor();
+  at::Tensor gb = want_b ? new_out({B, d}, opt) : at::Tensor();
+  at::Tensor stats = new_out({B * rows * 2}, opt);
   check(dpk_norm_lastdim_grad((int)kind, x.data_ptr(), g.data_ptr(), elem_kind(x), B, rows, d, (float)eps,
                               stats.data_ptr<float>(), want_w ? gw.data_ptr<float>() : nullptr,
                               want_b ? gb.data_ptr<float>() : nullptr, stream()),
@@ -396,8 +412,8 @@ std::vector<at::Tensor> norm_channel_grad(at::Tensor x, at::Tensor g, int64_t gr
   TORCH_CHECK(x.scalar_type() == g.scalar_type() && x.numel() == g.numel() && x.dim() >= 2, "x and g must match");
   const int64_t B = x.size(0), C = x.size(1), S = x.numel() / B / C;
   auto opt = x.options().dtype(at::kFloat);
-  at::Tensor gw = want_w ? at::empty({B, C}, opt) : at::Tensor();
-  at::Tensor gb = want_b ? at::empty({B, C}, opt) : at::Tensor();
+  at::Tensor gw = want_w ? new_out({B, C}, opt) : at::Tensor();
+  at::Tensor gb = want_b ? new_out({B, C}, opt) : at::Tensor();
   check(dpk_norm_channel_grad(x.data_ptr(), g.data_ptr(), elem_kind(x), B, C, S, (int)groups, (float)eps,
                               want_w ? gw.data_ptr<float>() : nullptr, want_b ? gb.data_ptr<float>() : nullptr,
                               stream()),
@@ -495,7 +511,7 @@ void sharded_dp_step(std::vector<int64_t> grad_ptrs, std::vector<int64_t> param_
 std::vector<at::Tensor> norm_allreduce_clip(std::vector<int64_t> slot_ptrs, std::vector<int64_t> flag_ptrs,
                                             c10::optional<at::Tensor> sharded, c10::optional<at::Tensor> replicated,
                                             int64_t n, int64_t capacity, int64_t rank, int64_t flag_base, int64_t epoch,
-                                            double max_norm, at::Device device) {
+                                            double max_norm, at::Device device, bool pull) {
   c10::cuda::CUDAGuard guard(device);
   raise_if_failed(device.index());
   const int world = (int)slot_ptrs.size();
@@ -512,12 +528,12 @@ std::vector<at::Tensor> norm_allreduce_clip(std::vector<int64_t> slot_ptrs, std:
   };
   p.sharded = vec(sharded, "sharded must be a contiguous fp32 CUDA vector of n elements");
   p.replicated = vec(replicated, "replicated must be a contiguous fp32 CUDA vector of n elements");
-  at::Tensor total = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
-  at::Tensor clip = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  at::Tensor total = new_out({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  at::Tensor clip = new_out({n}, at::TensorOptions().device(device).dtype(at::kFloat));
   p.total_out = total.data_ptr<float>();
   p.clip_out = clip.data_ptr<float>();
   p.n = (int)n; p.capacity = (int)capacity; p.world = world; p.rank = (int)rank; p.flag_base = (int)flag_base;
-  p.epoch = (uint32_t)epoch; p.max_norm = (float)max_norm;
+  p.epoch = (uint32_t)epoch; p.max_norm = (float)max_norm; p.pull = pull ? 1 : 0;
   p.status = status_for(device.index()).dev;
   check(dpk_norm_allreduce_clip(&p, stream()), "norm_allreduce_clip");
   return {total, clip};
@@ -569,8 +585,8 @@ std::vector<at::Tensor> cross_entropy_forward(at::Tensor logits, at::Tensor targ
   need_cuda_contig(target, "target");
   TORCH_CHECK(logits.dim() == 2 && target.dim() == 1 && target.size(0) == logits.size(0), "logits [rows, V], target [rows]");
   TORCH_CHECK(target.scalar_type() == at::kLong, "target must be int64");
-  at::Tensor loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
-  at::Tensor lse = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  at::Tensor loss = new_out({logits.size(0)}, logits.options().dtype(at::kFloat));
+  at::Tensor lse = new_out({logits.size(0)}, logits.options().dtype(at::kFloat));
   check(dpk_cross_entropy_forward(logits.data_ptr(), elem_kind(logits), target.data_ptr<int64_t>(), logits.size(0),
                                   logits.size(1), ignore_index, loss.data_ptr<float>(), lse.data_ptr<float>(), stream()),
         "cross_entropy_forward");
@@ -586,7 +602,7 @@ at::Tensor cross_entropy_backward(at::Tensor logits, at::Tensor target, at::Tens
   need_cuda_contig(grad_loss, "grad_loss");
   TORCH_CHECK(lse.scalar_type() == at::kFloat && grad_loss.scalar_type() == at::kFloat &&
               lse.numel() == logits.size(0) && grad_loss.numel() == logits.size(0), "lse / grad_loss: fp32 [rows]");
-  at::Tensor dx = at::empty_like(logits);
+  at::Tensor dx = new_out_like(logits);
   check(dpk_cross_entropy_backward(logits.data_ptr(), elem_kind(logits), target.data_ptr<int64_t>(),
                                    lse.data_ptr<float>(), grad_loss.data_ptr<float>(), logits.size(0), logits.size(1),
                                    ignore_index, dx.data_ptr(), stream()),
@@ -602,7 +618,7 @@ at::Tensor rope(at::Tensor x, double theta, bool src_heads, bool dst_heads, doub
   TORCH_CHECK(x.dim() == 4, "x must be 4-d");
   const int64_t B = x.size(0), hd = x.size(3);
   const int64_t T = src_heads ? x.size(2) : x.size(1), H = src_heads ? x.size(1) : x.size(2);
-  at::Tensor out = dst_heads ? at::empty({B, H, T, hd}, x.options()) : at::empty({B, T, H, hd}, x.options());
+  at::Tensor out = dst_heads ? new_out({B, H, T, hd}, x.options()) : new_out({B, T, H, hd}, x.options());
   check(dpk_rope(x.data_ptr(), out.data_ptr(), elem_kind(x), B, T, H, (int)hd, (float)theta, src_heads ? 1 : 0,
                  dst_heads ? 1 : 0, (float)sign, stream()),
         "rope");
@@ -614,7 +630,7 @@ at::Tensor swiglu_forward(at::Tensor gate, at::Tensor up) {
   need_cuda_contig(gate, "gate");
   need_cuda_contig(up, "up");
   TORCH_CHECK(gate.sizes() == up.sizes() && gate.scalar_type() == up.scalar_type(), "gate and up must match");
-  at::Tensor h = at::empty_like(gate);
+  at::Tensor h = new_out_like(gate);
   check(dpk_swiglu_forward(gate.data_ptr(), up.data_ptr(), h.data_ptr(), elem_kind(gate), gate.numel(), stream()),
         "swiglu_forward");
   return h;
@@ -627,7 +643,7 @@ std::vector<at::Tensor> swiglu_backward(at::Tensor gate, at::Tensor up, at::Tens
   need_cuda_contig(dh, "dh");
   TORCH_CHECK(gate.sizes() == up.sizes() && gate.sizes() == dh.sizes() && gate.scalar_type() == up.scalar_type() &&
               gate.scalar_type() == dh.scalar_type(), "gate, up and dh must match");
-  at::Tensor dg = at::empty_like(gate), du = at::empty_like(gate);
+  at::Tensor dg = new_out_like(gate), du = new_out_like(gate);
   check(dpk_swiglu_backward(gate.data_ptr(), up.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(),
                             elem_kind(gate), gate.numel(), stream()),
         "swiglu_backward");
@@ -647,12 +663,12 @@ std::vector<at::Tensor> add_rmsnorm_forward(at::Tensor x, c10::optional<at::Tens
   if (delta.has_value()) {
     need_cuda_contig(*delta, "delta");
     TORCH_CHECK(delta->sizes() == x.sizes() && delta->scalar_type() == x.scalar_type(), "delta must match x");
-    h = at::empty_like(x);
+    h = new_out_like(x);
     dp = delta->data_ptr();
     hp = h.data_ptr();
   }
-  at::Tensor y = at::empty_like(x);
-  at::Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  at::Tensor y = new_out_like(x);
+  at::Tensor rstd = new_out({rows}, x.options().dtype(at::kFloat));
   check(dpk_add_rmsnorm_forward(x.data_ptr(), dp, w.data_ptr(), hp, y.data_ptr(), rstd.data_ptr<float>(), elem_kind(x),
                                 rows, D, (float)eps, stream()),
         "add_rmsnorm_forward");
@@ -675,7 +691,7 @@ at::Tensor add_rmsnorm_backward(at::Tensor dy, c10::optional<at::Tensor> dres, a
     TORCH_CHECK(dres->sizes() == h.sizes() && dres->scalar_type() == h.scalar_type(), "dres must match h");
     rp = dres->data_ptr();
   }
-  at::Tensor dh = at::empty_like(h);
+  at::Tensor dh = new_out_like(h);
   check(dpk_add_rmsnorm_backward(dy.data_ptr(), rp, h.data_ptr(), rstd.data_ptr<float>(), w.data_ptr(), dh.data_ptr(),
                                  elem_kind(h), rows, D, stream()),
         "add_rmsnorm_backward");
@@ -684,7 +700,7 @@ at::Tensor add_rmsnorm_backward(at::Tensor dy, c10::optional<at::Tensor> dres, a
 
 at::Tensor philox_normal(int64_t n, int64_t seed, int64_t offset, double std, at::Device device) {
   c10::cuda::CUDAGuard guard(device);
-  at::Tensor out = at::empty({n}, at::TensorOptions().device(device).dtype(at::kFloat));
+  at::Tensor out = new_out({n}, at::TensorOptions().device(device).dtype(at::kFloat));
   check(dpk_philox_normal(out.data_ptr<float>(), n, (uint64_t)seed, (uint64_t)offset, (float)std, stream()),
         "philox_normal");
   return out;
@@ -725,7 +741,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("noise_std"), py::arg("inv_scale"), py::arg("seed"), py::arg("offset"), py::arg("noise_split"),
         py::arg("noise_shift"), py::arg("grad_mc") = 0, py::arg("param_mc") = 0, py::arg("segments") = py::none(),
         py::arg("max_blocks") = 0, py::arg("stripe_len") = 0, py::arg("stripe_stride") = 0);
-  m.def("norm_allreduce_clip", &norm_allreduce_clip);
+  m.def("norm_allreduce_clip", &norm_allreduce_clip, py::arg("slot_ptrs"), py::arg("flag_ptrs"), py::arg("sharded"),
+        py::arg("replicated"), py::arg("n"), py::arg("capacity"), py::arg("rank"), py::arg("flag_base"),
+        py::arg("epoch"), py::arg("max_norm"), py::arg("device"), py::arg("pull") = false);
   m.def("step_segment_size", []() { return (int64_t)sizeof(DpkStepSegment); });
   m.def("tp_gemm", &tp_gemm);
   m.def("cross_entropy_forward", &cross_entropy_forward);
@@ -737,6 +755,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rmsnorm_backward", &add_rmsnorm_backward);
   m.def("philox_normal", &philox_normal);
   m.def("check_status", &check_status);
+  m.def("set_debug", [](bool on) { g_debug = on; });
+  m.def("get_debug", []() { return g_debug; });
   m.def("_raise_wait_timeout_for_test", &raise_wait_timeout_for_test);
   m.def("tensor_entry_size", &tensor_entry_size);
 }

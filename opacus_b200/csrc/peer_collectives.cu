@@ -12,6 +12,11 @@
 // kernels (opacus/grad_sample/grad_sample_module_fast_gradient_clipping_tp.py:91-115,
 // opacus/grad_sample/grad_sample_module_fast_gradient_clipping.py:137-150).
 //
+// Pull form (p.pull != 0): the partial sums are not copied anywhere.  The ghost-norm kernels of the backward pass
+// accumulate straight into this rank's own slot of its own symmetric buffer (the epilogue of the Gram kernel adds
+// into that address), and this kernel, after the flag meeting, reads every rank's slot from that rank's memory with
+// plain peer loads.  The all-reduce is then nothing but the operand fetch of the clip-factor computation.
+//
 // Slots are double-buffered by the parity of the call number: a rank can run at most one
 // call ahead of a peer (it cannot pass the wait of call e+1 before every peer has raised
 // flag e+1, i.e. has finished reading the slots of call e).
@@ -26,10 +31,12 @@ __global__ void __launch_bounds__(256) norm_allreduce_clip_kernel(DpkNormAllRedu
   const int64_t half = (int64_t)p.world * p.capacity;          // floats per parity
   const int64_t my_slot = (int64_t)(p.epoch & 1u) * half + (int64_t)p.rank * p.capacity;
   if (threadIdx.x == 0) sh_ok = 1;
-  // 1. publish my partial sums at every rank (my own copy included)
-  for (int r = 0; r < p.world; ++r) {
-    float* dst = p.slots[r] + my_slot;
-    for (int i = threadIdx.x; i < p.n; i += blockDim.x) dst[i] = p.sharded ? p.sharded[i] : 0.f;
+  // 1. publish my partial sums at every rank (my own copy included); in pull form they already sit in my own slot
+  if (!p.pull) {
+    for (int r = 0; r < p.world; ++r) {
+      float* dst = p.slots[r] + my_slot;
+      for (int i = threadIdx.x; i < p.n; i += blockDim.x) dst[i] = p.sharded ? p.sharded[i] : 0.f;
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -55,7 +62,14 @@ __global__ void __launch_bounds__(256) norm_allreduce_clip_kernel(DpkNormAllRedu
   const volatile float* mine = p.slots[p.rank] + (int64_t)(p.epoch & 1u) * half;
   for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
     float t = 0.f;
-    for (int r = 0; r < p.world; ++r) t += mine[(int64_t)r * p.capacity + i];
+    if (p.pull) {
+      for (int r = 0; r < p.world; ++r) {
+        const volatile float* theirs = p.slots[r] + (int64_t)(p.epoch & 1u) * half + (int64_t)r * p.capacity;
+        t += theirs[i];
+      }
+    } else {
+      for (int r = 0; r < p.world; ++r) t += mine[(int64_t)r * p.capacity + i];
+    }
     if (p.replicated) t += p.replicated[i];
     if (p.total_out) p.total_out[i] = t;
     if (p.clip_out) p.clip_out[i] = clip_factor_of(t, p.max_norm);

@@ -242,8 +242,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             else:
                 self._capture_site(module, grad_out)
 
-    # Measured on the Llama-1B step: 78.8 -> 76.7 ms.  The norm kernels (persistent, one CTA per SM) and the
-    # library GEMMs of the backward pass fill each other's partial waves.
+    # The norm kernels (persistent, one CTA per SM) and the library GEMMs of the backward pass fill each other's
+    # partial waves when they run on two streams.
     overlap_norms = True
 
     def _join_norm_stream(self):
@@ -290,11 +290,11 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
             norm_sq = {}
         elif self.use_ghost_clipping and not self.force_functorch and mtype in self.NORM_SQ_SAMPLERS:
             fn = self.NORM_SQ_SAMPLERS[mtype]
-            if (self._use_total_fastpath and backprops.shape[0] == self._batch_len
+            if (self._total_fastpath_ok(module) and backprops.shape[0] == self._batch_len
                     and getattr(fn, "_accepts_total", None) is not False):
                 # built-in rules add straight into the running [B] buffer inside their kernel
                 if self._norm_sq_total is None:
-                    self._norm_sq_total = torch.zeros(self._batch_len, dtype=torch.float32, device=backprops.device)
+                    self._norm_sq_total = self._new_total(self._batch_len, backprops.device)
                 try:
                     norm_sq = fn(module, activations, backprops, g_scale, total=self._norm_sq_total)
                 except TypeError:
@@ -327,6 +327,13 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
     # kernel; subclasses that need to tell parameters apart switch this off.
     _use_total_fastpath = True
 
+    def _total_fastpath_ok(self, module) -> bool:
+        return self._use_total_fastpath
+
+    def _new_total(self, n: int, device) -> torch.Tensor:
+        """The zeroed ``[B]`` fp32 buffer that collects the squared norms of a pass."""
+        return torch.zeros(n, dtype=torch.float32, device=device)
+
     # ---- extension points for parallel layouts (identity here)
     def _batch_share(self, module) -> int:
         """How many times larger the whole batch is than what ``module`` sees."""
@@ -353,8 +360,9 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
 
     def _add_norm_sq(self, p, v):
         """Account the squared per-sample norm ``v`` of parameter ``p``."""
-        self._norm_sq_total = v.clone() if self._norm_sq_total is None else self._norm_sq_total.add_(
-            v.to(self._norm_sq_total.device))
+        if self._norm_sq_total is None:
+            self._norm_sq_total = self._new_total(v.shape[0], v.device)
+        self._norm_sq_total.add_(v.to(self._norm_sq_total.device))
 
     def _add_cross_terms(self):
         """``||sum_i g_i||^2 = sum_i ||g_i||^2 + 2 sum_{i<j} <g_i, g_j>`` for a

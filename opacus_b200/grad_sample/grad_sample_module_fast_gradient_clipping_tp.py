@@ -71,6 +71,21 @@ class GradSampleHooksFastGradientClippingTP(GradSampleHooksFastGradientClipping)
 
     # ---- single-pass bookkeeping: sharded and replicated parameters are kept apart
     _use_total_fastpath = False
+
+    def _total_fastpath_ok(self, module) -> bool:
+        """Layers all of whose parameters are shards add their norms inside the ghost-norm kernel straight into the
+        running sum of the sharded part -- which, with peer memory, is this rank's slot of the symmetric buffer the
+        group's all-reduce reads (``PeerNormReducer.accumulator``): no separate copy, no separate add."""
+        ps = [p for p in module.parameters(recurse=False) if p.requires_grad]
+        return bool(ps) and all(getattr(p, "merge_flag", False) and not getattr(p, "sp_local", False) for p in ps)
+
+    def _new_total(self, n: int, device) -> torch.Tensor:
+        reducer = self._peer_reducer(torch.empty(0, device=device)) if device.type == "cuda" else None
+        if reducer is not None:
+            acc = reducer.accumulator(n)
+            if acc is not None:
+                return acc
+        return super()._new_total(n, device)
     overlap_norms = False        # the rules of this controller issue collectives; keep them on the main stream
 
     # ---- activations sharded over samples between the tensor-parallel blocks (sequence parallelism)

@@ -66,6 +66,21 @@ class _Native:
         return call
 
 
+def set_debug(on: bool = True):
+    """Debug mode (also ``OPACUS_B200_DEBUG=1`` in the environment): every buffer handed to a kernel as an output
+    starts filled with NaN, so an element that a kernel fails to write shows in the result."""
+    load().set_debug(bool(on))
+
+
+def _out(*shape, dtype, device):
+    """Uninitialised output buffer for a kernel; NaN-filled in debug mode."""
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+        shape = tuple(shape[0])
+    if load().get_debug():
+        return torch.full(shape, float("nan"), dtype=dtype, device=device)
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
 def check_status(device=None):
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
     load().check_status(dev or 0)
@@ -130,10 +145,10 @@ def linear_grad_sample(a, g):
     n2 = torch.zeros(B, dtype=torch.float32, device=g.device)
     if g3.dtype == torch.float32:
         gl, ar = _split_pair(g3, a3)
-        out = torch.empty(B, d_out, d_in, dtype=torch.float32, device=g.device)
+        out = _out(B, d_out, d_in, dtype=torch.float32, device=g.device)
         C.wgrad_tn_ex(gl, ar, out, 0.0, n2, 0, 0, 0)
     else:
-        out = torch.empty(B, d_out, d_in, dtype=torch.bfloat16, device=g.device)
+        out = _out(B, d_out, d_in, dtype=torch.bfloat16, device=g.device)
         C.wgrad_tn_ex(g3.contiguous(), _bf16(a3), out, 0.0, n2, 0, 0, 0)
     out._dp_norm_sq = n2
     return out
@@ -151,8 +166,8 @@ def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0
     def outs():
         if acc:
             return (total if want_weight else None), (total if want_bias else None)
-        return (torch.empty(B, dtype=torch.float32, device=g.device) if want_weight else None,
-                torch.empty(B, dtype=torch.float32, device=g.device) if want_bias else None)
+        return (_out(B, dtype=torch.float32, device=g.device) if want_weight else None,
+                _out(B, dtype=torch.float32, device=g.device) if want_bias else None)
 
     def done(w, b):
         return (None, None) if acc else (w, b)
@@ -181,7 +196,7 @@ def linear_norm_sq(a, g, want_weight=True, want_bias=False, g_scale: float = 1.0
         w = n2 * s2 if s2 != 1.0 else n2
         b = None
         if want_bias:
-            b = torch.empty(B, dtype=torch.float32, device=g.device)
+            b = _out(B, dtype=torch.float32, device=g.device)
             scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
             C.gram_pair_norm(None, None, gb, s2, scratch, None, b, False)
         if acc:
@@ -242,7 +257,7 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
         g_op = C.scale_rows(g2.contiguous(), c, T, float(g_scale))
         a_op = _bf16(a2)
     if out is None or out.dtype != torch.float32 or not out.is_contiguous():
-        target = torch.empty(d_out, d_in, dtype=torch.float32, device=g.device)
+        target = _out(d_out, d_in, dtype=torch.float32, device=g.device)
         C.wgrad_tn(g_op, a_op, target, 0.0)
         if out is not None:
             out.add_(target) if accumulate else out.copy_(target)
@@ -270,7 +285,7 @@ def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] =
             return None
         return w
     C = load()
-    w = total if total is not None else torch.empty(B, dtype=torch.float32, device=g.device)
+    w = total if total is not None else _out(B, dtype=torch.float32, device=g.device)
     scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
     C.gram_pair_norm(None, ids2.contiguous().long(), g3.contiguous(), float(g_scale) ** 2, scratch, w, None,
                      total is not None)
@@ -468,11 +483,11 @@ def conv_grad_sample(x, backprops, plan, want_out=True, norm_total=None):
         Op, Cp = gh.shape[3], xh.shape[3]
         passes = _conv_passes(xh, gh, fp32)
         if simple:
-            out = torch.empty((B, Op, kh, kw, Cp), dtype=torch.bfloat16, device=x.device) if want_out else None
+            out = _out((B, Op, kh, kw, Cp), dtype=torch.bfloat16, device=x.device) if want_out else None
             C.conv_psg(passes[0][0], passes[0][1], geom, False, out, 0.0, norm)
         else:
             # the norm of a sum of three products needs the sum: the gradients are formed in fp32, then squared
-            out = torch.empty((B, Op, kh, kw, Cp), dtype=torch.float32, device=x.device)
+            out = _out((B, Op, kh, kw, Cp), dtype=torch.float32, device=x.device)
             for i, (xs, gs) in enumerate(passes):
                 C.conv_psg(xs, gs, geom, False, out, 0.0 if i == 0 else 1.0, None)
             norm.add_(C.row_norm_sq(out))
@@ -501,7 +516,7 @@ def conv_weighted_grad(x, backprops, coef, plan, g_scale=1.0):
     for xh, gh, cg, og in _conv_groups(x, backprops if scaled is None else scaled, plan):
         _, OH, OW, Op = gh.shape
         Cp = xh.shape[3]
-        out = torch.empty((Op, geom[0], geom[1], Cp), dtype=torch.float32, device=x.device)
+        out = _out((Op, geom[0], geom[1], Cp), dtype=torch.float32, device=x.device)
         if fp32:
             for i, (xs, gs) in enumerate(_conv_passes(xh, gh, True)):
                 C.conv_psg(xs, gs, geom, True, out, 0.0 if i == 0 else 1.0, None)

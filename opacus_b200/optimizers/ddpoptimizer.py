@@ -17,7 +17,7 @@ from .optimizer import DPOptimizer
 
 
 class DistributedDPOptimizer(DPOptimizer):
-    _fused_ok = False  # the update follows a collective; see parallel.fused_ddp for the fused form
+    _fused_ok = False  # the update follows a collective; the fused form is the sharded engine's step (engine=)
 
     def __init__(self, optimizer: Optimizer, *, noise_multiplier: float, max_grad_norm: float,
                  expected_batch_size: Optional[int], loss_reduction: str = "mean", generator=None,

@@ -83,18 +83,38 @@ class PeerNormReducer:
     """All-reduce of a per-sample ``[B]`` fp32 vector over the group plus the clip
     factor, as one single-block kernel per rank over peer memory
     (``csrc/peer_collectives.cu``); every rank obtains the same bits.  ``capacity``
-    bounds ``B``.  Construction is collective (symmetric allocation)."""
+    is the longest vector the current buffers hold; a longer one makes every rank
+    allocate larger buffers (all ranks of the group see the same batch, so they
+    grow in the same call).  Construction, and growth, are collective (symmetric
+    allocation)."""
 
     def __init__(self, device, group=None, capacity: int = 8192):
         self.group = group
         self.rank, self.world = world_info(group)
         self.capacity = int(capacity)
         self.device = torch.device(device)
-        self._slots = alloc(2 * self.world * self.capacity, torch.float32, self.device, group)
-        self._flags = alloc(64, torch.int32, self.device, group)
+        self._allocate()
+
+    def _allocate(self):
+        self._slots = alloc(2 * self.world * self.capacity, torch.float32, self.device, self.group)
+        self._flags = alloc(64, torch.int32, self.device, self.group)
         self._epoch = 0
         if self.world > 1:
-            dist.barrier(group=group)       # every rank's buffers are zeroed before anyone's first kernel
+            dist.barrier(group=self.group)  # every rank's buffers are zeroed before anyone's first kernel
+
+    def accumulator(self, n: int) -> Optional[torch.Tensor]:
+        """A zeroed ``[n]`` fp32 vector inside this rank's symmetric buffer for the partial sums of the NEXT call:
+        kernels that add their per-sample norms into it (the ghost-norm epilogues) leave nothing to copy -- the
+        next call, given this very tensor as ``sharded``, reads every rank's vector from that rank's memory.
+        None when ``n`` exceeds the capacity (the caller then uses an ordinary tensor; the call grows the buffers)."""
+        if n > self.capacity:
+            return None
+        half = self.world * self.capacity
+        start = ((self._epoch + 1) & 1) * half + self.rank * self.capacity
+        acc = self._slots.tensor[start: start + n]
+        acc.zero_()
+        self._handed_out = (self._epoch + 1, acc.data_ptr(), n)
+        return acc
 
     def __call__(self, sharded: Optional[torch.Tensor], replicated: Optional[torch.Tensor], max_norm: float):
         """-> ``(total, clip)`` with ``total = sum_ranks sharded + replicated``."""
@@ -103,10 +123,35 @@ class PeerNormReducer:
         ref = sharded if sharded is not None else replicated
         n = ref.numel()
         if n > self.capacity:
-            raise ValueError(f"batch of {n} exceeds the reducer's capacity {self.capacity}")
+            if n > (1 << 22):
+                raise ValueError(f"a batch of {n} samples is beyond what the reducer supports")
+            torch.cuda.synchronize(self.device)          # kernels of earlier calls are done with the old buffers
+            while self.capacity < n:
+                self.capacity *= 2
+            self._allocate()
         self._epoch += 1
+        handed = getattr(self, "_handed_out", None)
+        pull = (sharded is not None and handed is not None
+                and handed == (self._epoch, sharded.data_ptr(), sharded.numel()))
+        self._handed_out = None
+        if self.world > 1:
+            # every rank must take the same form: a rank that pulls reads the peers' own slots
+            pull = self._agree(pull)
         prep = lambda t: None if t is None else t.float().contiguous()
-        total, clip = _cuda.load().norm_allreduce_clip(self._slots.ptrs, self._flags.ptrs, prep(sharded), prep(replicated),
+        total, clip = _cuda.load().norm_allreduce_clip(self._slots.ptrs, self._flags.ptrs,
+                                                       None if pull else prep(sharded), prep(replicated),
                                                        n, self.capacity, self.rank, 0, self._epoch, float(max_norm),
-                                                       self.device)
+                                                       self.device, pull)
         return total, clip
+
+    def _agree(self, pull: bool) -> bool:
+        """All ranks run the same program, so they normally agree by construction; the first call checks it once
+        (a cheap all-reduce) and later calls trust it unless this rank's own answer changes."""
+        known = getattr(self, "_pull_agreed", None)
+        if known is not None and known[0] == pull:
+            return known[1]
+        flag = torch.tensor([1 if pull else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        agreed = bool(flag.item())
+        self._pull_agreed = (pull, agreed)
+        return agreed
