@@ -3,8 +3,8 @@
     python examples/fsdp_example.py                                  # one GPU
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 examples/fsdp_example.py
 
-A small Transformer encoder classifies synthetic token sequences (label = parity of a marked token, so the loss really
-falls).  ``FSDP2Wrapper`` hands the model to this package's sharded engine: bf16 compute weights, fp32 master weights
+A small Transformer encoder classifies synthetic token sequences (class 1 draws most of its tokens from the upper half
+of the vocabulary, class 0 from the lower half, so the loss really falls).  ``FSDP2Wrapper`` hands the model to this package's sharded engine: bf16 compute weights, fp32 master weights
 and AdamW moments sharded over the ranks, gradients reduced and parameters published inside the step kernel.  Two
 parameter groups (weight decay on matrices, none on norms and biases) show that groups may differ in learning rate
 and weight decay.  Half way through, the run saves a checkpoint with ``PrivacyEngine.save_checkpoint`` (model in fp32
@@ -60,9 +60,10 @@ class Classifier(nn.Module):
 
 
 def make_batch(gen, batch, seq, vocab, device):
-    ids = torch.randint(2, vocab, (batch, seq), generator=gen)
-    ids[:, 0] = torch.randint(0, 2, (batch,), generator=gen)         # the label is written into the first token
-    return ids.to(device), ids[:, 0].clone().to(device)
+    labels = torch.randint(0, 2, (batch,), generator=gen)
+    upper = torch.rand(batch, seq, generator=gen) < (0.25 + 0.5 * labels[:, None].float())
+    ids = torch.randint(0, vocab // 2, (batch, seq), generator=gen) + upper.long() * (vocab // 2)
+    return ids.to(device), labels.to(device)
 
 
 def build(args, world):
@@ -127,7 +128,8 @@ def main():
         print(f"checkpoint written after {half} steps, eps = {engine.get_epsilon(1e-5):.2f}; starting over from it")
 
     engine, module, optimizer, criterion = build(args, world)        # a fresh process would do exactly this
-    engine.load_checkpoint(path=path, module=module, optimizer=optimizer)
+    # map_location: the file holds rank 0's tensors; no rank should open a context on another rank's GPU for them
+    engine.load_checkpoint(path=path, module=module, optimizer=optimizer, torch_load_kwargs={"map_location": "cpu"})
     train(module, optimizer, criterion, gen, args, args.steps - half, rank, half)
     if rank == 0:
         print(f"done: {args.steps} steps accounted, eps(1e-5) = {engine.get_epsilon(1e-5):.2f}")

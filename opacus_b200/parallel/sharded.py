@@ -165,7 +165,7 @@ class ShardedDataParallel(nn.Module):
         self._steps = 0
         self._step_stream = None
         self._segments = None            # (key, device table) of the per-group hyper-parameter ranges
-        self._pending_fp32: Optional[Dict[str, torch.Tensor]] = None
+        self._loading = None
         self.last_step_launches = 0
         self.register_load_state_dict_pre_hook(self._before_load)
         self.register_load_state_dict_post_hook(self._after_load)
@@ -230,32 +230,67 @@ class ShardedDataParallel(nn.Module):
 
     def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
         """The wrapped module's ``state_dict`` (its own keys, no extra prefix) with every trainable parameter in
-        fp32 master precision.  Collective: all ranks of the group call it."""
-        sd = self.module.state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
+        fp32 master precision.  The module's own ``state_dict`` runs while its parameters point at the gathered
+        fp32 values, so key renaming or packing done by a layer (``DPMultiheadAttention`` writes ``in_proj_weight``)
+        applies to the master weights as well.  Collective: all ranks of the group call it."""
         full = self._gather(self.master)
-        for name, p in self._named_trainable():
-            o = self._offsets[p]
-            sd[prefix + name] = full[o: o + p.numel()].view(p.shape)
+        if full.data_ptr() == self.master.data_ptr():
+            full = full.clone()
+        with self._parameters_as(full):
+            sd = self.module.state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
+            if not keep_vars:
+                for k, v in list(sd.items()):      # nothing in the result may alias a Parameter that is switched back
+                    if isinstance(v, nn.Parameter):
+                        sd[k] = v.detach()
         return sd
 
+    class _Swap:
+        def __init__(self, engine, full):
+            self.engine, self.full, self.saved = engine, full, []
+
+        def __enter__(self):
+            eng = self.engine
+            for p in eng._params:
+                o = eng._offsets[p]
+                self.saved.append((p, p.data))
+                p.data = self.full[o: o + p.numel()].view(p.shape)
+            return self
+
+        def __exit__(self, *exc):
+            for p, data in self.saved:
+                p.data = data
+            self.saved = []
+            return False
+
+    def _parameters_as(self, full: torch.Tensor):
+        """Context: every trainable parameter's ``.data`` is its range of the fp32 ``[total]`` tensor ``full``."""
+        return ShardedDataParallel._Swap(self, full)
+
     def _before_load(self, module, state_dict, prefix, *unused):
-        """Keys come without the ``module.`` level (as :meth:`state_dict` writes them, and as a checkpoint of
-        the bare model has them); full-precision values are set aside for the master weights."""
+        """Keys come without the ``module.`` level (as :meth:`state_dict` writes them, and as a checkpoint of the
+        bare model has them).  While the wrapped module loads, its parameters point at an ordinary fp32 buffer:
+        the values arrive in full precision whatever the layers' own loading code does with the keys, and the
+        copies never target the peer-mapped compute buffer (a copy from another GPU of this process into it would
+        be executed by that GPU, which has no access to the mapping)."""
         own = prefix + "module."
         for key in [k for k in state_dict if k.startswith(prefix) and not k.startswith(own)]:
             state_dict[own + key[len(prefix):]] = state_dict.pop(key)
-        self._pending_fp32 = {}
-        for name, _ in self._named_trainable():
-            v = state_dict.get(own + name)
-            if isinstance(v, torch.Tensor):
-                self._pending_fp32[name] = v
+        full = self._flat_param.tensor.float()
+        self._share_of(full).copy_(self.master)          # what this rank owns keeps its full precision
+        self._loading = self._parameters_as(full)
+        self._loading.__enter__()
 
     def _after_load(self, module, incompatible_keys):
-        pending, self._pending_fp32 = self._pending_fp32, None
-        self.refresh_master(pending)
+        loading, self._loading = self._loading, None
+        if loading is None:
+            return
+        loading.__exit__()
+        with torch.no_grad():
+            self.master.copy_(self._share_of(loading.full))
+            self._flat_param.tensor.copy_(loading.full.to(self.param_dtype))
 
     def _after_inner_load(self, module, incompatible_keys):
-        if self._pending_fp32 is None:       # loaded through the wrapped module directly: compute precision only
+        if self._loading is None:            # loaded through the wrapped module directly: compute precision only
             self.refresh_master(None)
 
     @torch.no_grad()

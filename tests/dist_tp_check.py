@@ -35,6 +35,29 @@ def check_norm_reducer(rank, world):
         both = [torch.empty_like(clip) for _ in range(world)]
         dist.all_gather(both, clip)
         assert all(torch.equal(b, both[0]) for b in both), "clip factors differ between ranks"
+    # pull form: the partial sums are accumulated in this rank's slot of the symmetric buffer (as the ghost-norm
+    # epilogues do) and the call reads every rank's slot from that rank's memory; then a longer vector (growth)
+    for it, n in enumerate([40, 1024, 40]):
+        g = torch.Generator(device="cuda").manual_seed(500 + 10 * it + rank)
+        part = torch.rand(n, device="cuda", generator=g)
+        acc = red.accumulator(n)
+        assert acc is not None and float(acc.abs().sum()) == 0.0
+        acc.add_(part * 0.25)
+        acc.add_(part * 0.75)
+        total, clip = red(acc, None, 0.5)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part * 0.25 + part * 0.75)
+        ref = torch.zeros_like(part)
+        for p in parts:
+            ref = ref + p
+        assert torch.equal(total, ref), (rank, "pull", it, (total - ref).abs().max().item())
+        torch.testing.assert_close(clip, (0.5 / (ref.sqrt() + 1e-6)).clamp(max=1.0))
+    big = torch.rand(3000, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank))
+    assert red.accumulator(3000) is None
+    total, _ = red(big, None, 1.0)
+    parts = [torch.empty_like(big) for _ in range(world)]
+    dist.all_gather(parts, big)
+    assert red.capacity >= 3000 and torch.equal(total, sum(parts[1:], parts[0]))
     torch.cuda.synchronize()
     _cuda.check_status()
 
