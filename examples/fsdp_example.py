@@ -102,10 +102,10 @@ def main():
     ap.add_argument("--d-model", type=int, default=128)
     ap.add_argument("--vocab", type=int, default=1000)
     ap.add_argument("--seq", type=int, default=64)
-    ap.add_argument("--batch", type=int, default=32, help="per GPU")
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--batch", type=int, default=256, help="per GPU")
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--lr", type=float, default=2e-3)
-    ap.add_argument("--sigma", type=float, default=0.5)
+    ap.add_argument("--sigma", type=float, default=0.3)
     ap.add_argument("--checkpoint", default=None, help="where to write the checkpoint (default: a temporary file)")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
