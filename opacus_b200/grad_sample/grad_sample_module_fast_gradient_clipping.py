@@ -402,7 +402,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         if not self._sites or self._norm_sq_total is None:
             coef = torch.zeros(0, device=self.trainable_parameters[0].device) if self.trainable_parameters else None
             for p in self.trainable_parameters:
-                if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
+                if (p.grad is None and getattr(p, "_dp_grad_out", None) is None
+                        and getattr(p, "_dp_row_shard", None) is None):
                     p.grad = torch.zeros_like(p)
             self._reset_single_pass_state()
             return coef
@@ -414,7 +415,8 @@ class GradSampleHooksFastGradientClipping(GradSampleHooks):
         with phase("dp/clipped_sum"):
             self._write_clipped_sums(coef)
         for p in self.trainable_parameters:
-            if p.grad is None and getattr(p, "_dp_grad_out", None) is None:
+            if (p.grad is None and getattr(p, "_dp_grad_out", None) is None
+                    and getattr(p, "_dp_row_shard", None) is None):      # stepped by its engine, layer by layer
                 p.grad = torch.zeros_like(p)
         self._reset_single_pass_state()
         return coef

@@ -56,6 +56,9 @@ class GradSampleHooksFastGradientClippingFSDP(GradSampleHooksFastGradientClippin
         super().__init__(m, batch_first=batch_first, loss_reduction=loss_reduction, strict=strict,
                          force_functorch=False, max_grad_norm=max_grad_norm, use_ghost_clipping=True,
                          single_pass=single_pass)
+        if getattr(m, "_row_layers", None):
+            # row-sharded layers are stepped one after the other through one set of flag words: one stream
+            self.overlap_clipped_sums = False
 
     def _get_module_type(self, module: nn.Module):
         """``fully_shard`` turns ``Linear`` into ``FSDPLinear(FSDPModule, Linear)``."""

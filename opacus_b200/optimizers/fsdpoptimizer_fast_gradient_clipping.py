@@ -53,6 +53,8 @@ class FSDPOptimizerFastGradientClipping(DPOptimizerFastGradientClipping):
         self.rank = torch.distributed.get_rank()
         self.world_size = torch.distributed.get_world_size()
         self.engine = engine  # ShardedDataParallel, when the native path is used
+        if engine is not None and hasattr(engine, "attach_optimizer"):
+            engine.attach_optimizer(self)
         self.grad_state = {p: {"summed_grad": None} for p in self.params}
 
     def accumulate(self):

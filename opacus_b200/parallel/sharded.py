@@ -62,7 +62,8 @@ class ShardedDataParallel(nn.Module):
     when there is one (default; ``False`` or ``OPACUS_B200_MULTICAST=0`` keeps plain peer loads and stores)."""
 
     def __init__(self, module: nn.Module, *, param_dtype: torch.dtype = torch.bfloat16, process_group=None,
-                 tp_group=None, step_pieces: Optional[int] = None, multicast: Optional[bool] = None, **unused):
+                 tp_group=None, step_pieces: Optional[int] = None, multicast: Optional[bool] = None,
+                 shard_params: bool = False, **unused):
         super().__init__()
         first = next(module.parameters())
         if not first.is_cuda:
@@ -85,8 +86,19 @@ class ShardedDataParallel(nn.Module):
         self._offsets: Dict[nn.Parameter, int] = {}
         self.tp_group = tp_group
         self.tp_rank, self.tp_world = symm.world_info(tp_group) if tp_group is not None else (0, 1)
+        # ---- optional parameter sharding: eligible Linear layers keep only their rows of the weight (see
+        # parallel/param_sharding.py); their parameters live outside the flat space and are stepped layer by layer
+        self._row_layers = []
+        if shard_params:
+            if tp_group is not None:
+                raise NotImplementedError("shard_params together with a tensor-parallel group")
+            from .param_sharding import shard_linears
+
+            self._row_layers = shard_linears(module, process_group)
         distinct = []
         for p in module.parameters():
+            if getattr(p, "_dp_row_shard", None) is not None:
+                continue
             if p.requires_grad and not any(p is q for q in distinct):
                 distinct.append(p)
         shards = [p for p in distinct if getattr(p, "tp_sharded", False)]
@@ -161,6 +173,7 @@ class ShardedDataParallel(nn.Module):
                 b.data = b.data.to(param_dtype)
         self.state0: Optional[torch.Tensor] = None
         self.state1: Optional[torch.Tensor] = None
+        self._init_row_layers(dev)
         self._epoch = 0
         self._steps = 0
         self._step_stream = None
@@ -172,6 +185,133 @@ class ShardedDataParallel(nn.Module):
         module.register_load_state_dict_post_hook(self._after_inner_load)
         if self.world > 1:
             dist.barrier(group=process_group)
+
+    # ------------------------------------------------------------------ row-sharded layers
+    def _init_row_layers(self, dev):
+        self._row_scratch: Dict[tuple, symm.SymmetricBuffer] = {}
+        self._row_flags = None
+        self._row_epoch = 0
+        self._row_pass = None            # per logical step: the launch arguments shared by all layers
+        self._dpopt = None
+        base = self.total
+        for layer in self._row_layers:
+            layer.__dict__["_dp_engine"] = self           # plain attribute: the engine is not a submodule of the layer
+            layer.master = layer.initial_master_rows.reshape(-1).contiguous()
+            del layer.initial_master_rows
+            layer.state0 = layer.state1 = None
+            layer.noise_base = base                       # Philox counters of this weight: noise_base + index in it
+            layer.stepped = False
+            base += layer.full_shape[0] * layer.full_shape[1]
+            key = tuple(layer.full_shape)
+            if key not in self._row_scratch:
+                self._row_scratch[key] = symm.alloc(key[0] * key[1], torch.float32, dev, self.process_group, zero=False)
+        if self._row_layers:
+            self._row_flags = symm.alloc(64, torch.int32, dev, self.process_group)
+
+    def attach_optimizer(self, dpopt):
+        """The DP optimizer whose hyper-parameters the layer-by-layer steps of row-sharded layers read."""
+        self._dpopt = dpopt
+
+    def _row_pass_args(self):
+        """Launch arguments common to the row-sharded layers of one logical step (made at the first layer)."""
+        if self._row_pass is not None:
+            return self._row_pass
+        from ..ops import _cuda
+
+        dpopt = self._dpopt
+        if dpopt is None:
+            raise RuntimeError("row-sharded layers need the optimizer attached to the engine "
+                               "(FSDPOptimizerFastGradientClipping(..., engine=engine) does it)")
+        if dpopt._check_skip_next_step(pop_next=False):
+            raise NotImplementedError("logical batches split into several physical ones are not supported with "
+                                      "shard_params=True (the clipped sums of a sharded layer are consumed at once)")
+        if getattr(dpopt, "secure_mode", False):
+            raise NotImplementedError("secure_mode with shard_params=True")
+        inner = dpopt.original_optimizer
+        kind, g0, _ = self._hyper(inner)
+        t = self._steps + 1
+        h = dict(momentum=0.0, dampening=0.0, beta1=0.0, beta2=0.0, eps=0.0, bias_c1=1.0, bias_c2_sqrt=1.0)
+        nesterov, kcode = False, 0
+        if kind == "sgd":
+            h["momentum"] = float(g0.get("momentum", 0.0))
+            h["dampening"] = float(g0.get("dampening", 0.0))
+            nesterov = bool(g0.get("nesterov", False))
+        else:
+            b1, b2 = g0["betas"]
+            h.update(beta1=float(b1), beta2=float(b2), eps=float(g0["eps"]), bias_c1=1.0 - float(b1) ** t,
+                     bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
+            kcode = 2 if kind == "adamw" else 1
+        group_of = {}
+        for g in inner.param_groups:
+            for p in g["params"]:
+                group_of[p] = g
+        denom = float(dpopt._grad_denominator()) * (self.world if dpopt.loss_reduction == "mean" else 1)
+        n_row = sum(l.full_shape[0] * l.full_shape[1] for l in self._row_layers)
+        seed, offset = _cuda._rng_state(dpopt.generator, self.master.device, n_row)
+        self._row_pass = dict(kind=kind, kcode=kcode, nesterov=nesterov, h=h, group_of=group_of,
+                              noise_std=float(dpopt._noise_std()), inv_scale=1.0 / denom, seed=seed, offset=offset)
+        return self._row_pass
+
+    def step_row_layer(self, layer, activations, backprops, coef, g_scale: float):
+        """Clipped sum of a row-sharded layer into the symmetric scratch of its shape, then at once the step
+        kernel for this layer: reduce-scatter over the ranks (each rank sums its rows), noise, update of the fp32
+        master rows and moments, new bf16 rows into the shard."""
+        from .. import ops
+        from ..ops import _cuda
+
+        a = self._row_pass_args()
+        N, K = layer.full_shape
+        scratch = self._row_scratch[(N, K)]
+        ops.linear_weighted_grad(activations, backprops, coef, g_scale, want_bias=False,
+                                 out=scratch.tensor.view(N, K), accumulate=False)
+        dev = layer.master.device
+        h, kind = a["h"], a["kind"]
+        first_step = False
+        if kind == "sgd":
+            if h["momentum"] != 0.0 and layer.state0 is None:
+                layer.state0 = torch.zeros_like(layer.master)
+                first_step = True
+        elif layer.state0 is None:
+            layer.state0, layer.state1 = torch.zeros_like(layer.master), torch.zeros_like(layer.master)
+        group = a["group_of"].get(layer.weight)
+        if group is None:
+            raise RuntimeError("a row-sharded weight is missing from the optimizer's parameter groups")
+        begin = self.rank * layer.rows * K
+        n = layer.rows * K
+        # the kernel addresses the compute copy as param[r] + index in the whole weight: every entry is this rank's
+        # shard moved back by the offset of its first row, so all writes land in the shard itself
+        shifted = layer.weight.data_ptr() - begin * layer.weight.element_size()
+        self._row_epoch += 1
+        mc = scratch.mc_ptr if (self.multicast and self.multicast_reduce) else 0
+        _cuda.load().sharded_dp_step(
+            scratch.ptrs, [shifted] * self.world, self._row_flags.ptrs, layer.master, layer.state0, layer.state1,
+            begin, n, self.rank, True, self._row_epoch, a["kcode"], a["nesterov"], first_step, float(group["lr"]),
+            h["momentum"], h["dampening"], float(group.get("weight_decay", 0.0)), h["beta1"], h["beta2"], h["eps"],
+            h["bias_c1"], h["bias_c2_sqrt"], a["noise_std"], a["inv_scale"], a["seed"], a["offset"], 0,
+            layer.noise_base, mc, 0, None, 0, 0, 0)
+        layer.stepped = True
+        layer._slot.holder = None if layer._slot.holder is layer else layer._slot.holder   # the pool copy is stale
+
+    def _finish_row_layers(self):
+        """End of a logical step: every row-sharded layer must have been stepped in this pass."""
+        if not self._row_layers:
+            return
+        missing = [l for l in self._row_layers if not l.stepped]
+        if missing and any(l.stepped for l in self._row_layers):
+            raise RuntimeError(f"{len(missing)} row-sharded layers received no gradient in this step")
+        for l in self._row_layers:
+            l.stepped = False
+        self._row_pass = None
+
+    def _gather_rows(self, layer, rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Whole ``[N, K]`` fp32 tensor from every rank's ``[rows * K]`` vector (collective)."""
+        if rows is None:
+            return None
+        if self.world == 1:
+            return rows.view(layer.full_shape).clone()
+        parts = [torch.empty_like(rows) for _ in range(self.world)]
+        dist.all_gather(parts, rows.contiguous(), group=self.process_group)
+        return torch.cat(parts).view(layer.full_shape)
 
     # ------------------------------------------------------------------ layout helpers
     def _share_of(self, full: torch.Tensor) -> torch.Tensor:
@@ -221,9 +361,12 @@ class ShardedDataParallel(nn.Module):
         full = self._gather(self.master)
         out = {}
         for name, p in self.module.named_parameters():
+            layer = getattr(p, "_dp_row_shard", None)
             if p in self._offsets:
                 o = self._offsets[p]
                 out[name] = full[o: o + p.numel()].view(p.shape).clone()
+            elif layer is not None:
+                out[name] = self._gather_rows(layer, layer.master)       # the whole [N, K] weight
             else:
                 out[name] = p.detach().clone()
         return out
@@ -236,7 +379,8 @@ class ShardedDataParallel(nn.Module):
         full = self._gather(self.master)
         if full.data_ptr() == self.master.data_ptr():
             full = full.clone()
-        with self._parameters_as(full):
+        rows = {l.weight: self._gather_rows(l, l.master) for l in self._row_layers}
+        with self._parameters_as(full, rows):
             sd = self.module.state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
             if not keep_vars:
                 for k, v in list(sd.items()):      # nothing in the result may alias a Parameter that is switched back
@@ -245,8 +389,8 @@ class ShardedDataParallel(nn.Module):
         return sd
 
     class _Swap:
-        def __init__(self, engine, full):
-            self.engine, self.full, self.saved = engine, full, []
+        def __init__(self, engine, full, rows=None):
+            self.engine, self.full, self.rows, self.saved = engine, full, rows or {}, []
 
         def __enter__(self):
             eng = self.engine
@@ -254,6 +398,9 @@ class ShardedDataParallel(nn.Module):
                 o = eng._offsets[p]
                 self.saved.append((p, p.data))
                 p.data = self.full[o: o + p.numel()].view(p.shape)
+            for p, whole in self.rows.items():           # row-sharded weights appear with their whole shape
+                self.saved.append((p, p.data))
+                p.data = whole
             return self
 
         def __exit__(self, *exc):
@@ -262,9 +409,10 @@ class ShardedDataParallel(nn.Module):
             self.saved = []
             return False
 
-    def _parameters_as(self, full: torch.Tensor):
-        """Context: every trainable parameter's ``.data`` is its range of the fp32 ``[total]`` tensor ``full``."""
-        return ShardedDataParallel._Swap(self, full)
+    def _parameters_as(self, full: torch.Tensor, rows=None):
+        """Context: every trainable parameter's ``.data`` is its range of the fp32 ``[total]`` tensor ``full``
+        (row-sharded weights: the whole fp32 ``[N, K]`` tensor given for them in ``rows``)."""
+        return ShardedDataParallel._Swap(self, full, rows)
 
     def _before_load(self, module, state_dict, prefix, *unused):
         """Keys come without the ``module.`` level (as :meth:`state_dict` writes them, and as a checkpoint of the
@@ -277,7 +425,10 @@ class ShardedDataParallel(nn.Module):
             state_dict[own + key[len(prefix):]] = state_dict.pop(key)
         full = self._flat_param.tensor.float()
         self._share_of(full).copy_(self.master)          # what this rank owns keeps its full precision
-        self._loading = self._parameters_as(full)
+        rows = {l.weight: torch.zeros(l.full_shape, dtype=torch.float32, device=full.device) for l in self._row_layers}
+        for l in self._row_layers:                       # rows this rank owns start from their current values
+            rows[l.weight][self.rank * l.rows:(self.rank + 1) * l.rows].copy_(l.master.view(l.rows, -1))
+        self._loading = self._parameters_as(full, rows)
         self._loading.__enter__()
 
     def _after_load(self, module, incompatible_keys):
@@ -288,6 +439,13 @@ class ShardedDataParallel(nn.Module):
         with torch.no_grad():
             self.master.copy_(self._share_of(loading.full))
             self._flat_param.tensor.copy_(loading.full.to(self.param_dtype))
+            for l in self._row_layers:
+                mine = loading.rows[l.weight][self.rank * l.rows:(self.rank + 1) * l.rows]
+                l.master.copy_(mine.reshape(-1))
+                l.weight.data.copy_(mine.to(l.weight.dtype))
+                l._slot.holder = None
+        if self._row_layers and self.world > 1:
+            dist.barrier(group=self.process_group)       # every shard is rewritten before any rank gathers again
 
     def _after_inner_load(self, module, incompatible_keys):
         if self._loading is None:            # loaded through the wrapped module directly: compute precision only
@@ -329,6 +487,13 @@ class ShardedDataParallel(nn.Module):
                 index[sd["param_groups"][gi]["params"][pi]] = p
         state = {}
         for idx, p in index.items():
+            layer = getattr(p, "_dp_row_shard", None)
+            if layer is not None and layer.state0 is not None:     # row-sharded weight: whole [N, K] state
+                entry = {} if len(names) == 1 else {"step": torch.tensor(float(self._steps))}
+                for name, rows in zip(names, (layer.state0, layer.state1)):
+                    entry[name] = self._gather_rows(layer, rows)
+                state[idx] = entry
+                continue
             if p not in self._offsets:
                 continue
             o = self._offsets[p]
@@ -356,6 +521,16 @@ class ShardedDataParallel(nn.Module):
         for gi, g in enumerate(inner.param_groups):
             for pi, p in enumerate(g["params"]):
                 entry = state.get(sd["param_groups"][gi]["params"][pi])
+                layer = getattr(p, "_dp_row_shard", None)
+                if entry is not None and layer is not None:
+                    mine = slice(self.rank * layer.rows, (self.rank + 1) * layer.rows)
+                    vals = [entry[name].to(device=dev, dtype=torch.float32).view(layer.full_shape)[mine].reshape(-1)
+                            .clone() for name in names if name in entry]
+                    layer.state0 = vals[0] if vals else None
+                    layer.state1 = vals[1] if len(vals) > 1 else None
+                    if "step" in entry:
+                        steps = max(steps, int(float(entry["step"])))
+                    continue
                 if entry is None or p not in self._offsets:
                     continue
                 o = self._offsets[p]
@@ -537,6 +712,7 @@ class ShardedDataParallel(nn.Module):
             self.last_step_launches = len(runs)
         dpopt._is_last_step_skipped = False
         self.mark_grads_fresh()
+        self._finish_row_layers()
         return None
 
     def _ready_runs(self, had_fresh: bool):

@@ -31,9 +31,11 @@ from opacus_b200.utils.fast_gradient_clipping_utils import DPLossFastGradientCli
 B, T, C = 4, 64, 0.5
 
 
-def build(group, expected, sigma, opt_cls, **engine_kw):
+def build(group, expected, sigma, opt_cls, wide=False, **engine_kw):
     torch.manual_seed(0)
-    model = Llama(LlamaConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=256)).cuda()
+    cfg = LlamaConfig(vocab_size=512, d_model=512, n_layers=2, n_heads=8, n_kv_heads=4, ffn_dim=1024) if wide else \
+        LlamaConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=256)
+    model = Llama(cfg).cuda()
     eng = ShardedDataParallel(model, process_group=group, **engine_kw)
     gsm = GradSampleModuleFastGradientClippingFSDP(eng, max_grad_norm=C)
     inner = opt_cls(model.parameters(), lr=1e-2)
@@ -123,6 +125,40 @@ def main():
     if rank == 0:
         print("sharded resume ok")
     dist.barrier()
+
+    # parameter sharding: Linear weights kept as row shards (fused all-gather -> GEMM forward, layer-by-layer
+    # reduce-scatter + step) against the replicated layout run by rank 0 alone on the whole batch
+    if world in (1, 2, 4):
+        from opacus_b200.parallel.param_sharding import ShardedLinear
+
+        eng, gsm, opt, crit = build(None, B, 0.0, torch.optim.AdamW, wide=True, shard_params=True)
+        assert sum(isinstance(m, ShardedLinear) for m in eng.module.modules()) >= 8
+        run(gsm, opt, crit, mine, 3)
+        got = eng.full_precision_state_dict()
+        if rank == 0:
+            eng1, gsm1, opt1, crit1 = build(solo, B * world, 0.0, torch.optim.AdamW, wide=True)
+            run(gsm1, opt1, crit1, ids_all, 3)
+            want = eng1.full_precision_state_dict()
+            for k in want:
+                err = ((got[k] - want[k]).norm() / (want[k].norm() + 1e-12)).item()
+                assert err < 2e-2, ("shard_params", k, err)
+        dist.barrier()
+        # noise on a sharded weight: one draw of std sigma * C per element of the whole weight, rows independent
+        eng, gsm, opt, crit = build(None, B, 50.0, torch.optim.SGD, wide=True, shard_params=True)
+        layer = next(m for m in eng.module.modules() if isinstance(m, ShardedLinear))
+        before = layer.master.clone()
+        run(gsm, opt, crit, mine, 1)
+        delta = (layer.master - before) * (B * world) / 1e-2
+        std = delta.std().item()
+        assert abs(std - 50.0 * C) / (50.0 * C) < 0.05, ("shard noise", std)
+        parts = [torch.empty_like(delta) for _ in range(world)]
+        dist.all_gather(parts, delta)
+        if world > 1:
+            corr = (parts[0] * parts[1]).mean().item() / (std * std)
+            assert abs(corr) < 0.03, corr
+        if rank == 0:
+            print("sharded parameters ok")
+        dist.barrier()
     dist.destroy_process_group()
 
 

@@ -282,6 +282,65 @@ def test_engine_secure_mode_noise_comes_from_the_optimizer_generator(pg):
     assert abs(delta.std().item() - 100.0 * 0.5) / 50.0 < 0.05
 
 
+def _wide_model():
+    from opacus_b200.models import Llama, LlamaConfig
+
+    torch.manual_seed(0)
+    return Llama(LlamaConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=512)).cuda()
+
+
+def test_parameter_sharding_equals_replicated_engine(pg, tmp_path):
+    """shard_params=True (row-sharded Linear weights: fused all-gather -> GEMM forward, layer-by-layer reduce-scatter +
+    step) trains like the replicated layout, and its checkpoint holds whole fp32 weights."""
+    from opacus_b200 import PrivacyEngine
+    from opacus_b200.parallel.param_sharding import ShardedLinear
+    from opacus_b200.parallel.sharded import ShardedDataParallel
+
+    ids = torch.randint(0, 512, (4, 129), device="cuda")
+    results = {}
+    for shard in (False, True):
+        model = _wide_model()
+        eng = ShardedDataParallel(model, shard_params=shard)
+        n_sharded = sum(isinstance(m, ShardedLinear) for m in model.modules())
+        assert (n_sharded > 0) == shard
+        if shard:
+            assert n_sharded == 2 * 5                      # q, o, gate, up, down of both blocks; k / v are too narrow
+        m, opt, crit, _ = _private(eng, "ghost_fsdp", 0.0, torch.optim.AdamW, weight_decay=0.05)
+        for _ in range(3):
+            _step(m, opt, crit, ids)
+        torch.cuda.synchronize()
+        results[shard] = (eng.full_precision_state_dict(), m.per_sample_gradient_norms.clone(), eng, m, opt)
+    a, b = results[False][0], results[True][0]
+    assert set(a) == set(b)
+    assert torch.allclose(results[False][1], results[True][1], rtol=2e-2)
+    for k in a:
+        assert a[k].shape == b[k].shape, k
+        assert ((a[k] - b[k]).norm() / (a[k].norm() + 1e-12)).item() < 2e-2, k
+    # checkpoint of the sharded layout: whole fp32 weights under the model's own keys, torch.optim optimizer layout
+    _, _, eng, m, opt = results[True]
+    sd = m.state_dict()
+    key = "_module.layers.0.self_attn.q_proj.weight"
+    assert sd[key].shape == (256, 256) and sd[key].dtype == torch.float32
+    osd = opt.state_dict()
+    shapes = {tuple(v["exp_avg"].shape) for v in osd["state"].values()}
+    assert (512, 256) in shapes and (256, 512) in shapes
+    # a fresh sharded engine resumes from it
+    model2 = _wide_model()
+    with torch.no_grad():
+        for p in model2.parameters():
+            p.add_(0.3)
+    eng2 = ShardedDataParallel(model2, shard_params=True)
+    m2, opt2, crit2, _ = _private(eng2, "ghost_fsdp", 0.0, torch.optim.AdamW, weight_decay=0.05)
+    m2.load_state_dict(sd)
+    opt2.load_state_dict(osd)
+    _step(m, opt, crit, ids)
+    _step(m2, opt2, crit2, ids)
+    torch.cuda.synchronize()
+    x, y = eng.full_precision_state_dict(), eng2.full_precision_state_dict()
+    for k in x:
+        assert ((x[k] - y[k]).norm() / (x[k].norm() + 1e-12)).item() < 1e-3, k
+
+
 def test_engine_serves_hooks_mode_data_parallel(pg):
     """DistributedDPOptimizer on top of the engine (fp32 compute weights) equals the plain DPOptimizer."""
     import copy
