@@ -163,6 +163,24 @@ def run(op, B, T, din, dout, iters=20):
             _, hs, rs = C.add_rmsnorm_forward(xs, dl, wn, 1e-5)
             ms = _time(lambda: C.add_rmsnorm_backward(xs, dl, hs, rs, wn), iters, flush)
             rows.append(("add + rmsnorm backward", ms, 4 * byts / ms / 1e6, "GB/s", 4 * byts / ms / 1e6 / bw_peak))
+    if op in ("norm_rule", "all") and din % 8 == 0 and din <= 4096:
+        # LayerNorm / RMSNorm per-sample gradients + their norms in one launch: reads x and g once (x twice, L1)
+        xs = torch.randn(B, T, din, device=dev, dtype=torch.bfloat16)
+        gn = torch.randn(B, T, din, device=dev, dtype=torch.bfloat16)
+        byts = xs.numel() * 2.0 * 2
+        ms = _time(lambda: ops.norm_affine_grad_sample("rms", xs, gn, eps=1e-5, normalized_ndim=1, want_bias=False),
+                   iters, flush)
+        rows.append(("rmsnorm per-sample grad + norm (one launch)", ms, byts / ms / 1e6, "GB/s", byts / ms / 1e6 / bw_peak))
+    if op in ("fp32_split", "all"):
+        # fp32 operands through the three-plane bf16 split: 3x the bf16 FLOPs of the fp32 product
+        a32, g32 = a.float(), g.float()
+        flops = 2.0 * B * T * din * dout
+        ms = _time(lambda: ops.linear_weighted_grad(a32, g32, c), iters, flush)
+        rows.append(("fp32 clipped sum (split3 + wgrad_tn, 3 planes)", ms, flops / ms / 1e9, "TFLOP/s (fp32-equivalent)",
+                     3 * flops / ms / 1e9 / tf_peak))
+        ms = _time(lambda: torch.matmul((g32 * c[:, None, None]).reshape(B * T, dout).t(), a32.reshape(B * T, din)),
+                   iters, flush)
+        rows.append(("cuBLAS fp32/tf32 TN (library, for scale)", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
     _cuda.check_status()
     print(f"shape B={B} T={T} d_in={din} d_out={dout}; peaks: {tf_peak} TFLOP/s bf16, {bw_peak} GB/s ({src})")
     for name, ms, rate, unit, frac in rows:

@@ -33,10 +33,12 @@ def test_tensor_parallel_peer_collectives_multi_gpu():
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_tensor_parallel_times_sharded_data_parallel_multi_gpu():
-    """2-way tensor parallel x sharded data parallel.  Two ranks by default (one tensor-parallel group, single-rank
-    data-parallel groups: the shard / replica noise ranges and the engine under the tensor-parallel controller);
-    OPACUS_B200_2D_RANKS=4 or 8 adds data-parallel groups of 2 or 4 ranks."""
+    """2-way tensor parallel x sharded data parallel.  With four or more GPUs visible: 4 ranks (2 x 2, the gradient
+    reduction inside the data-parallel groups under the tensor-parallel controller); with two: one tensor-parallel
+    group and single-rank data-parallel groups (the shard / replica noise ranges).  OPACUS_B200_2D_RANKS overrides
+    (2, 4 or 8)."""
     n = torch.cuda.device_count()
-    nproc = min(int(os.environ.get("OPACUS_B200_2D_RANKS", "2")), n - n % 2)
+    default = "4" if n >= 4 else "2"
+    nproc = min(int(os.environ.get("OPACUS_B200_2D_RANKS", default)), n - n % 2)
     out = _launch("dist_tp_fsdp_check.py", nproc, TP_SIZE="2")
     assert "tp x fsdp check ok" in out
