@@ -64,6 +64,9 @@ def main():
         try:
             out = run_reference(args, dev, rank, world)
         except Exception as exc:                        # reported, never fatal for the caller
+            import traceback
+
+            traceback.print_exc()
             out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
         if rank == 0:
             print(json.dumps(out))
@@ -206,7 +209,7 @@ def run_reference(args, dev, rank, world):
             ids = host[i].to(dev, non_blocking=True)
             opt.zero_grad(set_to_none=True)
             opt.signal_skip_step(do_skip=i < n_micro - 1)
-            logits = gsm(ids[:, :-1])
+            logits = gsm(ids[:, :-1].contiguous())         # its embedding rule takes a view of the ids
             loss = crit(logits.float().flatten(0, 1), ids[:, 1:].reshape(-1), shape=(args.micro, T))
             loss.backward()
             opt.step()

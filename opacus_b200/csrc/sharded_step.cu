@@ -281,11 +281,15 @@ extern "C" int dpk_sharded_dp_step(const DpkShardedStep* ph, cudaStream_t stream
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kShThreads, 0) != cudaSuccess || n < 1) n = 1;
     per_sm_cached[slot] = n > 4 ? 4 : n;
   }
+  // A capped launch shares the GPU with compute-bound kernels (the weight-gradient GEMMs: one 256-thread CTA per
+  // SM holding ~23 K registers): blocks of 256 threads keep this kernel's registers per block low enough for one
+  // block to be resident on every SM beside a GEMM CTA, which 512-thread blocks are not.
+  const int threads = p.max_blocks > 0 ? 256 : kShThreads;
   int grid = num_sms() * per_sm_cached[slot];
   if (p.max_blocks > 0 && p.max_blocks < grid) grid = p.max_blocks;   // a piece beside GEMMs leaves them the SMs
   const int64_t nvec = p.slice_len >> 3;
-  const int64_t need = (nvec + kShThreads - 1) / kShThreads;
+  const int64_t need = (nvec + threads - 1) / threads;
   if (need < grid) grid = need < 1 ? 1 : (int)need;
-  kernel<<<grid, kShThreads, 0, stream>>>(p);
+  kernel<<<grid, threads, 0, stream>>>(p);
   return cudaGetLastError();
 }
