@@ -132,7 +132,7 @@ def main():
         from opacus_b200.parallel.param_sharding import ShardedLinear
 
         eng, gsm, opt, crit = build(None, B, 0.0, torch.optim.AdamW, wide=True, shard_params=True)
-        assert sum(isinstance(m, ShardedLinear) for m in eng.module.modules()) >= 8
+        assert sum(isinstance(m, ShardedLinear) for m in eng.module.modules()) >= 4      # 10 on 2 ranks, 4 on 4
         run(gsm, opt, crit, mine, 3)
         got = eng.full_precision_state_dict()
         if rank == 0:
