@@ -72,11 +72,13 @@ int dpk_outer_norm_sq(const void* a, const void* g, int elem_kind, int64_t B, in
 int dpk_norm_lastdim_grad(int kind, const void* x, const void* g, int elem_kind, int64_t B, int64_t rows, int64_t d,
                           float eps, float* stats_scratch, float* gw, float* gb, cudaStream_t stream);
 // The same gradients plus their squared norms n2w[n] = ||gw[n]||^2, n2b[n] = ||gb[n]||^2 (+= when accumulate) in
-// ONE launch.  gw / gb ([B, d], gb may be NULL) and tickets ([B] words) must be zero on entry.  Covers d % 8 == 0,
-// d <= 4096 (d <= 2048 with gb) and 16-byte aligned x / g; returns cudaErrorNotSupported otherwise.
+// ONE launch.  tickets ([B] words) must be zero on entry; part: scratch of dpk_norm_lastdim_psg_scratch_floats()
+// floats (per-block partial sums, added in a fixed order: the results are reproducible bit for bit).  Covers
+// d % 8 == 0, d <= 4096 (d <= 2048 with gb) and 16-byte aligned x / g; returns cudaErrorNotSupported otherwise.
+int64_t dpk_norm_lastdim_psg_scratch_floats(int64_t B, int64_t rows, int64_t d, int with_bias);
 int dpk_norm_lastdim_psg_fused(int kind, const void* x, const void* g, int elem_kind, int64_t B, int64_t rows,
                                int64_t d, float eps, float* gw, float* gb, float* n2w, float* n2b, int accumulate,
-                               unsigned int* tickets, cudaStream_t stream);
+                               unsigned int* tickets, float* part, cudaStream_t stream);
 // kind 2 = GroupNorm / InstanceNorm on [B, C, S] with `groups` groups; gw/gb: [B, C] fp32.
 int dpk_norm_channel_grad(const void* x, const void* g, int elem_kind, int64_t B, int64_t C, int64_t S, int groups,
                           float eps, float* gw, float* gb, cudaStream_t stream);

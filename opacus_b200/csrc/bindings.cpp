@@ -387,18 +387,20 @@ std::vector<at::Tensor> norm_lastdim_psg(int64_t kind, at::Tensor x, at::Tensor 
   const int64_t B = x.size(0), rows = x.numel() / B / d;
   if ((d & 7) || d > 4096 || (want_b && d > 2048) || B > 65535 || B == 0 || rows == 0) return {};
   const int64_t per = B * d;
-  at::Tensor buf = at::zeros({per * (want_b ? 2 : 1) + B * (want_b ? 3 : 2)}, x.options().dtype(at::kFloat));
-  float* base = buf.data_ptr<float>();
-  at::Tensor gw = buf.narrow(0, 0, per).view({B, d});
-  at::Tensor gb = want_b ? buf.narrow(0, per, per).view({B, d}) : at::Tensor();
-  const int64_t tail = per * (want_b ? 2 : 1);
-  at::Tensor n2w = buf.narrow(0, tail, B);
-  at::Tensor n2b = want_b ? buf.narrow(0, tail + B, B) : at::Tensor();
-  unsigned int* tickets = reinterpret_cast<unsigned int*>(base + tail + B * (want_b ? 2 : 1));
+  at::Tensor gw = new_out({B, d}, x.options().dtype(at::kFloat));
+  at::Tensor gb = want_b ? new_out({B, d}, x.options().dtype(at::kFloat)) : at::Tensor();
+  // small zeroed block: the two norm vectors and the ticket counters
+  at::Tensor small = at::zeros({B * 3}, x.options().dtype(at::kFloat));
+  at::Tensor n2w = small.narrow(0, 0, B);
+  at::Tensor n2b = want_b ? small.narrow(0, B, B) : at::Tensor();
+  unsigned int* tickets = reinterpret_cast<unsigned int*>(small.data_ptr<float>() + 2 * B);
+  at::Tensor part = at::empty({dpk_norm_lastdim_psg_scratch_floats(B, rows, d, want_b ? 1 : 0)},
+                              x.options().dtype(at::kFloat));
+  (void)per;
   const int rc = dpk_norm_lastdim_psg_fused((int)kind, x.data_ptr(), g.data_ptr(), elem_kind(x), B, rows, d, (float)eps,
                                             gw.data_ptr<float>(), want_b ? gb.data_ptr<float>() : nullptr,
                                             n2w.data_ptr<float>(), want_b ? n2b.data_ptr<float>() : nullptr, 0, tickets,
-                                            stream());
+                                            part.data_ptr<float>(), stream());
   if (rc == cudaErrorNotSupported) return {};
   check(rc, "norm_lastdim_psg");
   return {gw, gb, n2w, n2b};

@@ -252,14 +252,14 @@ __global__ void lastdim_grad_kernel(const void* x, const void* g, const float2* 
 // the launcher).  grid = (chunks, B); a block takes rows [r0, r1) of sample n, one row per warp at a time:
 //   pass 1 over the row gives mean / rstd, pass 2 (the row is in L1 by then) accumulates xhat * g (and g) in
 //   registers, lane l holding columns 8 * (l + 32 * i) .. + 8;
-// the warps of a block are added in shared memory, blocks are added with atomics into gw / gb (zeroed by the
-// launcher), and the last block of a sample to finish (a ticket counter per sample) squares and sums the complete
-// [d] vectors: n2w[n] / n2b[n] (+= when accumulate).  The counter is left at zero again.
+// the warps of a block are added in shared memory, every block writes its partial [d] vector to scratch, and the
+// last block of a sample to finish (a ticket counter per sample) adds the partial vectors in a fixed order into
+// gw / gb and squares and sums them: n2w[n] / n2b[n] (+= when accumulate).  The counter is left at zero again.
 template <int KIND, int NV, bool BIAS>
 __global__ void __launch_bounds__(256)
 lastdim_psg_fused_kernel(int norm_kind, const void* x, const void* g, int64_t rows, int64_t d, int64_t rows_per_block,
                          float eps, float* gw, float* gb, float* n2w, float* n2b, int accumulate,
-                         unsigned int* tickets) {
+                         unsigned int* tickets, float* part) {
   extern __shared__ float red[];               // [d] (+ [d] with BIAS)
   __shared__ float sh[32];
   __shared__ unsigned int sh_last;
@@ -328,11 +328,11 @@ lastdim_psg_fused_kernel(int norm_kind, const void* x, const void* g, int64_t ro
     }
     __syncthreads();
   }
-  for (int64_t j = threadIdx.x; j < d; j += blockDim.x) {
-    atomicAdd(gw + n * d + j, red[j]);
-    if (BIAS) atomicAdd(gb + n * d + j, red[d + j]);
-  }
-  // the last block of this sample finishes the norms
+  // block -> global: this block's partial sums go to its own row of `part` ([B, chunks, d] (x2 with BIAS)); the last
+  // block of the sample to finish adds the rows in chunk order -- no atomics on the result, same bits on every run
+  const int64_t width = BIAS ? 2 * d : d;
+  float* mine = part + (n * gridDim.x + blockIdx.x) * width;
+  for (int64_t j = threadIdx.x; j < width; j += blockDim.x) mine[j] = red[j];
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -343,10 +343,16 @@ lastdim_psg_fused_kernel(int norm_kind, const void* x, const void* g, int64_t ro
   if (!sh_last) return;
   __threadfence();
   float qw = 0.f, qb = 0.f;
+  const float* all = part + n * gridDim.x * width;
   for (int64_t j = threadIdx.x; j < d; j += blockDim.x) {
-    const float v = __ldcg(gw + n * d + j);
+    float v = 0.f, u = 0.f;
+    for (unsigned int c = 0; c < gridDim.x; ++c) {
+      v += __ldcg(all + c * width + j);
+      if (BIAS) u += __ldcg(all + c * width + d + j);
+    }
+    gw[n * d + j] = v;
     qw = fmaf(v, v, qw);
-    if (BIAS) { const float u = __ldcg(gb + n * d + j); qb = fmaf(u, u, qb); }
+    if (BIAS) { gb[n * d + j] = u; qb = fmaf(u, u, qb); }
   }
   qw = block_sum(qw, sh);
   if (BIAS) qb = block_sum(qb, sh);
@@ -670,19 +676,29 @@ extern "C" int dpk_norm_lastdim_grad(int norm_kind, const void* x, const void* g
   return cudaGetLastError();
 }
 
-// One-launch form: gw (and gb) [B, d] and tickets [B] must be ZERO on entry (one allocation, one memset by the
-// caller).  Returns cudaErrorNotSupported when the shape is outside what the kernel covers
+// One-launch form: tickets [B] must be ZERO on entry; part is scratch of dpk_norm_lastdim_psg_scratch_floats() floats.  Returns cudaErrorNotSupported when the shape is outside what the kernel covers
 // (d % 8, d > 4096, or d > 2048 with a bias) so that the caller can take the two-kernel path.
+// Blocks per sample: two blocks per SM over the whole batch, at least 16 rows (two per warp) per block.
+static int64_t psg_chunks(int64_t B, int64_t rows) {
+  int64_t chunks = ((int64_t)dpk::num_sms() * 2 + B - 1) / B;
+  if (chunks > (rows + 15) / 16) chunks = (rows + 15) / 16;
+  return chunks < 1 ? 1 : chunks;
+}
+
+extern "C" int64_t dpk_norm_lastdim_psg_scratch_floats(int64_t B, int64_t rows, int64_t d, int with_bias) {
+  return B * psg_chunks(B, rows) * d * (with_bias ? 2 : 1);
+}
+
 extern "C" int dpk_norm_lastdim_psg_fused(int norm_kind, const void* x, const void* g, int kind, int64_t B,
                                           int64_t rows, int64_t d, float eps, float* gw, float* gb, float* n2w,
-                                          float* n2b, int accumulate, unsigned int* tickets, cudaStream_t stream) {
+                                          float* n2b, int accumulate, unsigned int* tickets, float* part,
+                                          cudaStream_t stream) {
   if (B <= 0 || rows <= 0 || d <= 0) return 0;
   const bool bias = gb != nullptr;
-  if ((d & 7) || d > 4096 || (bias && d > 2048) || B > 65535 || gw == nullptr) return cudaErrorNotSupported;
+  if ((d & 7) || d > 4096 || (bias && d > 2048) || B > 65535 || gw == nullptr || part == nullptr)
+    return cudaErrorNotSupported;
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g)) & 15) != 0) return cudaErrorNotSupported;
-  int64_t chunks = ((int64_t)num_sms() * 3 + B - 1) / B;
-  if (chunks > (rows + 7) / 8) chunks = (rows + 7) / 8;
-  if (chunks < 1) chunks = 1;
+  int64_t chunks = psg_chunks(B, rows);
   const int64_t rpb = (rows + chunks - 1) / chunks;
   chunks = (rows + rpb - 1) / rpb;
   dim3 grid((unsigned)chunks, (unsigned)B);
@@ -690,7 +706,7 @@ extern "C" int dpk_norm_lastdim_psg_fused(int norm_kind, const void* x, const vo
   const int nv = (int)((d + 255) / 256);
 #define PSG_LAUNCH(NV_, BIAS_)                                                                                   \
   DISPATCH_KIND(kind, (lastdim_psg_fused_kernel<KIND, NV_, BIAS_><<<grid, 256, smem, stream>>>(                  \
-                          norm_kind, x, g, rows, d, rpb, eps, gw, gb, n2w, n2b, accumulate, tickets)))
+                          norm_kind, x, g, rows, d, rpb, eps, gw, gb, n2w, n2b, accumulate, tickets, part)))
   if (bias) {
     if (nv <= 1) { PSG_LAUNCH(1, true); } else if (nv <= 2) { PSG_LAUNCH(2, true); }
     else if (nv <= 4) { PSG_LAUNCH(4, true); } else { PSG_LAUNCH(8, true); }

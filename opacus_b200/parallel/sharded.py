@@ -59,7 +59,8 @@ class ShardedDataParallel(nn.Module):
 
     ``step_pieces``: into how many pieces the flat space is cut (default: 16 with several ranks and a model of
     at least a few million parameters, else 1).  ``multicast``: use the NVLink multicast address of the buffers
-    when there is one (default; ``False`` or ``OPACUS_B200_MULTICAST=0`` keeps plain peer loads and stores)."""
+    when there is one (default: for groups of 4 or more ranks; ``True`` / ``False`` or ``OPACUS_B200_MULTICAST=1`` /
+    ``0`` force it on where available / off)."""
 
     def __init__(self, module: nn.Module, *, param_dtype: torch.dtype = torch.bfloat16, process_group=None,
                  tp_group=None, step_pieces: Optional[int] = None, multicast: Optional[bool] = None,
@@ -137,7 +138,10 @@ class ShardedDataParallel(nn.Module):
         self._flat_grad = symm.alloc(self.total, torch.float32, dev, process_group)
         self._flags = symm.alloc(64, torch.int32, dev, process_group)
         if multicast is None:
-            multicast = os.environ.get("OPACUS_B200_MULTICAST", "1") != "0"
+            # measured on NVLink 5 / NVSwitch: with 2 ranks the in-switch reduction is slower than plain peer loads
+            # (every rank's own copy crosses its link too); from 4 ranks on it is at least as fast
+            env = os.environ.get("OPACUS_B200_MULTICAST", "")
+            multicast = self.world >= 4 if env == "" else env != "0"
         self.multicast = bool(multicast) and self.world > 1 and self._flat_param.mc_ptr != 0 \
             and self._flat_grad.mc_ptr != 0
         if self.world > 1:                 # all ranks take the same path or none

@@ -67,7 +67,7 @@ def main():
 
     used_multicast = False
     for opt_cls, engine_kw in ((torch.optim.AdamW, dict(step_pieces=1, multicast=False)),
-                               (torch.optim.AdamW, dict(step_pieces=4)),
+                               (torch.optim.AdamW, dict(step_pieces=4, multicast=True)),
                                (torch.optim.SGD, dict(step_pieces=4))):
         eng, gsm, opt, crit = build(None, B, 0.0, opt_cls, **engine_kw)
         run(gsm, opt, crit, mine, 3)

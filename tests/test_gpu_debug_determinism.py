@@ -91,6 +91,12 @@ def test_ghost_norm_kernels_are_bitwise_reproducible():
         again = [ops.linear_norm_sq(a, g, True, True), ops.embedding_norm_sq(ids, g)]
         assert torch.equal(first[0][0], again[0][0]) and torch.equal(first[0][1], again[0][1])
         assert torch.equal(first[1], again[1])
+    # LayerNorm / RMSNorm rule: per-block partial sums added in chunk order
+    xs = torch.randn(4, 1024, 2048, device="cuda").bfloat16()
+    gn = torch.randn_like(xs)
+    w1, _ = ops.norm_affine_grad_sample("rms", xs, gn, eps=1e-5, normalized_ndim=1, want_bias=False)
+    w2, _ = ops.norm_affine_grad_sample("rms", xs, gn, eps=1e-5, normalized_ndim=1, want_bias=False)
+    assert torch.equal(w1, w2) and torch.equal(w1._dp_norm_sq, w2._dp_norm_sq)
     # per-sample gradients of the batched kernel (no K split, no atomics on the output)
     gs1, gs2 = ops.linear_grad_sample(a, g), ops.linear_grad_sample(a, g)
     assert torch.equal(gs1, gs2)
