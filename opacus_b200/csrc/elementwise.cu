@@ -344,15 +344,33 @@ lastdim_psg_fused_kernel(int norm_kind, const void* x, const void* g, int64_t ro
   __threadfence();
   float qw = 0.f, qb = 0.f;
   const float* all = part + n * gridDim.x * width;
-  for (int64_t j = threadIdx.x; j < d; j += blockDim.x) {
-    float v = 0.f, u = 0.f;
-    for (unsigned int c = 0; c < gridDim.x; ++c) {
-      v += __ldcg(all + c * width + j);
-      if (BIAS) u += __ldcg(all + c * width + d + j);
+  // width is a multiple of 8: 16-byte loads, four partial rows in flight per thread
+  for (int64_t j4 = threadIdx.x; j4 < (width >> 2); j4 += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    unsigned int c = 0;
+    for (; c + 4 <= gridDim.x; c += 4) {
+      const float4 v0 = __ldcg(reinterpret_cast<const float4*>(all + (c + 0) * width) + j4);
+      const float4 v1 = __ldcg(reinterpret_cast<const float4*>(all + (c + 1) * width) + j4);
+      const float4 v2 = __ldcg(reinterpret_cast<const float4*>(all + (c + 2) * width) + j4);
+      const float4 v3 = __ldcg(reinterpret_cast<const float4*>(all + (c + 3) * width) + j4);
+      acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;       // chunk order: same bits on every run
+      acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+      acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+      acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
     }
-    gw[n * d + j] = v;
-    qw = fmaf(v, v, qw);
-    if (BIAS) { gb[n * d + j] = u; qb = fmaf(u, u, qb); }
+    for (; c < gridDim.x; ++c) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(all + c * width) + j4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int64_t j = j4 << 2;
+    const float sq = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    if (!BIAS || j < d) {
+      *reinterpret_cast<float4*>(gw + n * d + j) = acc;
+      qw += sq;
+    } else {
+      *reinterpret_cast<float4*>(gb + n * d + (j - d)) = acc;
+      qb += sq;
+    }
   }
   qw = block_sum(qw, sh);
   if (BIAS) qb = block_sum(qb, sh);
