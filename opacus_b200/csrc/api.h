@@ -19,6 +19,14 @@ int dpk_gram_pair_norm(const void* x, const int64_t* ids, const void* g, int B, 
                        float* scratch, float* out_w, float* out_b, int accumulate, uint32_t* status,
                        cudaStream_t stream);
 
+// The same with distinct left / right operands of each Gram product: x, g are [B, 2 * right_off, d]; rows [0, T) of a
+// sample are the left operand, rows [right_off, right_off + T) the right one (right_off a multiple of 128, >= T,
+// rows in between zero).  L R^T must be symmetric, as it is for the planes (hi, hi, lo) x (hi, lo, hi) of an fp32
+// operand split into bf16 parts stacked along d.
+int dpk_gram_pair_norm_lr(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g,
+                          int right_off, float scale, float* scratch, float* out_w, float* out_b, int accumulate,
+                          uint32_t* status, cudaStream_t stream);
+
 // ---- clipped weight gradient: out[M, N] = beta*out + sum_k Gs[k, m] * A[k, n]   (bf16 in, fp32 accumulate)
 // gs: [K, M] bf16 row-major, a: [K, N] bf16 row-major, out: [M, N] fp32 or bf16 (out_bf16 != 0).
 int dpk_wgrad_tn(const void* gs, const void* a, int K, int M, int N, void* out, int out_bf16, float beta,

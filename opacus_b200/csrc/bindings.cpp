@@ -108,17 +108,21 @@ cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 // x: [B,T,dx] bf16 or None; ids: [B,T] int64 or None; g: [B,T,dg] bf16.
 void gram_pair_norm(c10::optional<at::Tensor> x, c10::optional<at::Tensor> ids, at::Tensor g, double scale,
                     at::Tensor scratch, c10::optional<at::Tensor> out_w, c10::optional<at::Tensor> out_b,
-                    bool accumulate) {
+                    bool accumulate, int64_t right_off, int64_t logical_T) {
   c10::cuda::CUDAGuard guard(g.device());
   raise_if_failed(g.get_device());
   need_cuda_contig(g, "g");
   TORCH_CHECK(g.dim() == 3 && g.scalar_type() == at::kBFloat16, "g must be [B,T,d] bf16");
-  const int B = g.size(0), T = g.size(1), dg = g.size(2);
+  // right_off > 0: tensors are [B, 2 * right_off, d] (left rows, then right rows) and logical_T is the true T
+  TORCH_CHECK(right_off == 0 || (g.size(1) == 2 * right_off && logical_T > 0 && logical_T <= right_off),
+              "with right_off the operands must have 2 * right_off rows per sample");
+  const int B = g.size(0), T = right_off > 0 ? (int)logical_T : (int)g.size(1), dg = g.size(2);
+  const int rows_in = g.size(1);
   const void* xp = nullptr;
   int dx = 0;
   if (x.has_value()) {
     need_cuda_contig(*x, "x");
-    TORCH_CHECK(x->dim() == 3 && x->scalar_type() == at::kBFloat16 && x->size(0) == B && x->size(1) == T,
+    TORCH_CHECK(x->dim() == 3 && x->scalar_type() == at::kBFloat16 && x->size(0) == B && x->size(1) == rows_in,
                 "x must be [B,T,d] bf16");
     xp = x->data_ptr();
     dx = x->size(2);
@@ -134,8 +138,9 @@ void gram_pair_norm(c10::optional<at::Tensor> x, c10::optional<at::Tensor> ids, 
               "scratch too small");
   float* ow = out_w.has_value() ? out_w->data_ptr<float>() : nullptr;
   float* ob = out_b.has_value() ? out_b->data_ptr<float>() : nullptr;
-  check(dpk_gram_pair_norm(xp, idp, g.data_ptr(), B, T, dx, dg, (float)scale, scratch.data_ptr<float>(), ow, ob,
-                           accumulate ? 1 : 0, status_for(g.get_device()).dev, stream()),
+  check(dpk_gram_pair_norm_lr(xp, idp, g.data_ptr(), B, T, dx, dg, (int)right_off, (float)scale,
+                              scratch.data_ptr<float>(), ow, ob, accumulate ? 1 : 0, status_for(g.get_device()).dev,
+                              stream()),
         "gram_pair_norm");
 }
 
@@ -718,7 +723,9 @@ int64_t tensor_entry_size() { return (int64_t)sizeof(DpkTensorEntry); }
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gram_pair_norm", &gram_pair_norm);
+  m.def("gram_pair_norm", &gram_pair_norm, py::arg("x"), py::arg("ids"), py::arg("g"), py::arg("scale"),
+        py::arg("scratch"), py::arg("out_w"), py::arg("out_b"), py::arg("accumulate"), py::arg("right_off") = 0,
+        py::arg("logical_T") = 0);
   m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
   m.def("wgrad_tn", &wgrad_tn);
   m.def("wgrad_tn_ex", &wgrad_tn_ex);

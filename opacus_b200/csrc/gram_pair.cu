@@ -41,6 +41,8 @@ struct GramParams {
   int64_t V;
   int gather_fp32;
   int want_w, want_b;
+  int right_off;           // > 0: the column tiles are read right_off rows further down (the operands hold a "left"
+                           // block of rows followed by a "right" block per sample: split fp32 operands)
   float* scratch;          // [items][2]
   const int64_t* ids;      // [B, T] when mask_mode
   uint32_t* status;
@@ -139,7 +141,8 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           uint8_t* dst = smem + stage * kStageBytes;
           mbar_expect_tx(&bars->full[stage], kStageBytes);
           tma_load_3d(dst, map, &bars->full[stage], k0, tb * kTile, n);
-          tma_load_3d(dst + kTileBytes, p.cross_mode ? &map_g : map, &bars->full[stage], k0, sb * kTile, n);
+          tma_load_3d(dst + kTileBytes, p.cross_mode ? &map_g : map, &bars->full[stage], k0,
+                      sb * kTile + (p.cross_mode ? 0 : p.right_off), n);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -318,12 +321,28 @@ extern "C" size_t dpk_gram_pair_scratch_floats(int B, int T) {
   return 2 * static_cast<size_t>(B) * (nT * (nT + 1) / 2);
 }
 
+int dpk_gram_pair_launch_lr(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g,
+                            int right_off, float scale, float* scratch, float* out_w, float* out_b, int accumulate,
+                            uint32_t* status, cudaStream_t stream);
+
 int dpk_gram_pair_launch(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g, float scale,
                          float* scratch, float* out_w, float* out_b, int accumulate, uint32_t* status,
                          cudaStream_t stream) {
+  return dpk_gram_pair_launch_lr(x, ids, g, B, T, d_x, d_g, 0, scale, scratch, out_w, out_b, accumulate, status, stream);
+}
+
+// right_off > 0: x and g are [B, 2 * right_off, d] with rows [0, T) the left operand and rows
+// [right_off, right_off + T) the right operand of each Gram product (rows in between zero); right_off is a
+// multiple of 128 and at least T.  The products L R^T must be symmetric (they are for split fp32 operands).
+int dpk_gram_pair_launch_lr(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g,
+                            int right_off, float scale, float* scratch, float* out_w, float* out_b, int accumulate,
+                            uint32_t* status, cudaStream_t stream) {
   if (B <= 0 || T <= 0 || d_g <= 0 || (d_g % 8) != 0 || (x != nullptr && (d_x <= 0 || (d_x % 8) != 0)))
     return cudaErrorInvalidValue;
+  if (right_off < 0 || (right_off > 0 && ((right_off % kTile) != 0 || right_off < T))) return cudaErrorInvalidValue;
+  const int rows = right_off > 0 ? 2 * right_off : T;
   GramParams p{};
+  p.right_off = right_off;
   p.B = B;
   p.T = T;
   p.nT = (T + kTile - 1) / kTile;
@@ -339,10 +358,10 @@ int dpk_gram_pair_launch(const void* x, const int64_t* ids, const void* g, int B
   p.status = status;
 
   CUtensorMap map_x, map_g;
-  int rc = make_tmap_3d_bf16(&map_g, g, d_g, T, B, kBK, kTile);
+  int rc = make_tmap_3d_bf16(&map_g, g, d_g, rows, B, kBK, kTile);
   if (rc) return rc;
   if (x) {
-    rc = make_tmap_3d_bf16(&map_x, x, d_x, T, B, kBK, kTile);
+    rc = make_tmap_3d_bf16(&map_x, x, d_x, rows, B, kBK, kTile);
     if (rc) return rc;
   } else {
     map_x = map_g;
@@ -370,6 +389,13 @@ extern "C" int dpk_gram_pair_norm(const void* x, const int64_t* ids, const void*
                                   float scale, float* scratch, float* out_w, float* out_b, int accumulate,
                                   uint32_t* status, cudaStream_t stream) {
   return dpk_gram_pair_launch(x, ids, g, B, T, d_x, d_g, scale, scratch, out_w, out_b, accumulate, status, stream);
+}
+
+extern "C" int dpk_gram_pair_norm_lr(const void* x, const int64_t* ids, const void* g, int B, int T, int d_x, int d_g,
+                                     int right_off, float scale, float* scratch, float* out_w, float* out_b,
+                                     int accumulate, uint32_t* status, cudaStream_t stream) {
+  return dpk_gram_pair_launch_lr(x, ids, g, B, T, d_x, d_g, right_off, scale, scratch, out_w, out_b, accumulate, status,
+                                 stream);
 }
 
 // 2 <g_E, g_H> of a weight shared by an embedding (ids, output gradient g_e [B, T, D]) and an output projection

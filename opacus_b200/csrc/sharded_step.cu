@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(kShThreads, WORLD == 1 ? 2 : 1) sharded_step_k
     DpkStepHyper h = p.h;
     const Philox rng(h.seed);
     const int64_t nvec = p.slice_len >> 3;
-    const bool wide = ((p.slice_len | p.stripe_len) & 255) == 0;
+    // (with one rank everything is local and cached: consecutive elements per thread are slightly faster there)
+    const bool wide = WORLD != 1 && ((p.slice_len | p.stripe_len) & 255) == 0;
     const bool has_m = p.state0 != nullptr && (h.kind != 0 || h.momentum != 0.f);
     for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
       int64_t li[2], gi[2];            // index inside the owned share covered by this launch / in the flat space

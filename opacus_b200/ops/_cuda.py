@@ -130,6 +130,21 @@ def _split_pair(g3, a3, c=None, g_scale: float = 1.0):
     return gl, ar
 
 
+def _split_lr(t3):
+    """fp32 ``[B, T, d]`` -> (bf16 ``[B, 2 * Tp, 3d]``, Tp): rows ``[0, T)`` hold the planes (hi, hi, lo) side by
+    side, rows ``[Tp, Tp + T)`` the planes (hi, lo, hi), everything else zero (Tp = T rounded up to 128).  The Gram
+    kernel multiplies the first block by the transposed second one: ``hi hi^T + hi lo^T + lo hi^T``."""
+    B, T, d = t3.shape
+    Tp = (T + 127) // 128 * 128
+    x = t3.float()
+    hi = x.bfloat16()
+    lo = (x - hi.float()).bfloat16()
+    buf = torch.zeros(B, 2 * Tp, 3 * d, dtype=torch.bfloat16, device=t3.device)
+    buf[:, :T, :d], buf[:, :T, d:2 * d], buf[:, :T, 2 * d:] = hi, hi, lo
+    buf[:, Tp:Tp + T, :d], buf[:, Tp:Tp + T, d:2 * d], buf[:, Tp:Tp + T, 2 * d:] = hi, lo, hi
+    return buf, Tp
+
+
 # ----------------------------------------------------------------------- Linear
 def linear_grad_sample(a, g):
     """``[B, d_out, d_in]`` per-sample gradients (dtype of ``g``) by the batched
@@ -278,7 +293,7 @@ def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] =
     ids2 = ids.reshape(B, -1)
     T = ids2.shape[1]
     g3 = g.reshape(B, T, -1)
-    if padding_idx is not None or g3.dtype != torch.bfloat16 or g3.shape[-1] % 8:
+    if padding_idx is not None or g3.dtype not in (torch.bfloat16, torch.float32) or g3.shape[-1] % 8:
         w = _ref.embedding_norm_sq(ids, g, g_scale, padding_idx)
         if total is not None:
             total.add_(w)
@@ -287,6 +302,12 @@ def embedding_norm_sq(ids, g, g_scale: float = 1.0, padding_idx: Optional[int] =
     C = load()
     w = total if total is not None else _out(B, dtype=torch.float32, device=g.device)
     scratch = _scratch_for(g.device, C.gram_pair_scratch_floats(B, T))
+    if g3.dtype == torch.float32:
+        # fp32 gradients: the same mask-Gram kernel on the three-plane split (left rows x right rows)
+        both, Tp = _split_lr(g3)
+        C.gram_pair_norm(None, ids2.contiguous().long(), both, float(g_scale) ** 2, scratch, w, None,
+                         total is not None, Tp, T)
+        return None if total is not None else w
     C.gram_pair_norm(None, ids2.contiguous().long(), g3.contiguous(), float(g_scale) ** 2, scratch, w, None,
                      total is not None)
     return None if total is not None else w

@@ -55,6 +55,19 @@ def test_embedding_ghost_norm(B, T, D, V):
     ops._cuda.check_status()
 
 
+@pytest.mark.parametrize("B,T,D,V", [(3, 128, 64, 50), (2, 200, 128, 1000), (4, 77, 40, 9)])
+def test_embedding_ghost_norm_fp32_through_split_operands(B, T, D, V):
+    """fp32 gradients: the mask-Gram kernel on (hi, hi, lo) x (hi, lo, hi) planes agrees with fp64 far inside bf16."""
+    torch.manual_seed(0)
+    ids = torch.randint(0, V, (B, T), device=_dev())
+    g = torch.randn(B, T, D, device=_dev()) * 0.1
+    got = ops.embedding_norm_sq(ids, g, g_scale=2.0)
+    dense = _ref.embedding_grad_sample(ids, g.double() * 2.0, V)
+    want = dense.pow(2).sum(dim=(1, 2))
+    assert _rel(got.double(), want) < 1e-4, (got, want)
+    ops._cuda.check_status()
+
+
 @pytest.mark.parametrize("B,T,din,dout", [(2, 128, 64, 128), (3, 100, 72, 40), (4, 256, 256, 512), (2, 64, 512, 1000),
                                            (8, 1024, 2048, 512)])
 @pytest.mark.parametrize("bias", [False, True])
