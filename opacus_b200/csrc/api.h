@@ -32,6 +32,11 @@ int dpk_gram_pair_norm_lr(const void* x, const int64_t* ids, const void* g, int 
 int dpk_wgrad_tn(const void* gs, const void* a, int K, int M, int N, void* out, int out_bf16, float beta,
                  uint32_t* status, cudaStream_t stream);
 
+// The same product on pairs of SMs (tcgen05 cta_group::2, clusters of two CTAs per 256 x 256 tile, double-buffered
+// accumulators): fp32 out, beta in {0, 1} when splits > 1.
+int dpk_wgrad2_tn(const void* gs, const void* a, int K, int M, int N, float* out, float beta, int splits,
+                  uint32_t* status, cudaStream_t stream);
+
 // Batched / tunable form: gs [batch, K, M], a [batch, K, N], out [batch, M, N]; norm_sq (or NULL) receives
 // += ||out[b]||_F^2 per batch entry (fp32 atomics; only without K splitting).  force_* = 0 lets the
 // launcher choose tile shape (256x256, 128x256, 128x128) and K split (1, 2, 4, 8).

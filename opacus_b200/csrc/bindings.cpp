@@ -163,6 +163,23 @@ void wgrad_tn(at::Tensor gs, at::Tensor a, at::Tensor out, double beta) {
         "wgrad_tn");
 }
 
+// The pair-of-SMs form of wgrad_tn (fp32 out only); splits = 0 lets the binding choose.
+void wgrad2_tn(at::Tensor gs, at::Tensor a, at::Tensor out, double beta, int64_t splits) {
+  c10::cuda::CUDAGuard guard(gs.device());
+  raise_if_failed(gs.get_device());
+  need_cuda_contig(gs, "gs");
+  need_cuda_contig(a, "a");
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(gs.dim() == 2 && a.dim() == 2 && gs.size(0) == a.size(0), "gs [K,M] and a [K,N] expected");
+  TORCH_CHECK(gs.scalar_type() == at::kBFloat16 && a.scalar_type() == at::kBFloat16, "bf16 operands expected");
+  const int K = gs.size(0), M = gs.size(1), N = a.size(1);
+  TORCH_CHECK(out.numel() == (int64_t)M * N && out.scalar_type() == at::kFloat, "out must be fp32 with M*N elements");
+  if (splits <= 0) splits = 1;
+  check(dpk_wgrad2_tn(gs.data_ptr(), a.data_ptr(), K, M, N, out.data_ptr<float>(), (float)beta, (int)splits,
+                      status_for(gs.get_device()).dev, stream()),
+        "wgrad2_tn");
+}
+
 // gs [batch, K, M] (or [K, M]), a [batch, K, N] (or [K, N]) bf16; out [batch, M, N]; norm_sq optional fp32 [batch]
 void wgrad_tn_ex(at::Tensor gs, at::Tensor a, c10::optional<at::Tensor> out_opt, double beta,
                  c10::optional<at::Tensor> norm_sq, int64_t force_bm, int64_t force_bn, int64_t force_splits) {
@@ -729,6 +746,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gram_pair_scratch_floats", &gram_pair_scratch_floats);
   m.def("wgrad_tn", &wgrad_tn);
   m.def("wgrad_tn_ex", &wgrad_tn_ex);
+  m.def("wgrad2_tn", &wgrad2_tn);
   m.def("conv_psg", &conv_psg);
   m.def("tied_cross_norm", &tied_cross_norm);
   m.def("scale_rows", &scale_rows);

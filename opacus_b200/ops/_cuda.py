@@ -12,6 +12,7 @@ products' cost.  The bandwidth-bound kernels are dtype generic.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import numpy as np
@@ -20,6 +21,7 @@ import torch
 from . import _ref
 
 _C = None
+_USE_PAIR_GEMM = os.environ.get("OPACUS_B200_PAIR_GEMM", "0") == "1"
 _scratch: Dict[tuple, torch.Tensor] = {}
 
 
@@ -278,6 +280,9 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
             out.add_(target) if accumulate else out.copy_(target)
         else:
             out = target
+    elif _USE_PAIR_GEMM and d_out >= 256 and d_in >= 256:
+        # the same product on pairs of SMs (cta_group::2); measured equal to the one-CTA 256 x 256 tile, kept selectable
+        C.wgrad2_tn(g_op, a_op, out, 1.0 if accumulate else 0.0, 1)
     else:
         C.wgrad_tn(g_op, a_op, out, 1.0 if accumulate else 0.0)
     bias = None

@@ -648,7 +648,21 @@ class ShardedDataParallel(nn.Module):
             h.update(beta1=float(b1), beta2=float(b2), eps=float(g0["eps"]), bias_c1=1.0 - float(b1) ** t,
                      bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
             kcode = 2 if kind == "adamw" else 1
-        segments = self._segment_table(inner, per_group) if per_group is not None else None
+        runs = self._ready_runs(had_fresh) if self.overlap_step else None
+        side = None
+        if runs is not None:
+            side = self._step_stream
+            if side is None:
+                side = self._step_stream = torch.cuda.Stream(device=dev)
+        # The table of per-group ranges is uploaded on the stream that will run the step: the main stream still holds
+        # every weight-gradient GEMM of this pass, and waiting for it would undo the overlap of the pieces.
+        if per_group is None:
+            segments = None
+        elif side is not None:
+            with torch.cuda.stream(side):
+                segments = self._segment_table(inner, per_group)
+        else:
+            segments = self._segment_table(inner, per_group)
 
         # per-worker expected batch (times accumulated batches in hooks mode), summed over the workers
         denom = float(dpopt._grad_denominator()) * (self.world if dpopt.loss_reduction == "mean" else 1)
@@ -695,16 +709,15 @@ class ShardedDataParallel(nn.Module):
                               offset, self.noise_split if noise_shift else 0, noise_shift, grad_mc, param_mc,
                               segments, max_blocks, self.stripe if n_pieces > 1 else 0, self.piece_len)
 
-        runs = self._ready_runs(had_fresh) if self.overlap_step and not secure else None
+        if secure:
+            runs = None                       # the host-side noise was added on the main stream, behind all GEMMs
         if runs is None:
             launch(0, self.pieces, self.single_launch_blocks)
             self.last_step_launches = 1
         else:
+            # Nothing this method queued on the main stream concerns the pieces (no gradient was zero-filled: that
+            # case takes the one-launch path), so the side stream waits for the events of the writes only.
             main = torch.cuda.current_stream(dev)
-            side = self._step_stream
-            if side is None:
-                side = self._step_stream = torch.cuda.Stream(device=dev)
-            side.wait_stream(main)            # what this method queued on the main stream so far
             cap = int(os.environ.get("OPACUS_B200_OVERLAP_BLOCKS", "0")) or (
                 self.overlap_blocks_multicast if self.multicast else self.overlap_blocks_peer)
             for k, (first_piece, n_pieces, events) in enumerate(runs):

@@ -426,6 +426,28 @@ def test_conv_kernel_coverage_beyond_plain_bf16(cfg):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("K,M,N,splits,beta", [(64, 256, 256, 1, 0.0), (1024, 512, 768, 1, 0.0), (300, 264, 200, 1, 0.0),
+                                                (4096, 512, 2048, 4, 0.0), (2048, 256, 512, 2, 1.0),
+                                                (128, 128, 64, 1, 1.0), (8192, 2048, 2048, 1, 0.0)])
+def test_wgrad_on_sm_pairs(K, M, N, splits, beta):
+    """The cta_group::2 form of the clipped-sum GEMM (clusters of two CTAs per 256 x 256 tile) against fp32 torch and,
+    without a K split, bit for bit against the one-CTA kernel."""
+    C = ops._cuda.load()
+    torch.manual_seed(0)
+    gs = (torch.randn(K, M, device=_dev()) * 0.1).bfloat16()
+    a = torch.randn(K, N, device=_dev()).bfloat16()
+    start = torch.randn(M, N, device=_dev())
+    out = start.clone()
+    C.wgrad2_tn(gs, a, out, beta, splits)
+    ref = gs.float().t() @ a.float() + beta * start
+    assert _rel(out, ref) < 1e-4
+    if splits == 1:
+        one = start.clone()
+        C.wgrad_tn_ex(gs, a, one, beta, None, 256, 256, 1)
+        assert torch.equal(out, one)
+    ops._cuda.check_status()
+
+
 @pytest.mark.parametrize("B,T,din,dout", [(4, 128, 512, 512), (3, 50, 72, 40), (2, 1024, 256, 128)])
 def test_fp32_linear_rules_run_on_split_bf16_operands(B, T, din, dout):
     """fp32 activations and gradients: per-sample gradient, ghost norm and clipped sum through the three-plane
