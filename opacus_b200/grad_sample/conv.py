@@ -47,7 +47,8 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
 
         out = {}
         if layer.weight.requires_grad:
-            out[layer.weight] = _cuda.conv_grad_sample(x, backprops, geom)
+            out[layer.weight] = (_conv3d_grad_sample(layer, x, backprops, geom) if x.dim() == 5
+                                 else _cuda.conv_grad_sample(x, backprops, geom))
         if want_b:
             out[layer.bias] = backprops.reshape(n, O, -1).sum(dim=2)
         return out
@@ -87,19 +88,92 @@ def compute_conv_grad_sample(layer: Union[nn.Conv1d, nn.Conv2d, nn.Conv3d], acti
 
 
 def _implicit_geometry(layer, x, backprops):
-    """Geometry tuple when the implicit-unfold CUDA kernel covers this call, else None."""
-    if not x.is_cuda or backprops.dtype not in (torch.bfloat16, torch.float32) or _base_type(layer) is nn.Conv3d:
+    """Geometry tuple when the implicit-unfold CUDA kernel covers this call, else None.  A Conv3d is covered through
+    its depth-stacked 2-d form (:func:`depth_stacked_pairs`); its tuple is the plan of those 2-d problems."""
+    if not x.is_cuda or backprops.dtype not in (torch.bfloat16, torch.float32):
         return None
     from ..ops import _cuda
 
+    if _base_type(layer) is nn.Conv3d:
+        if getattr(layer, "padding_mode", "zeros") != "zeros" or x.dim() != 5:
+            return None
+        return _cuda.conv_plan2d(layer.kernel_size[1:], layer.stride[1:], (0, 0), layer.dilation[1:], layer.groups,
+                                 None, backprops.shape[-1], backprops.dtype == torch.float32)
     return _cuda.conv_geometry(layer, x, backprops)
+
+
+def _explicit_pads(layer):
+    """``[(low, high)]`` zero padding per spatial axis, whatever form ``layer.padding`` has."""
+    pad = layer.padding
+    if isinstance(pad, str):
+        if pad == "valid":
+            return [(0, 0)] * len(layer.kernel_size)
+        tot = [d * (k - 1) for k, d in zip(layer.kernel_size, layer.dilation)]
+        return [(t // 2, t - t // 2) for t in tot]
+    return [(int(p), int(p)) for p in pad]
+
+
+def depth_stacked_pairs(layer: nn.Conv3d, x: torch.Tensor, backprops: torch.Tensor):
+    """A Conv3d weight gradient as ``kernel_depth`` Conv2d weight gradients.
+
+    For the kernel's depth offset ``a`` the gradient slice ``grad[:, :, a]`` is
+    ``sum_d conv2d_weight(x_pad[:, :, d * stride_d + a * dilation_d], backprops[:, :, d])``.  The sum over output depth
+    is folded into the image: the ``D_out`` input slices are laid one under the other (each padded to a height that is
+    a multiple of the stride, so that output rows of different slices never mix) and so are the output-gradient
+    slices (with zero rows where a slice has fewer output rows than its pitch).  Yields
+    ``(a, x2d [B, C, D_out * pitch, W_pad], g2d [B, O, rows, W_out])``; the 2-d problem has the layer's in-plane kernel,
+    stride and dilation and no padding.  Values are exact (only zeros are added)."""
+    kd, kh, _ = layer.kernel_size
+    sd, sh, _ = layer.stride
+    dd, dh, _ = layer.dilation
+    pads = _explicit_pads(layer)
+    xp = F.pad(x, [v for lr in reversed(pads) for v in lr]) if any(v for lr in pads for v in lr) else x
+    B, C, _, Hp, Wp = xp.shape
+    _, O, Do, Ho, Wo = backprops.shape
+    pitch = -(-Hp // sh) * sh
+    rows = pitch // sh
+    g2 = F.pad(backprops, (0, 0, 0, rows - Ho)) if rows != Ho else backprops
+    g2 = g2.reshape(B, O, Do * rows, Wo)
+    g2 = g2[:, :, :(Do * pitch - dh * (kh - 1) - 1) // sh + 1]          # what a 2-d convolution of the stack puts out
+    for a in range(kd):
+        xs = xp[:, :, a * dd: a * dd + (Do - 1) * sd + 1: sd]
+        if pitch != Hp:
+            xs = F.pad(xs, (0, 0, 0, pitch - Hp))
+        yield a, xs.reshape(B, C, Do * pitch, Wp), g2
+
+
+def _conv3d_grad_sample(layer, x, backprops, plan, want_out=True):
+    """Per-sample Conv3d weight gradients (and their squared norms) on the 2-d implicit-unfold kernel."""
+    from ..ops import _cuda
+
+    norm = torch.zeros(x.shape[0], dtype=torch.float32, device=x.device)
+    slices = []
+    for _, x2, g2 in depth_stacked_pairs(layer, x, backprops):
+        if want_out:
+            gs = _cuda.conv_grad_sample(x2, g2, plan)
+            norm += gs._dp_norm_sq
+            slices.append(gs)
+        else:
+            _cuda.conv_grad_sample(x2, g2, plan, want_out=False, norm_total=norm)
+    if not want_out:
+        return norm
+    out = torch.stack(slices, dim=3)                    # [B, O, C/groups, kd, kh, kw]
+    out._dp_norm_sq = norm
+    return out
+
+
+def _conv3d_weighted_grad(layer, x, backprops, coef, plan, g_scale):
+    from ..ops import _cuda
+
+    return torch.stack([_cuda.conv_weighted_grad(x2, g2, coef, plan, g_scale)
+                        for _, x2, g2 in depth_stacked_pairs(layer, x, backprops)], dim=2)
 
 
 @register_norm_sq_sampler(_CONVS)
 def compute_conv_norm_sq(layer, activations, backprops, g_scale: float = 1.0, total=None):
-    """Squared per-sample gradient norms of a conv layer.  On the GPU (bf16, 1-d/2-d, up to 8
-    groups) the per-sample gradient tiles are formed in tensor memory and squared
-    there, never written; otherwise the gradients are instantiated
+    """Squared per-sample gradient norms of a conv layer.  On the GPU (bf16 or fp32 data, up to 8
+    groups; 3-d layers through their depth-stacked 2-d form) the per-sample gradient tiles are formed in tensor
+    memory and squared there, never written; otherwise the gradients are instantiated
     (``opacus/grad_sample/grad_sample_module_fast_gradient_clipping.py:226-250``)."""
     x = activations[0]
     n = x.shape[0]
@@ -111,7 +185,9 @@ def compute_conv_norm_sq(layer, activations, backprops, g_scale: float = 1.0, to
         from ..ops import _cuda
 
         if want_w:
-            out[layer.weight] = _cuda.conv_grad_sample(x, backprops, geom, want_out=False) * (g_scale * g_scale)
+            n2 = (_conv3d_grad_sample(layer, x.to(backprops.dtype), backprops, geom, want_out=False) if x.dim() == 5
+                  else _cuda.conv_grad_sample(x, backprops, geom, want_out=False))
+            out[layer.weight] = n2 * (g_scale * g_scale)
         if want_b:
             out[layer.bias] = (backprops.reshape(n, layer.out_channels, -1).sum(dim=2).float() * g_scale).square().sum(dim=1)
     else:
@@ -136,7 +212,8 @@ def compute_conv_weighted_grad(layer, activations, backprops, coef, g_scale: flo
 
         out = {}
         if layer.weight.requires_grad:
-            out[layer.weight] = _cuda.conv_weighted_grad(x, backprops, coef, geom, g_scale)
+            out[layer.weight] = (_conv3d_weighted_grad(layer, x.to(backprops.dtype), backprops, coef, geom, g_scale)
+                                 if x.dim() == 5 else _cuda.conv_weighted_grad(x, backprops, coef, geom, g_scale))
         if layer.bias is not None and layer.bias.requires_grad:
             per = backprops.reshape(backprops.shape[0], backprops.shape[1], -1).sum(dim=2).float()
             out[layer.bias] = (per * (coef.float() * g_scale)[:, None]).sum(dim=0)

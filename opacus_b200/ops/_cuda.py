@@ -424,7 +424,8 @@ def conv_geometry(layer, x, backprops):
     Conv1d / Conv2d call, else None.  Covered: bf16 and fp32 data (fp32 as three bf16 passes over split operands),
     any channel counts (padded with zero channels to multiples of 8), up to 8 groups (one call per group; more,
     e.g. depthwise, stay on the batched-GEMM path), zero padding including ``"same"`` with an odd total (the input is
-    padded explicitly first).  Not covered: 3-d convolutions, non-zero padding modes, strides above 8."""
+    padded explicitly first).  A Conv3d reaches the kernel as one 2-d problem per kernel-depth offset
+    (``grad_sample/conv.py``: ``depth_stacked_pairs``).  Not covered: non-zero padding modes, strides above 8."""
     nsp = x.dim() - 2
     if nsp not in (1, 2) or backprops.dtype not in (torch.bfloat16, torch.float32) or not x.is_cuda:
         return None
@@ -446,14 +447,18 @@ def conv_geometry(layer, x, backprops):
     k, s, d = tuple(layer.kernel_size), tuple(layer.stride), tuple(layer.dilation)
     if nsp == 1:
         k, s, pad, d = (1,) + k, (1,) + s, (0,) + tuple(pad), (1,) + d
-    ow = backprops.shape[-1]
+    return conv_plan2d(k, s, pad, d, layer.groups, prepad, backprops.shape[-1], backprops.dtype == torch.float32)
+
+
+def conv_plan2d(k, s, pad, d, groups, prepad, out_width, fp32):
+    """The plan tuple of a 2-d problem given as numbers, or None when the kernel's pixel boxes cannot cover the strides."""
     bw = 1
-    while bw < ow and bw < 64:
+    while bw < out_width and bw < 64:
         bw *= 2
-    if max(s) > 8 or bw * s[1] > 256 or (64 // bw) * s[0] > 256:
+    if max(s) > 8 or bw * s[1] > 256 or (64 // bw) * s[0] > 256 or groups > _MAX_GROUP_CALLS:
         return None
-    return (k[0], k[1], s[0], s[1], int(pad[0]), int(pad[1]), d[0], d[1], int(layer.groups), prepad,
-            backprops.dtype == torch.float32)
+    return (int(k[0]), int(k[1]), int(s[0]), int(s[1]), int(pad[0]), int(pad[1]), int(d[0]), int(d[1]), int(groups),
+            prepad, bool(fp32))
 
 
 def _nhwc(t):

@@ -426,6 +426,48 @@ def test_conv_kernel_coverage_beyond_plain_bf16(cfg):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [
+    dict(C=16, O=24, size=(6, 10, 12), k=3, s=1, p=1, d=1, groups=1, dtype=torch.bfloat16),
+    dict(C=8, O=16, size=(7, 9, 8), k=(2, 3, 3), s=(2, 2, 1), p=(1, 0, 2), d=1, groups=1, dtype=torch.bfloat16),
+    dict(C=16, O=16, size=(6, 8, 9), k=(3, 2, 3), s=(1, 3, 2), p=(2, 1, 1), d=(2, 1, 1), groups=2, dtype=torch.bfloat16),
+    dict(C=3, O=8, size=(4, 6, 5), k=(2, 4, 3), s=1, p="same", d=1, groups=1, dtype=torch.bfloat16),
+    dict(C=8, O=8, size=(5, 8, 8), k=3, s=1, p=1, d=1, groups=1, dtype=torch.float32),
+])
+def test_conv3d_on_the_implicit_kernel(cfg):
+    """Conv3d per-sample gradients, ghost norms and clipped sums run on the 2-d implicit-unfold kernel (one call per
+    kernel-depth offset over depth-stacked images) and agree with per-sample autograd."""
+    from opacus_b200.grad_sample.conv import (_implicit_geometry, compute_conv_grad_sample, compute_conv_norm_sq,
+                                              compute_conv_weighted_grad)
+    from opacus_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    B, dt = 3, cfg["dtype"]
+    conv = torch.nn.Conv3d(cfg["C"], cfg["O"], cfg["k"], stride=cfg["s"], padding=cfg["p"], dilation=cfg["d"],
+                           groups=cfg["groups"], bias=True).cuda().to(dt)
+    x = torch.randn(B, cfg["C"], *cfg["size"], device="cuda", dtype=dt)
+    g = torch.randn_like(conv(x))
+    assert _implicit_geometry(conv, x, g) is not None
+    ref = _conv_oracle_general(conv, x, g)
+    tol = 1e-2 if dt == torch.bfloat16 else 2e-4
+    rtol = 2e-3 if dt == torch.bfloat16 else 1e-4
+    out = compute_conv_grad_sample(conv, [x], g)
+    gw = out[conv.weight]
+    assert gw.shape == ref.shape
+    assert (gw.float() - ref).abs().max() <= tol * ref.abs().max()
+    nref = ref.flatten(1).square().sum(1)
+    torch.testing.assert_close(gw._dp_norm_sq, nref, rtol=rtol, atol=0)
+    torch.testing.assert_close(out[conv.bias].float(), g.float().flatten(2).sum(2), rtol=1e-2, atol=1e-2)
+    nsq = compute_conv_norm_sq(conv, [x], g, 2.0)
+    torch.testing.assert_close(nsq[conv.weight], 4.0 * nref, rtol=rtol, atol=0)
+    coef = torch.rand(B, device="cuda")
+    wg = compute_conv_weighted_grad(conv, [x], g, coef, 1.0)
+    wref = (ref * coef[:, None, None, None, None, None]).sum(0)
+    assert wg[conv.weight].shape == wref.shape
+    assert (wg[conv.weight].float() - wref).abs().max() <= tol * wref.abs().max()
+    _cuda.check_status()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("K,M,N,splits,beta", [(64, 256, 256, 1, 0.0), (1024, 512, 768, 1, 0.0), (300, 264, 200, 1, 0.0),
                                                 (4096, 512, 2048, 4, 0.0), (2048, 256, 512, 2, 1.0),
                                                 (128, 128, 64, 1, 1.0), (8192, 2048, 2048, 1, 0.0)])

@@ -373,3 +373,30 @@ def test_llama_matches_plain_definition():
     b.square().sum().backward()
     for (n, p), q in zip(ours.named_parameters(), plain.parameters()):
         assert torch.allclose(p.grad, q.grad, atol=1e-5), n
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(k=3, s=1, p=1, d=1, groups=1, size=(5, 6, 7)),
+    dict(k=(2, 3, 3), s=(2, 2, 1), p=(1, 0, 2), d=1, groups=1, size=(7, 9, 8)),
+    dict(k=(3, 2, 3), s=(1, 3, 2), p=(2, 1, 1), d=(2, 1, 1), groups=2, size=(6, 8, 9)),
+    dict(k=(2, 4, 3), s=1, p="same", d=1, groups=1, size=(4, 6, 5)),
+    dict(k=(1, 3, 3), s=(1, 2, 2), p="valid", d=1, groups=1, size=(3, 7, 7)),
+])
+def test_conv3d_as_depth_stacked_conv2d(cfg):
+    """The 2-d problems that carry a Conv3d onto the implicit-unfold kernel have exactly its weight gradient."""
+    from opacus_b200.grad_sample.conv import depth_stacked_pairs
+
+    torch.manual_seed(0)
+    B, C, O = 3, 4, 6
+    conv = torch.nn.Conv3d(C, O, cfg["k"], stride=cfg["s"], padding=cfg["p"], dilation=cfg["d"], groups=cfg["groups"],
+                           bias=False).double()
+    x = torch.randn(B, C, *cfg["size"], dtype=torch.float64)
+    y = conv(x)
+    g = torch.randn_like(y)
+    for b in range(B):
+        (want,) = torch.autograd.grad(conv(x[b:b + 1]), conv.weight, g[b:b + 1])
+        for a, x2, g2 in depth_stacked_pairs(conv, x[b:b + 1], g[b:b + 1]):
+            shape2 = (O, C // cfg["groups"]) + tuple(conv.kernel_size[1:])
+            got = torch.nn.grad.conv2d_weight(x2, shape2, g2.contiguous(), stride=conv.stride[1:], padding=0,
+                                              dilation=conv.dilation[1:], groups=cfg["groups"])
+            torch.testing.assert_close(got, want[:, :, a], rtol=1e-10, atol=1e-10)
