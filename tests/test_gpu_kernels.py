@@ -371,17 +371,19 @@ def test_conv_implicit_per_sample_grad(cfg):
 
 
 def _conv_oracle_general(conv, x, g):
-    """fp32 per-sample weight gradients through the layer's own forward (groups, string padding included)."""
+    """Per-sample weight gradients through the layer's own forward (groups, string padding included), computed in
+    fp64 (fp32 convolutions of the library may run on tf32 tensor cores, which is coarser than the kernels under test)
+    and returned in fp32."""
     import copy
 
-    ref = copy.deepcopy(conv).float()
+    ref = copy.deepcopy(conv).double()
     out = []
     for b in range(x.shape[0]):
         ref.zero_grad()
-        y = ref(x[b:b + 1].float())
-        (gw,) = torch.autograd.grad(y, ref.weight, g[b:b + 1].float())
+        y = ref(x[b:b + 1].double())
+        (gw,) = torch.autograd.grad(y, ref.weight, g[b:b + 1].double())
         out.append(gw)
-    return torch.stack(out)
+    return torch.stack(out).float()
 
 
 @pytest.mark.gpu
