@@ -138,7 +138,7 @@ for epoch in range(args.epochs):
 # %% [markdown]
 # ## What to tune
 # * `max_grad_norm`: too small biases the gradient, too large means more noise for the same guarantee; values around
-#   the median per-sample gradient norm work well (`optimizer.per_sample_gradient_norms` holds the last batch's).
+#   the median per-sample gradient norm work well (in ghost mode `model.per_sample_gradient_norms` holds the last batch's).
 # * batch size: larger logical batches improve the signal-to-noise ratio per step at the price of fewer steps per epoch.
 # * learning rate: usually lower than without privacy.
 # * `grad_sample_mode="ghost"` never materialises per-sample gradients (one backward pass in this package); it is the
