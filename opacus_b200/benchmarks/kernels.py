@@ -2,6 +2,7 @@
 
     python -m opacus_b200.benchmarks.kernels --op ghost_norm --B 8 --T 1024 --din 2048 --dout 8192
     python -m opacus_b200.benchmarks.kernels --op wgrad --B 8 --T 1024 --din 2048 --dout 8192
+    python -m opacus_b200.benchmarks.kernels --op wgrad_pair --B 8 --T 1024 --din 2048 --dout 8192
     python -m opacus_b200.benchmarks.kernels --op all
     python -m opacus_b200.benchmarks.kernels --op conv --B 512 --C 64 --O 64 --HW 32 --k 3
 
@@ -72,6 +73,14 @@ def run(op, B, T, din, dout, iters=20):
         rows.append(("wgrad_tn", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
         ms = _time(lambda: torch.matmul(gs.t(), a2), iters, flush)
         rows.append(("cublas_tn (library, for scale)", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+    if op in ("wgrad_pair", "all"):
+        # the same product on SM pairs (tcgen05 cta_group::2, clusters of two CTAs)
+        gs = g.reshape(B * T, dout).contiguous()
+        a2 = a.reshape(B * T, din).contiguous()
+        out = torch.empty(dout, din, device=dev)
+        flops = 2.0 * B * T * din * dout
+        ms = _time(lambda: C.wgrad2_tn(gs, a2, out, 0.0, 1), iters, flush)
+        rows.append(("wgrad2_tn (SM pairs)", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
     if op in ("weighted_grad", "all"):
         flops = 2.0 * B * T * din * dout
         ms = _time(lambda: ops.linear_weighted_grad(a, g, c), iters, flush)
