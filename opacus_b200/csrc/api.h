@@ -68,6 +68,14 @@ int dpk_scale_rows(const void* x, int x_is_fp32, const float* c, void* y_bf16, i
 // along the contraction axis give the fp32 product on the bf16 tensor cores up to a relative 2^-16.
 int dpk_split3_rows(const float* x, const float* c, void* y_bf16, int64_t rows, int64_t cols, int64_t T, float scale,
                     int right, cudaStream_t stream);
+// ---- ChaCha20 keystream (20 rounds, 64-bit block counter, 64-bit nonce; key8_host: eight host words).
+// dpk_chacha_words: n_blocks * 16 raw words.  dpk_chacha_normal: n Gaussians of deviation std by Box-Muller on word
+// pairs; draws == 4: element i = std * (sum of the four normals of words [4i, 4i+4)) / 2, draws == 1: the cosine normal
+// of words [2i, 2i+2).  `out` 16-byte aligned.
+int dpk_chacha_words(uint32_t* out, int64_t n_blocks, const uint32_t* key8_host, uint64_t nonce, uint64_t first_block,
+                     cudaStream_t stream);
+int dpk_chacha_normal(float* out, int64_t n, const uint32_t* key8_host, uint64_t nonce, uint64_t first_block, float std,
+                      int draws, cudaStream_t stream);
 // c[n] = min(1, C / (sqrt(max(norm_sq[n], 0)) + 1e-6))
 int dpk_clip_factor(const float* norm_sq, float* c, int64_t B, float max_grad_norm, cudaStream_t stream);
 // out[n] (+)= sum_j x[n, j]^2    (x: fp32 / bf16 / fp16 by elem_kind 0/1/2)

@@ -324,6 +324,33 @@ at::Tensor split3_rows(at::Tensor x, c10::optional<at::Tensor> c, int64_t T, dou
   return y;
 }
 
+// ChaCha20 keystream words / Gaussians into `out` (see dpk_chacha_words, dpk_chacha_normal); nonce and first block
+// are passed as Python ints below 2^64.
+void chacha_words(at::Tensor out, std::vector<int64_t> key, py::int_ nonce, py::int_ first_block) {
+  c10::cuda::CUDAGuard guard(out.device());
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(out.scalar_type() == at::kInt && out.numel() % 16 == 0, "out must be int32 with a multiple of 16 elements");
+  TORCH_CHECK(key.size() == 8, "key must have eight 32-bit words");
+  uint32_t k[8];
+  for (int i = 0; i < 8; ++i) k[i] = (uint32_t)key[i];
+  check(dpk_chacha_words(reinterpret_cast<uint32_t*>(out.data_ptr<int>()), out.numel() / 16, k,
+                         nonce.cast<uint64_t>(), first_block.cast<uint64_t>(), stream()),
+        "chacha_words");
+}
+
+void chacha_normal(at::Tensor out, std::vector<int64_t> key, py::int_ nonce, py::int_ first_block, double std,
+                   int64_t draws) {
+  c10::cuda::CUDAGuard guard(out.device());
+  need_cuda_contig(out, "out");
+  TORCH_CHECK(out.scalar_type() == at::kFloat, "out must be fp32");
+  TORCH_CHECK(key.size() == 8, "key must have eight 32-bit words");
+  uint32_t k[8];
+  for (int i = 0; i < 8; ++i) k[i] = (uint32_t)key[i];
+  check(dpk_chacha_normal(out.data_ptr<float>(), out.numel(), k, nonce.cast<uint64_t>(), first_block.cast<uint64_t>(),
+                          (float)std, (int)draws, stream()),
+        "chacha_normal");
+}
+
 at::Tensor clip_factor(at::Tensor n2, double C) {
   c10::cuda::CUDAGuard guard(n2.device());
   need_cuda_contig(n2, "norm_sq");
@@ -752,6 +779,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scale_rows", &scale_rows);
   m.def("clip_factor", &clip_factor);
   m.def("split3_rows", &split3_rows);
+  m.def("chacha_words", &chacha_words);
+  m.def("chacha_normal", &chacha_normal);
   m.def("row_norm_sq", &row_norm_sq);
   m.def("weighted_sum", &weighted_sum, py::arg("x"), py::arg("c"), py::arg("dest") = py::none());
   m.def("outer_norm_sq", &outer_norm_sq);

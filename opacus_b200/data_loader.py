@@ -8,7 +8,7 @@ import logging
 from typing import Any, List, Mapping, Optional, Sequence, Tuple, Type, Union
 
 import torch
-from torch.utils.data import BatchSampler, DataLoader, Dataset, IterableDataset, Sampler
+from torch.utils.data import BatchSampler, DataLoader, Dataset, IterableDataset, RandomSampler, Sampler
 from torch.utils.data._utils.collate import default_collate
 
 from .utils.uniform_sampler import DistributedUniformWithReplacementSampler, UniformWithReplacementSampler
@@ -126,7 +126,7 @@ class DPDataLoader(DataLoader):
                 sample_empty_shapes=[(0, *shape_safe(x)) for x in probe],
                 dtypes=[dtype_safe(x) for x in probe],
             ),
-            generator=generator,
+            generator=_torch_generator(generator),
             **kwargs,
         )
 
@@ -154,6 +154,12 @@ class DPDataLoader(DataLoader):
         )
 
 
+def _torch_generator(generator):
+    """What ``DataLoader(generator=...)`` may be given: a ``torch.Generator`` or None (it seeds worker processes and
+    the default sampler only; this package's ``SecureGenerator`` feeds the samplers directly)."""
+    return generator if generator is None or isinstance(generator, torch.Generator) else None
+
+
 def _is_supported_batch_sampler(sampler: Sampler):
     return isinstance(sampler, (BatchSampler, UniformWithReplacementSampler, DistributedUniformWithReplacementSampler))
 
@@ -169,8 +175,15 @@ def switch_generator(*, data_loader: DataLoader, generator):
     if isinstance(bs, BatchSampler):
         if not hasattr(bs.sampler, "generator"):
             raise ValueError("Target sampler doesn't have generator attribute: nothing to switch")
-        bs.sampler.generator = generator
+        if getattr(generator, "gaussian_like", None) is not None and isinstance(bs.sampler, RandomSampler):
+            # torch's sampler can only draw from a torch.Generator: same sampling, drawn from the ChaCha20 stream
+            from .utils.secure_rng import SecureRandomSampler
+
+            bs.sampler = SecureRandomSampler(bs.sampler.data_source, generator, replacement=bs.sampler.replacement,
+                                             num_samples=bs.sampler._num_samples)
+        else:
+            bs.sampler.generator = generator
     else:
         bs.generator = generator
     return DataLoader(dataset=data_loader.dataset, batch_sampler=bs, collate_fn=data_loader.collate_fn,
-                      generator=generator, **_carry(data_loader))
+                      generator=_torch_generator(generator), **_carry(data_loader))

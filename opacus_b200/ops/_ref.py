@@ -167,6 +167,9 @@ def gaussian_like(ref: torch.Tensor, std: float, generator=None, secure_mode: bo
     floating-point artefacts a single draw exposes (Mironov 2012)."""
     if std == 0:
         return torch.zeros_like(ref)
+    if getattr(generator, "gaussian_like", None) is not None:
+        # this package's ChaCha20 generator (utils/secure_rng.py): it implements the draw rule itself, on either device
+        return generator.gaussian_like(ref, std, draws=4 if secure_mode else 1)
     if not secure_mode:
         return torch.normal(mean=0, std=std, size=ref.shape, device=ref.device, dtype=ref.dtype, generator=generator)
     torch.normal(mean=0, std=std, size=(1, 1), device=ref.device, generator=generator)

@@ -70,12 +70,14 @@ class PrivacyEngine:
         if secure_mode:
             try:
                 import torchcsprng as csprng
-            except ImportError as e:
-                raise ImportError(
-                    "To use secure RNG, you must install the torchcsprng package! "
-                    "Check out the instructions here: https://github.com/pytorch/csprng#installation"
-                ) from e
-            self.secure_rng = csprng.create_random_device_generator("/dev/urandom")
+
+                self.secure_rng = csprng.create_random_device_generator("/dev/urandom")
+            except ImportError:
+                # the reference stops here; this package carries its own generator (ChaCha20 keyed from the OS
+                # entropy pool, the same stream on CPU and GPU)
+                from .utils.secure_rng import SecureGenerator
+
+                self.secure_rng = SecureGenerator()
         else:
             warnings.warn(
                 "Secure RNG turned off. This is perfectly fine for experimentation as it allows for much faster "

@@ -10,7 +10,10 @@ from torch.utils.data import Sampler
 
 
 def _bernoulli_indices(n: int, rate: float, generator) -> torch.Tensor:
-    """Indices ``i < n`` kept by independent coin flips of probability ``rate``."""
+    """Indices ``i < n`` kept by independent coin flips of probability ``rate``.  ``generator``: a ``torch.Generator``
+    (or None), or this package's ``SecureGenerator``, which draws its own uniforms."""
+    if getattr(generator, "gaussian_like", None) is not None:
+        return (generator.rand(n) < rate).nonzero(as_tuple=False).reshape(-1)
     return (torch.rand(n, generator=generator) < rate).nonzero(as_tuple=False).reshape(-1)
 
 

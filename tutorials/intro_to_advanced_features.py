@@ -177,11 +177,20 @@ print(f"5. median per-sample gradient norm over the epoch: {min(seen):.2f} .. {m
 
 # %% [markdown]
 # ## 6. Random numbers
-# `secure_mode=True` draws noise from a cryptographically secure generator and sums several draws per element to defeat
-# floating-point attacks; use it for the final run.  (It needs the `torchcsprng` package; this guide only shows the
-# switch.)  For reproducible experiments pass your own `noise_generator`.
+# `secure_mode=True` draws both the Poisson samples and the noise from a cryptographically secure generator (the
+# `torchcsprng` package if it is installed, otherwise this package's ChaCha20 generator keyed from the OS entropy pool,
+# which computes the same stream on CPU and GPU) and sums four draws per element to defeat floating-point attacks on the
+# Gaussian sampler.  Use it for the final run.  For reproducible experiments pass your own `noise_generator` instead
+# (the two are mutually exclusive: a seeded generator is the opposite of a secure one).
 
 # %%
+model, optimizer, loader = fresh()
+engine = PrivacyEngine(secure_mode=True)
+model, optimizer, loader = engine.make_private(module=model, optimizer=optimizer, data_loader=loader,
+                                                noise_multiplier=1.0, max_grad_norm=1.0)
+run(model, optimizer, loader)
+print(f"6. secure mode: generator {type(engine.secure_rng).__name__}, eps = {engine.get_epsilon(1e-5):.2f}")
+
 outs = []
 for _ in range(2):
     torch.manual_seed(1)
