@@ -97,6 +97,16 @@ def run(op, B, T, din, dout, iters=20):
         flops = 2.0 * 128 * 128 * dout * B * nT * (nT + 1) // 2
         ms = _time(lambda: ops.embedding_norm_sq(ids, g), iters, flush)
         rows.append(("embedding_ghost_norm", ms, flops / ms / 1e9, "TFLOP/s", flops / ms / 1e9 / tf_peak))
+    if op in ("secure_noise", "all"):
+        # secure-mode noise: ChaCha20 block per thread -> Box-Muller -> four draws summed and halved per element
+        from ..utils.secure_rng import SecureGenerator
+
+        gen = SecureGenerator()
+        ref = torch.empty(1 << 28, device=dev)
+        for draws in (4, 1):
+            ms = _time(lambda: gen.gaussian_like(ref, 1.0, draws=draws), max(2, iters // 4), flush)
+            rows.append((f"chacha_normal (draws={draws}, 2^28 elements)", ms, ref.numel() / ms / 1e6, "Gelem/s",
+                         ref.numel() * 4.0 / ms / 1e6 / bw_peak))
     if op in ("dp_step", "all"):
         n = 1 << 27
         p = torch.nn.Parameter(torch.zeros(n, device=dev))
