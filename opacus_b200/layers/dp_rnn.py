@@ -27,7 +27,14 @@ import torch.nn as nn
 from torch import Tensor
 from torch.nn.utils.rnn import PackedSequence
 
+from ..utils.packed_sequences import compute_seq_lengths  # noqa: F401  (re-exported as in the reference)
 from .param_rename import RenameParamsMixin
+
+
+def apply_permutation(tensor: Tensor, dim: int, permutation: Optional[Tensor]) -> Tensor:
+    """``tensor`` reordered along ``dim`` by ``permutation`` (unchanged when the permutation is None); the helper
+    that ``opacus/layers/dp_rnn.py:30-36`` exports for the sorted / unsorted indices of a ``PackedSequence``."""
+    return tensor if permutation is None else tensor.index_select(dim, permutation)
 
 
 class RNNLinear(nn.Linear):

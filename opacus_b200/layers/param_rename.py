@@ -68,3 +68,9 @@ def _drop_nested_names(module, state_dict, prefix, local_metadata):
     for old in module.old_to_new:
         state_dict.pop(prefix + old, None)
     return state_dict
+
+
+def filter_out_old_keys(self, state_dict, prefix, local_metadata):
+    """State-dict hook under the reference's name (``opacus/layers/param_rename.py:24-30``): a copy of ``state_dict``
+    without the pre-rename parameter names of ``self``."""
+    return {name: value for name, value in state_dict.items() if name not in self.old_to_new}
