@@ -281,7 +281,8 @@ def linear_weighted_grad(a, g, c, g_scale: float = 1.0, want_bias: bool = False,
         else:
             out = target
     elif _USE_PAIR_GEMM and d_out >= 256 and d_in >= 256:
-        # the same product on pairs of SMs (cta_group::2); measured equal to the one-CTA 256 x 256 tile, kept selectable
+        # the same product on pairs of SMs (cta_group::2): faster in isolation, no different inside a training step
+        # (two GEMM streams already fill each other's partial waves), hence opt-in
         tiles = -(-d_out // 256) * -(-d_in // 256)
         C.wgrad2_tn(g_op, a_op, out, 1.0 if accumulate else 0.0, 1 if tiles >= 64 else min(4, 74 // tiles))
     else:
