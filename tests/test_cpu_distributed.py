@@ -234,6 +234,35 @@ def test_tensor_parallel_noise_is_independent_between_shards_and_equal_on_replic
     assert not torch.equal(got[0][0]["col.weight"], got[0][1]["col.weight"])
 
 
+def _tp_secure_noise_job(rank, world):
+    """secure_mode: every rank has its own ChaCha20 generator keyed from the OS pool."""
+    from opacus_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, TensorParallelDPOptimizer
+    from opacus_b200.utils.secure_rng import SecureGenerator
+
+    torch.manual_seed(0)
+    full = _TPNet(nn.Linear(12, 256), nn.Linear(256, 12))
+    net = _TPNet(ColumnParallelLinear.from_linear(full.col), RowParallelLinear.from_linear(full.row))
+    opt = TensorParallelDPOptimizer(torch.optim.SGD(net.parameters(), lr=1.0), noise_multiplier=2.0, max_grad_norm=0.5,
+                                    expected_batch_size=1, loss_reduction="sum", generator=SecureGenerator(),
+                                    secure_mode=True)
+    for p in net.parameters():
+        p.summed_grad = torch.zeros_like(p)
+    opt.add_noise()
+    return {n: p.grad.detach().clone() for n, p in net.named_parameters()}
+
+
+def test_tensor_parallel_secure_noise_shards_independent_replicas_equal():
+    got = _run(_tp_secure_noise_job)
+    a, b = got[0], got[1]
+    for name in ("col.weight", "row.weight"):
+        za, zb = a[name].flatten(), b[name].flatten()
+        assert abs(float(za.std()) - 1.0) < 0.1 and abs(float(zb.std()) - 1.0) < 0.1
+        corr = float((za * zb).mean() / (za.std() * zb.std()))
+        assert abs(corr) < 5.0 / za.numel() ** 0.5, (name, corr)
+    for name in ("ln.weight", "ln.bias", "row.bias"):      # drawn by the first rank of the group, broadcast
+        assert torch.equal(a[name], b[name]) and float(a[name].abs().sum()) > 0
+
+
 def test_tensor_parallel_ghost_matches_unsharded():
     from opacus_b200.grad_sample import GradSampleModuleFastGradientClipping
     from opacus_b200.optimizers import DPOptimizerFastGradientClipping
