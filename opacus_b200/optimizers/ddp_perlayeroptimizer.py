@@ -42,6 +42,16 @@ from .optimizer import DPOptimizer, _generate_noise
 from .perlayeroptimizer import DPPerLayerOptimizer
 
 
+def _clip_and_accumulate_parameter(p: nn.Parameter, max_grad_norm: float) -> None:
+    """Clip the per-sample gradients of ONE parameter to ``max_grad_norm`` and add their sum to ``p.summed_grad``
+    (created on the parameter's device when it is None).  Module-level helper kept under the name the reference
+    exports (``opacus/optimizers/ddp_perlayeroptimizer.py:29-37``); the optimiser below runs the same three stages
+    from its gradient hook."""
+    gs = p.grad_sample
+    clipped = ops.weighted_sum(gs, ops.clip_factor(ops.grad_sample_norm_sq(gs), float(max_grad_norm))).view_as(p)
+    p.summed_grad = clipped if p.summed_grad is None else p.summed_grad + clipped.to(p.summed_grad.dtype)
+
+
 class SimpleDistributedPerLayerOptimizer(DPPerLayerOptimizer, DistributedDPOptimizer):
     def __init__(self, optimizer: Optimizer, *, noise_multiplier: float, max_grad_norm: float,
                  expected_batch_size: Optional[int], loss_reduction: str = "mean", generator=None,
