@@ -22,7 +22,8 @@ API = {
     ],
     "optimizers": [
         "AdaClipDPOptimizer", "DPOptimizer", "DPOptimizerFastGradientClipping", "DPPerLayerOptimizer",
-        "DistributedDPOptimizer", "FSDPOptimizerFastGradientClipping", "SimpleDistributedPerLayerOptimizer"
+        "DistributedDPOptimizer", "FSDPOptimizerFastGradientClipping", "SimpleDistributedPerLayerOptimizer",
+        "DistributedPerLayerOptimizer", "DistributedDPOptimizerFastGradientClipping", "get_optimizer_class"
     ],
     "accountants": [
         "GaussianAccountant", "IAccountant", "PRVAccountant", "RDPAccountant", "create_accountant",
