@@ -35,3 +35,19 @@ def test_tensor_parallel_examples(script, extra):
     out = _run(["-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                 "29788", os.path.join("examples", script)] + extra, timeout=400)
     assert "step 0" in out
+
+
+def test_cifar10_example():
+    out = _run(["examples/cifar10.py", "--logical-batch", "64", "--physical-batch", "32", "--steps", "1", "--device", "cpu"])
+    assert "epsilon" in out
+
+
+def test_imdb_example():
+    out = _run(["examples/imdb.py", "--epochs", "1", "--device", "cpu"])
+    assert "epsilon spent" in out
+
+
+def test_vision_benchmark_example():
+    out = _run(["examples/vision_benchmark.py", "--device", "cpu", "--architecture", "cnn", "--batch-size", "16",
+                "--steps", "2", "--modes", "none,hooks,ghost"])
+    assert "of non-private" in out and "ghost" in out
