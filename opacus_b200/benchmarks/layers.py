@@ -1,7 +1,7 @@
 """Per-layer DP step timing: forward + backward + clip + noise + SGD step of a
 single layer at batch 64, in hooks and ghost-clipping modes, fp32 and bf16.
 
-    python -m opacus_b200.benchmarks.layers [--impl ours|reference] [--dtype fp32|bf16|both]
+    python -m opacus_b200.benchmarks.layers [--impl ours|reference] [--dtype fp32|bf16|both] [--batch 64]
                                             [--layers linear,conv,...] [--iters 20] [--json out.json]
 
 Layers and shapes: Linear 512->512 on [64,128,512]; Conv2d 64->64 k3 on
@@ -182,12 +182,15 @@ def main():
     ap.add_argument("--layers", default="all")
     ap.add_argument("--modes", default="hooks,ghost")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=64, help="samples per step (the reference's suite sweeps 16 ... 512)")
     ap.add_argument("--json", default=None)
     ap.add_argument("--kernels", action="store_true", help="list the GEMM-shaped kernels of one step per row")
     args = ap.parse_args()
     import warnings
 
     warnings.simplefilter("ignore")
+    global B
+    B = args.batch
     lib = _load(args.impl)
     specs = _specs(lib)
     names = list(specs) if args.layers == "all" else args.layers.split(",")
@@ -206,7 +209,7 @@ def main():
                     err = None
                 except Exception as e:  # a layer/mode/dtype the library cannot run is reported, not fatal
                     ms, err = None, f"{type(e).__name__}: {str(e)[:120]}"
-                rows.append({"impl": args.impl, "layer": name, "dtype": str(dt).split(".")[-1], "mode": mode,
+                rows.append({"impl": args.impl, "layer": name, "dtype": str(dt).split(".")[-1], "mode": mode, "batch": B,
                              "ms": ms, "peak_mb": peak, "gemm_kernels": kernels, "error": err})
                 shown = f"{ms:9.3f} ms {peak:10.1f} MB" if ms is not None else f"   failed ({err})"
                 print(f"{name:13s} {str(dt).split('.')[-1]:9s} {mode:6s} {shown}"
