@@ -100,3 +100,47 @@ def test_cli(capsys):
     main(["-r", "0.04", "-n", "1.5", "-e", "90", "-d", "1e-5"])
     out = capsys.readouterr().out
     assert "7.3" in out
+
+
+# ---- invariants (property-based): what any privacy accountant must satisfy
+from hypothesis import given, settings  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+
+def _eps(kind, sigma, q, steps, delta=1e-5):
+    from opacus_b200.accountants import create_accountant
+
+    acc = create_accountant(kind)
+    acc.history = [(sigma, q, steps)]
+    return acc.get_epsilon(delta)
+
+
+@settings(max_examples=25, deadline=None)
+@given(sigma=st.floats(0.6, 4.0), q=st.floats(0.001, 0.2), steps=st.integers(1, 2000))
+def test_rdp_epsilon_grows_with_steps_and_rate_and_falls_with_noise(sigma, q, steps):
+    base = _eps("rdp", sigma, q, steps)
+    assert base >= 0
+    assert _eps("rdp", sigma, q, steps * 2) >= base - 1e-9
+    assert _eps("rdp", sigma * 1.5, q, steps) <= base + 1e-9
+    assert _eps("rdp", sigma, min(1.0, q * 1.5), steps) >= base - 1e-9
+    # a weaker delta can only make epsilon smaller
+    assert _eps("rdp", sigma, q, steps, delta=1e-3) <= base + 1e-9
+
+
+@settings(max_examples=10, deadline=None)
+@given(sigma=st.floats(0.8, 3.0), q=st.floats(0.005, 0.1), steps=st.integers(10, 1000))
+def test_prv_is_not_looser_than_rdp_by_more_than_its_error_and_both_agree_roughly(sigma, q, steps):
+    rdp, prv = _eps("rdp", sigma, q, steps), _eps("prv", sigma, q, steps)
+    assert prv <= rdp * 1.02 + 0.05           # the numerical composition is the tighter analysis
+    assert prv >= 0.3 * rdp - 0.05            # and not wildly different
+
+
+@settings(max_examples=8, deadline=None)
+@given(eps=st.floats(0.5, 10.0), q=st.floats(0.005, 0.1), steps=st.integers(50, 2000))
+def test_noise_multiplier_search_meets_its_target(eps, q, steps):
+    from opacus_b200.accountants.utils import get_noise_multiplier
+
+    sigma = get_noise_multiplier(target_epsilon=eps, target_delta=1e-5, sample_rate=q, steps=steps, accountant="rdp",
+                                 epsilon_tolerance=0.01)
+    got = _eps("rdp", sigma, q, steps)
+    assert got <= eps + 1e-6 and got >= eps - 0.05 - 0.02 * eps
