@@ -26,3 +26,24 @@ def test_tutorial_runs(script, argv, expect):
                          timeout=600, env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     assert expect in out.stdout, out.stdout[-2000:]
+
+
+def test_notebooks_match_their_scripts():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "tutorials", "make_notebooks.py"), "--check"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_a_notebook_executes_cell_by_cell():
+    """The code cells of one generated notebook run in order in a fresh namespace, from the notebooks folder."""
+    import json
+
+    path = os.path.join(ROOT, "tutorials", "notebooks", "guide_to_module_validator.ipynb")
+    with open(path, encoding="utf-8") as f:
+        cells = [c for c in json.load(f)["cells"] if c["cell_type"] == "code"]
+    program = "\n\n".join("".join(c["source"]) for c in cells)
+    out = subprocess.run([sys.executable, "-c", program], capture_output=True, text=True, timeout=300,
+                         cwd=os.path.join(ROOT, "tutorials", "notebooks"),
+                         env=dict(os.environ, PYTHONWARNINGS="ignore", CUDA_VISIBLE_DEVICES=""))
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "SampleMaxScale" in out.stdout

@@ -115,7 +115,7 @@ if __name__ == "__main__":
     ap.add_argument("--sigma", type=float, default=1.0)
     ap.add_argument("--clip", type=float, default=1.0)
     ap.add_argument("--lr", type=float, default=0.2)
-    args = ap.parse_args()
+    args, _ = ap.parse_known_args()          # a notebook kernel passes arguments of its own
     if args.spawn:
         args.cpu = args.cpu or torch.cuda.device_count() < args.spawn
         mp.spawn(_spawned, args=(args.spawn, args), nprocs=args.spawn, join=True)
