@@ -632,28 +632,38 @@ class ShardedDataParallel(nn.Module):
         dev = self.master.device
         h = dict(lr=float(g0["lr"]), momentum=0.0, dampening=0.0, weight_decay=float(g0.get("weight_decay", 0.0)),
                  beta1=0.0, beta2=0.0, eps=0.0, bias_c1=1.0, bias_c2_sqrt=1.0)
-        first_step, nesterov, kcode = False, False, 0
-        if kind == "sgd":
-            h["momentum"] = float(g0.get("momentum", 0.0))
-            h["dampening"] = float(g0.get("dampening", 0.0))
-            nesterov = bool(g0.get("nesterov", False))
-            if h["momentum"] != 0.0 and self.state0 is None:
-                self.state0 = torch.zeros(self.slice_len, dtype=torch.float32, device=dev)
-                first_step = True
-        else:
-            b1, b2 = g0["betas"]
-            if self.state0 is None:
-                self.state0 = torch.zeros(self.slice_len, dtype=torch.float32, device=dev)
-                self.state1 = torch.zeros(self.slice_len, dtype=torch.float32, device=dev)
-            h.update(beta1=float(b1), beta2=float(b2), eps=float(g0["eps"]), bias_c1=1.0 - float(b1) ** t,
-                     bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
-            kcode = 2 if kind == "adamw" else 1
         runs = self._ready_runs(had_fresh) if self.overlap_step else None
         side = None
         if runs is not None:
             side = self._step_stream
             if side is None:
                 side = self._step_stream = torch.cuda.Stream(device=dev)
+
+        def zeros_for_state():
+            # Optimiser state that is born in this step is zero-filled on the stream that runs the step: on the
+            # main stream the fill would queue behind every weight-gradient GEMM of this pass, i.e. after the
+            # pieces of the side stream had already read and written the state.
+            if side is None:
+                return torch.zeros(self.slice_len, dtype=torch.float32, device=dev)
+            with torch.cuda.stream(side):
+                return torch.zeros(self.slice_len, dtype=torch.float32, device=dev)
+
+        first_step, nesterov, kcode = False, False, 0
+        if kind == "sgd":
+            h["momentum"] = float(g0.get("momentum", 0.0))
+            h["dampening"] = float(g0.get("dampening", 0.0))
+            nesterov = bool(g0.get("nesterov", False))
+            if h["momentum"] != 0.0 and self.state0 is None:
+                self.state0 = zeros_for_state()
+                first_step = True
+        else:
+            b1, b2 = g0["betas"]
+            if self.state0 is None:
+                self.state0 = zeros_for_state()
+                self.state1 = zeros_for_state()
+            h.update(beta1=float(b1), beta2=float(b2), eps=float(g0["eps"]), bias_c1=1.0 - float(b1) ** t,
+                     bias_c2_sqrt=math.sqrt(1.0 - float(b2) ** t))
+            kcode = 2 if kind == "adamw" else 1
         # The table of per-group ranges is uploaded on the stream that will run the step: the main stream still holds
         # every weight-gradient GEMM of this pass, and waiting for it would undo the overlap of the pieces.
         if per_group is None:
@@ -711,6 +721,8 @@ class ShardedDataParallel(nn.Module):
 
         if secure:
             runs = None                       # the host-side noise was added on the main stream, behind all GEMMs
+            if side is not None:              # what was prepared on the side stream (segment table, new state)
+                torch.cuda.current_stream(dev).wait_stream(side)
         if runs is None:
             launch(0, self.pieces, self.single_launch_blocks)
             self.last_step_launches = 1
